@@ -1,0 +1,263 @@
+"""The cache manager: pages of keys and values with a block table per request, and slots for
+per-request state of fixed size.
+
+What the model asks for arrives as ``StateSpec``s keyed by (entry of the layer list, name).
+Paged specs are sorted into *groups* by what they keep (every position, or a window of the last
+``w``); each group has its own pool of page numbers and its own block table per request, and
+every layer of the group indexes its own tensor ``[pages, 2, kv_heads, page, head_dim]`` with
+the group's page numbers. Pages return to the group's pool when the request ends, or, in a
+window group, as soon as no later query can see them, and are handed out again (lowest number
+first, so runs are reproducible). Page 0 of every pool and slot 0 are never handed out: padded
+rows of a batch point there. Fixed-size state (``SlotState``) is a row ``[*shape]`` per request
+in a ``[slots, *shape]`` tensor; a request starting at position 0 reads it as zeros by
+contract, so rows are not cleared on reuse.
+
+The bookkeeping is plain host code and is tested without a GPU (``device="meta"`` or "cpu");
+the reference keeps the same books on the device (Tokenomos core/state.py:19-46,
+core/pools.py:90-108, kernels/engine/slots.py:20-108).
+"""
+
+from __future__ import annotations
+
+import heapq
+from dataclasses import dataclass, field
+
+import torch
+
+from tokenomos_b200.parts.contract import (PagedKV, SharedState, SlotState, StateKey, StateSpec,
+                                           WindowKV)
+
+
+class OutOfPages(RuntimeError):
+    """A request needs more pages (or a slot) than the pool has free right now."""
+
+
+class CacheError(RuntimeError):
+    """The manager's books were used wrongly (unknown request, double free, ...)."""
+
+
+class FreeList:
+    """Numbers ``first .. count-1``, handed out lowest first, each held at most once."""
+
+    def __init__(self, count: int, first: int = 1):
+        self.count, self.first = count, first
+        self._heap = list(range(first, count))
+        heapq.heapify(self._heap)
+        self._held: set[int] = set()
+
+    def __len__(self) -> int:
+        return len(self._heap)
+
+    def take(self) -> int:
+        if not self._heap:
+            raise OutOfPages("pool is empty")
+        n = heapq.heappop(self._heap)
+        self._held.add(n)
+        return n
+
+    def give(self, n: int) -> None:
+        if n not in self._held:
+            raise CacheError(f"{n} given back but not held (freed twice, or never taken)")
+        self._held.remove(n)
+        heapq.heappush(self._heap, n)
+
+    @property
+    def held(self) -> set[int]:
+        return self._held
+
+
+@dataclass
+class Group:
+    """Paged layers that keep the same positions: one page numbering, one block table."""
+
+    key: tuple
+    window: int | None
+    pages: FreeList
+    members: list[StateKey] = field(default_factory=list)
+
+
+@dataclass
+class RequestState:
+    slot: int
+    length: int = 0                                   # tokens in the cache
+    reserved: int = 0                                 # tokens pages are held for (>= length)
+    tables: dict[tuple, list[int]] = field(default_factory=dict)  # group -> page per block (0: none)
+
+
+class CacheManager:
+    def __init__(self, specs: dict[StateKey, StateSpec], page_size: int, num_pages: int,
+                 max_requests: int, dtype: torch.dtype, device, max_len: int | None = None):
+        """``num_pages``: pages of each group's pool, the null page included. ``max_requests``:
+        live requests (slots 1..max_requests). ``max_len``: longest sequence (sets the block
+        table's width; default: what the pool could hold)."""
+        if page_size < 1 or num_pages < 2 or max_requests < 1:
+            raise ValueError("cache: page_size >= 1, num_pages >= 2 (page 0 is the null page), "
+                             "max_requests >= 1")
+        self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
+        self.dtype, self.device = dtype, torch.device(device)
+        self.max_len = max_len or (num_pages - 1) * page_size
+        self.max_blocks = -(-self.max_len // page_size)
+        self.specs = dict(specs)
+        self.groups: dict[tuple, Group] = {}
+        self.states: dict[StateKey, torch.Tensor] = {}
+        self.state_groups: dict[StateKey, tuple] = {}
+        self.slots = FreeList(max_requests + 1, first=1)
+        self.requests: dict[object, RequestState] = {}
+        for key, spec in specs.items():
+            if isinstance(spec, (PagedKV, WindowKV)):
+                g = self.groups.get(spec.group)
+                if g is None:
+                    window = spec.window if isinstance(spec, WindowKV) else None
+                    g = self.groups[spec.group] = Group(spec.group, window, FreeList(num_pages))
+                g.members.append(key)
+                shape = (num_pages, 2, spec.kv_heads, page_size, spec.head_dim)
+                self.states[key] = torch.zeros(shape, dtype=dtype, device=self.device)
+                self.state_groups[key] = spec.group
+            elif isinstance(spec, SlotState):
+                self.states[key] = torch.zeros((max_requests + 1, *spec.shape),
+                                               dtype=spec.dtype or dtype, device=self.device)
+        for key, spec in specs.items():
+            if isinstance(spec, SharedState):
+                src = (spec.source, spec.name)
+                if src not in self.states:
+                    raise ValueError(f"state {key} reads {src}, which owns no memory")
+                self.states[key] = self.states[src]
+                if src in self.state_groups:
+                    self.state_groups[key] = self.state_groups[src]
+
+    # ---- sizes ----
+
+    def bytes_per_page(self) -> int:
+        """Bytes one page costs across every paged layer (all groups)."""
+        total = 0
+        for key, spec in self.specs.items():
+            if isinstance(spec, (PagedKV, WindowKV)):
+                total += 2 * spec.kv_heads * self.page_size * spec.head_dim * self.dtype.itemsize
+        return total
+
+    def free_pages(self, group: tuple | None = None) -> int:
+        """Free pages of ``group``, or the smallest count over the groups."""
+        if group is not None:
+            return len(self.groups[group].pages)
+        return min((len(g.pages) for g in self.groups.values()), default=1 << 30)
+
+    def free_slots(self) -> int:
+        return len(self.slots)
+
+    # ---- a request's life ----
+
+    def admit(self, rid) -> RequestState:
+        """Give ``rid`` a slot (no pages yet)."""
+        if rid in self.requests:
+            raise CacheError(f"request {rid!r} is already live")
+        if not len(self.slots):
+            raise OutOfPages("no free slot")
+        st = RequestState(self.slots.take(), tables={k: [] for k in self.groups})
+        self.requests[rid] = st
+        return st
+
+    def _first_needed_block(self, g: Group, ctx: int) -> int:
+        """First block a query at position ``ctx`` or later can read in group ``g``."""
+        if g.window is None:
+            return 0
+        return max(0, ctx - g.window + 1) // self.page_size
+
+    def pages_needed(self, rid, n_new: int) -> dict[tuple, int]:
+        """Pages each group must still hand out so ``rid`` can take ``n_new`` more tokens."""
+        st = self._get(rid)
+        end_block = -(-(st.length + n_new) // self.page_size)
+        need = {}
+        for k, g in self.groups.items():
+            table = st.tables[k]
+            lo = self._first_needed_block(g, st.length)
+            have = sum(1 for b in range(lo, min(len(table), end_block)) if table[b])
+            need[k] = max(0, end_block - lo - have)
+        return need
+
+    def can_extend(self, rid, n_new: int) -> bool:
+        if self._get(rid).length + n_new > self.max_len:
+            return False
+        return all(n <= len(self.groups[k].pages) for k, n in self.pages_needed(rid, n_new).items())
+
+    def extend(self, rid, n_new: int) -> None:
+        """Hold pages for positions ``[length, length + n_new)`` in every group; all or nothing."""
+        st = self._get(rid)
+        if st.length + n_new > self.max_len:
+            raise OutOfPages(f"request {rid!r}: {st.length} + {n_new} tokens exceed the longest "
+                             f"sequence the block table holds ({self.max_len})")
+        need = self.pages_needed(rid, n_new)
+        short = {k: (n, len(self.groups[k].pages)) for k, n in need.items()
+                 if n > len(self.groups[k].pages)}
+        if short:
+            raise OutOfPages(f"request {rid!r} needs pages (group: needed, free) {short}")
+        end_block = -(-(st.length + n_new) // self.page_size)
+        for k, g in self.groups.items():
+            table = st.tables[k]
+            lo = self._first_needed_block(g, st.length)
+            while len(table) < end_block:
+                table.append(0)
+            for b in range(lo, end_block):
+                if not table[b]:
+                    table[b] = g.pages.take()
+        st.reserved = max(st.reserved, st.length + n_new)
+
+    def commit(self, rid, n_new: int) -> None:
+        """The step wrote ``n_new`` tokens: advance, and give back what a window has passed."""
+        st = self._get(rid)
+        if st.length + n_new > st.reserved:
+            raise CacheError(f"request {rid!r}: commit of {n_new} tokens beyond what was extended")
+        st.length += n_new
+        for k, g in self.groups.items():
+            if g.window is None:
+                continue
+            table = st.tables[k]
+            for b in range(min(self._first_needed_block(g, st.length), len(table))):
+                if table[b]:
+                    g.pages.give(table[b])
+                    table[b] = 0
+
+    def release(self, rid) -> None:
+        """The request ended: its pages and its slot go back."""
+        st = self.requests.pop(rid, None)
+        if st is None:
+            raise CacheError(f"request {rid!r} is not live (released twice?)")
+        for k, g in self.groups.items():
+            for page in st.tables[k]:
+                if page:
+                    g.pages.give(page)
+        self.slots.give(st.slot)
+
+    def _get(self, rid) -> RequestState:
+        st = self.requests.get(rid)
+        if st is None:
+            raise CacheError(f"request {rid!r} is not live")
+        return st
+
+    def length(self, rid) -> int:
+        return self._get(rid).length
+
+    def slot(self, rid) -> int:
+        return self._get(rid).slot
+
+    def block_table(self, rid, group: tuple) -> list[int]:
+        return self._get(rid).tables[group]
+
+    # ---- invariants (tests call this after every operation) ----
+
+    def check(self) -> None:
+        """No page lost, none held twice: per group, pages held by requests and free pages
+        partition ``1 .. num_pages-1``; same for slots."""
+        for k, g in self.groups.items():
+            held = [p for st in self.requests.values() for p in st.tables[k] if p]
+            if len(held) != len(set(held)):
+                raise CacheError(f"group {k}: a page is held twice")
+            if set(held) != g.pages.held:
+                raise CacheError(f"group {k}: pages held by requests differ from the pool's books")
+            free = set(g.pages._heap)
+            if len(free) != len(g.pages._heap) or free & set(held):
+                raise CacheError(f"group {k}: a page is both free and held, or free twice")
+            if free | set(held) != set(range(1, self.num_pages)):
+                raise CacheError(f"group {k}: a page is lost")
+        slots = [st.slot for st in self.requests.values()]
+        if len(slots) != len(set(slots)) or set(slots) != self.slots.held:
+            raise CacheError("slots: held twice or lost")

@@ -1,0 +1,92 @@
+// Shared device helpers for the sm_100a kernels: storage-type conversion (float or bfloat16
+// storage, 32-bit arithmetic everywhere), warp/block reductions, and the error channel that the
+// extern "C" entry points use (every entry point returns 0 or a negative code and leaves a
+// message that tk_last_error() hands to Python).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TK_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side (ops/_lib.py)
+enum TkDtype : int { TK_F32 = 0, TK_BF16 = 1 };
+
+void tk_set_error(const char* fmt, ...);
+
+#define TK_CHECK_ARG(cond, ...)            \
+    do {                                   \
+        if (!(cond)) {                     \
+            tk_set_error(__VA_ARGS__);     \
+            return -1;                     \
+        }                                  \
+    } while (0)
+
+#define TK_CHECK_LAUNCH(name)                                                   \
+    do {                                                                        \
+        cudaError_t e__ = cudaGetLastError();                                   \
+        if (e__ != cudaSuccess) {                                               \
+            tk_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+            return -2;                                                          \
+        }                                                                       \
+    } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// The value as it would read back after a store in T: the places where the 16-bit path rounds.
+template <typename T>
+__device__ __forceinline__ float round_as(float v) {
+    return to_f<T>(from_f<T>(v));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // `red` may still be read from an earlier call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

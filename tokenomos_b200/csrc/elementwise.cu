@@ -1,0 +1,188 @@
+// Row-wise kernels of the residual stream: embedding / row gather, residual add + RMSNorm,
+// SwiGLU, and the per-head sigmoid gate. Storage is float or bfloat16; statistics, sums and
+// products are formed in 32-bit and rounded where the 16-bit reference rounds
+// (Tokenomos kernels/norm/fused.py:22-28,69-82; models/blocks/ffn.py:31).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// gather: out[r, :] = table[ids[r], :]  (embedding lookup, and row selection before the head)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                   T* __restrict__ out, int width, int rows_in_table) {
+    const int r = blockIdx.x;
+    int id = ids[r];
+    // an id outside the table would read foreign memory: clamp (callers validate on the host)
+    id = id < 0 ? 0 : (id >= rows_in_table ? rows_in_table - 1 : id);
+    const T* src = table + (size_t)id * width;
+    T* dst = out + (size_t)r * width;
+    constexpr int VEC = 16 / sizeof(T);
+    if (width % VEC == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < width / VEC; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+TK_API int tk_gather_rows(const void* table, const int* ids, void* out, int rows, int width,
+                          int rows_in_table, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0 && rows_in_table > 0, "gather_rows: bad sizes rows=%d width=%d table=%d",
+                 rows, width, rows_in_table);
+    if (rows == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == TK_F32)
+        gather_rows_kernel<float><<<rows, threads, 0, stream>>>((const float*)table, ids, (float*)out,
+                                                               width, rows_in_table);
+    else if (dtype == TK_BF16)
+        gather_rows_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(
+            (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, width, rows_in_table);
+    else
+        TK_CHECK_ARG(false, "gather_rows: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("gather_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// add + RMSNorm: stream = round(residual + [prenorm](x)); y = round(round(stream*rstd) * w)
+// One block per row; the row lives in shared memory as float. `x` may be a strided view.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, int64_t x_stride,
+                                   const T* __restrict__ residual, const float* __restrict__ pre_w,
+                                   float pre_eps, const float* __restrict__ w, float eps,
+                                   T* __restrict__ y, T* __restrict__ stream, int width) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const T* xr = x + (size_t)r * x_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = to_f<T>(xr[i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    if (pre_w != nullptr) {
+        // sandwich norm on the block output before it joins the stream
+        const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + pre_eps);
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            row[i] = round_as<T>(round_as<T>(row[i] * rstd) * pre_w[i]);
+    }
+    if (residual != nullptr || pre_w != nullptr) {
+        ss = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = row[i];
+            if (residual != nullptr) v = round_as<T>(v + to_f<T>(residual[(size_t)r * width + i]));
+            row[i] = v;
+            ss += v * v;
+            if (stream != nullptr) stream[(size_t)r * width + i] = from_f<T>(v);
+        }
+    }
+    if (w == nullptr) return;  // the stream alone
+    const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        y[(size_t)r * width + i] = from_f<T>(round_as<T>(row[i] * rstd) * w[i]);
+}
+
+TK_API int tk_add_rmsnorm(const void* x, int64_t x_stride, const void* residual,
+                          const float* pre_w, float pre_eps, const float* w, float eps, void* y,
+                          void* stream_out, int rows, int width, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0, "add_rmsnorm: bad sizes rows=%d width=%d", rows, width);
+    TK_CHECK_ARG((size_t)width * sizeof(float) <= 200 * 1024,
+                 "add_rmsnorm: width %d does not fit a row in shared memory (limit 51200)", width);
+    TK_CHECK_ARG(w == nullptr || y != nullptr, "add_rmsnorm: norm weight without an output");
+    if (rows == 0) return 0;
+    const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    const size_t smem = (size_t)width * sizeof(float);
+    if (dtype == TK_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<rows, threads, smem, stream>>>(
+            (const float*)x, x_stride, (const float*)residual, pre_w, pre_eps, w, eps, (float*)y,
+            (float*)stream_out, width);
+    } else if (dtype == TK_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>(
+            (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)residual, pre_w, pre_eps, w, eps,
+            (__nv_bfloat16*)y, (__nv_bfloat16*)stream_out, width);
+    } else {
+        TK_CHECK_ARG(false, "add_rmsnorm: unknown dtype %d", dtype);
+    }
+    TK_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = round(round(silu(g[t, i])) * u[t, i]) with gu = [g | u] of width 2*inter
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total,
+                              int inter) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (; i < total; i += step) {
+        const int64_t t = i / inter;
+        const int c = (int)(i - t * inter);
+        const float g = to_f<T>(gu[t * 2 * inter + c]);
+        const float u = to_f<T>(gu[t * 2 * inter + inter + c]);
+        const float s = round_as<T>(g / (1.0f + expf(-g)));
+        out[i] = from_f<T>(s * u);
+    }
+}
+
+TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int dtype,
+                     cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    if (rows == 0) return 0;
+    const int64_t total = (int64_t)rows * inter;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
+                                                                        : 148 * 16);
+    if (dtype == TK_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+    else if (dtype == TK_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+    else
+        TK_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-head sigmoid gate: x[t, h, :] = round(x[t, h, :] * round(sigmoid(g[t, h])))
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int64_t total,
+                                 int head_dim) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (; i < total; i += step) {
+        const float gate = to_f<T>(g[i / head_dim]);
+        const float s = round_as<T>(1.0f / (1.0f + expf(-gate)));
+        x[i] = from_f<T>(to_f<T>(x[i]) * s);
+    }
+}
+
+TK_API int tk_head_gate(void* x, const void* g, int rows, int heads, int head_dim, int dtype,
+                        cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && heads > 0 && head_dim > 0, "head_gate: bad sizes");
+    if (rows == 0) return 0;
+    const int64_t total = (int64_t)rows * heads * head_dim;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
+                                                                        : 148 * 16);
+    if (dtype == TK_F32)
+        head_gate_kernel<float><<<blocks, threads, 0, stream>>>((float*)x, (const float*)g, total, head_dim);
+    else if (dtype == TK_BF16)
+        head_gate_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            (__nv_bfloat16*)x, (const __nv_bfloat16*)g, total, head_dim);
+    else
+        TK_CHECK_ARG(false, "head_gate: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("head_gate");
+    return 0;
+}

@@ -1,0 +1,106 @@
+// Per-head q/k RMSNorm + rotate-half RoPE on the fused qkv projection, with the new keys and
+// values written straight into the paged cache (one kernel instead of norm, rotate, write).
+//
+// Formulas (Tokenomos kernels/attention/qk.py:21-30,72-94; models/blocks/rope.py:33-35,51-59):
+//   y = round(round(x * rstd) * w),  rstd = 1/sqrt(mean(x^2) + eps)      (q and k heads)
+//   f = float(pos) * inv_freq[c mod R/2];  cos, sin rounded to the storage type
+//   out[c] = y[c]*cos + rot[c]*sin,  rot[c] = -y[c + R/2] (c < R/2) else y[c - R/2]; c >= R passes
+// V is neither normed nor rotated.  Cache layout: [pages, 2 (K|V), Hkv, P, D].
+#include "common.cuh"
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(
+    const T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ q_out, T* __restrict__ kv_pool,
+    const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const int* __restrict__ tok_seq, const int* __restrict__ block_table, int bt_stride, int H,
+    int Hkv, int D, int R, int P) {
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    float* buf = smem + warp * D;
+    const int pos = positions[t];
+    const int half = R >> 1;
+    size_t cache_row = 0;
+    if (Hkv > 0) {
+        const int s = tok_seq[t];
+        const int page = block_table[(size_t)s * bt_stride + pos / P];
+        cache_row = (size_t)page * 2 * Hkv * P + (pos % P);  // + (kv*Hkv + kh)*P rows
+    }
+    const T* row = qkv + (size_t)t * qkv_stride;
+    for (int hh = warp; hh < H + 2 * Hkv; hh += nwarp) {
+        const T* src = row + (size_t)hh * D;
+        T* dst;
+        const float* w = nullptr;
+        bool rotate = true;
+        if (hh < H) {
+            dst = q_out + ((size_t)t * H + hh) * D;
+            w = wq;
+        } else if (hh < H + Hkv) {
+            const int kh = hh - H;
+            dst = kv_pool + (cache_row + (size_t)kh * P) * D;
+            w = wk;
+        } else {
+            const int kh = hh - H - Hkv;
+            dst = kv_pool + (cache_row + (size_t)(Hkv + kh) * P) * D;
+            rotate = false;
+        }
+        if (!rotate) {
+            for (int c = lane; c < D; c += 32) dst[c] = src[c];
+            continue;
+        }
+        float ss = 0.f;
+        for (int c = lane; c < D; c += 32) {
+            const float v = to_f<T>(src[c]);
+            buf[c] = v;
+            ss += v * v;
+        }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+            for (int c = lane; c < D; c += 32) buf[c] = round_as<T>(round_as<T>(buf[c] * rstd) * w[c]);
+        }
+        __syncwarp();
+        for (int c = lane; c < D; c += 32) {
+            float o = buf[c];
+            if (c < R) {
+                const int i = c < half ? c : c - half;
+                const float f = (float)pos * inv_freq[i];
+                const float cs = round_as<T>(cosf(f)), sn = round_as<T>(sinf(f));
+                const float rot = c < half ? -buf[c + half] : buf[c - half];
+                o = o * cs + rot * sn;
+            }
+            dst[c] = from_f<T>(o);
+        }
+        __syncwarp();
+    }
+}
+
+// qkv: [T, (H + 2*Hkv) * D] with row stride `qkv_stride` (elements); Hkv = 0 for a layer that
+// only has queries (it reads another layer's cache). wq / wk may be null (no q/k norm).
+TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_out, void* kv_pool,
+                                 const float* wq, const float* wk, float eps,
+                                 const float* inv_freq, const int* positions, const int* tok_seq,
+                                 const int* block_table, int bt_stride, int T_, int H, int Hkv,
+                                 int D, int R, int P, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(T_ >= 0 && H > 0 && Hkv >= 0 && D > 0 && P > 0, "qk_norm_rope_write: bad sizes");
+    TK_CHECK_ARG(R >= 0 && R <= D && R % 2 == 0, "qk_norm_rope_write: rotary width %d of head %d", R, D);
+    TK_CHECK_ARG(D <= 1024, "qk_norm_rope_write: head_dim %d above the limit of 1024", D);
+    TK_CHECK_ARG((wq == nullptr) == (wk == nullptr) || Hkv == 0,
+                 "qk_norm_rope_write: q and k norms come together");
+    if (T_ == 0) return 0;
+    const int threads = 128;
+    const size_t smem = (size_t)(threads / 32) * D * sizeof(float);
+    if (dtype == TK_F32)
+        qk_norm_rope_write_kernel<float><<<T_, threads, smem, stream>>>(
+            (const float*)qkv, qkv_stride, (float*)q_out, (float*)kv_pool, wq, wk, eps, inv_freq,
+            positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
+    else if (dtype == TK_BF16)
+        qk_norm_rope_write_kernel<__nv_bfloat16><<<T_, threads, smem, stream>>>(
+            (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_pool, wq,
+            wk, eps, inv_freq, positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
+    else
+        TK_CHECK_ARG(false, "qk_norm_rope_write: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("qk_norm_rope_write");
+    return 0;
+}

@@ -1,0 +1,249 @@
+"""The kernels as functions over torch tensors on a CUDA device.
+
+torch is the allocator and the stream owner here, nothing more: every function checks its
+tensors, picks the entry point for the storage type (float32 or bfloat16) and launches on the
+current stream. Tensors on the CPU are refused: there is no CPU implementation on the product
+path (the plain implementation under ``tests/`` is the oracle, not a fallback).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokenomos_b200.ops import _lib
+from tokenomos_b200.ops._lib import BF16, F32, KernelError
+
+__all__ = [
+    "KernelError", "available", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
+    "qk_norm_rope_write", "attention", "attention_rows", "conv_gated", "conv_min_tile",
+    "gemm", "sample",
+]
+
+
+def available() -> None:
+    """Raise unless the library loads and the current device can run it."""
+    _lib.call("tk_check_device")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"storage type {t.dtype} is not built (float32 and bfloat16 are)")
+
+
+def _cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("tokenomos_b200 kernels run on CUDA tensors only; got a "
+                              f"{t.device} tensor (there is no CPU path)")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+def _f32vec(t: torch.Tensor | None, name: str, n: int) -> torch.Tensor | None:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+        raise KernelError(f"{name} must be a contiguous float32 vector of {n} elements, got "
+                          f"{t.dtype} {tuple(t.shape)}")
+    return t
+
+
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None):
+    """``out[r] = table[ids[r]]``: the embedding lookup and the row selection before the head."""
+    _cuda(table, ids, out)
+    rows, width = ids.numel(), table.shape[1]
+    if not table.is_contiguous():
+        raise KernelError("gather_rows: the table must be contiguous")
+    if out is None:
+        out = torch.empty(rows, width, dtype=table.dtype, device=table.device)
+    _lib.call("tk_gather_rows", _ptr(table), _ptr(_i32(ids, "ids")), _ptr(out), rows, width,
+              table.shape[0], _dtype_code(table), _stream())
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor | None,
+                eps: float, pre: tuple[torch.Tensor, float] | None = None):
+    """``stream = residual + [pre-norm](x)``; ``y = rmsnorm(stream) * weight``.
+
+    Returns ``(y, stream)``; ``stream`` is ``x`` itself when nothing was added, ``y`` is None
+    without ``weight``. ``x`` may be a row-strided view; the other tensors are contiguous."""
+    _cuda(x, residual, weight)
+    rows, width = x.shape
+    if x.stride(1) != 1:
+        raise KernelError("add_rmsnorm: rows of x must be contiguous")
+    w = _f32vec(weight, "norm weight", width)
+    pre_w = _f32vec(pre[0], "pre-norm weight", width) if pre is not None else None
+    y = torch.empty(rows, width, dtype=x.dtype, device=x.device) if w is not None else None
+    writes = residual is not None or pre is not None
+    stream = torch.empty(rows, width, dtype=x.dtype, device=x.device) if writes else None
+    if residual is not None and (not residual.is_contiguous() or residual.shape != x.shape
+                                 or residual.dtype != x.dtype):
+        raise KernelError("add_rmsnorm: residual must match x and be contiguous")
+    _lib.call("tk_add_rmsnorm", _ptr(x), x.stride(0), _ptr(residual), _ptr(pre_w),
+              float(pre[1]) if pre is not None else 0.0, _ptr(w), float(eps), _ptr(y),
+              _ptr(stream), rows, width, _dtype_code(x), _stream())
+    if stream is None:
+        stream = x if x.is_contiguous() else x.contiguous()
+    return y, stream
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """``silu(gu[:, :I]) * gu[:, I:]`` for ``gu`` of width ``2 I``."""
+    _cuda(gu)
+    if not gu.is_contiguous() or gu.shape[1] % 2:
+        raise KernelError("swiglu: input must be contiguous with an even width")
+    rows, inter = gu.shape[0], gu.shape[1] // 2
+    out = torch.empty(rows, inter, dtype=gu.dtype, device=gu.device)
+    _lib.call("tk_swiglu", _ptr(gu), _ptr(out), rows, inter, _dtype_code(gu), _stream())
+    return out
+
+
+def head_gate(x: torch.Tensor, g: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
+    """In place: ``x[t, h, :] *= sigmoid(g[t, h])``."""
+    _cuda(x, g)
+    if not (x.is_contiguous() and g.is_contiguous() and g.dtype == x.dtype):
+        raise KernelError("head_gate: contiguous tensors of one storage type")
+    rows = x.numel() // (heads * head_dim)
+    if g.numel() != rows * heads:
+        raise KernelError("head_gate: one gate per (token, head)")
+    _lib.call("tk_head_gate", _ptr(x), _ptr(g), rows, heads, head_dim, _dtype_code(x), _stream())
+    return x
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, kv_pool: torch.Tensor | None,
+                       wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float,
+                       inv_freq: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor,
+                       block_table: torch.Tensor | None, heads: int, kv_heads: int,
+                       head_dim: int, page: int) -> torch.Tensor:
+    """Norm + rotate the q and k heads of ``qkv`` [T, (H + 2 Hkv) D]; returns q [T, H, D] and
+    writes k, v into ``kv_pool`` [pages, 2, Hkv, P, D] at each token's position. ``kv_heads`` 0:
+    queries only (the layer reads another layer's cache)."""
+    _cuda(qkv, kv_pool, wq, wk, inv_freq, positions, tok_seq, block_table)
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qk_norm_rope_write: qkv of width {qkv.shape[1]} for {heads}+2*{kv_heads} "
+                          f"heads of {head_dim}")
+    rot = 2 * inv_freq.numel()
+    _f32vec(inv_freq, "inv_freq", rot // 2)
+    q = torch.empty(T, heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    if kv_heads:
+        if kv_pool is None or block_table is None:
+            raise KernelError("qk_norm_rope_write: keys need a cache and a block table")
+        if kv_pool.dtype != qkv.dtype or not kv_pool.is_contiguous() or tuple(kv_pool.shape[1:]) != (
+                2, kv_heads, page, head_dim):
+            raise KernelError(f"qk_norm_rope_write: cache {tuple(kv_pool.shape)} {kv_pool.dtype} does "
+                              f"not match [pages, 2, {kv_heads}, {page}, {head_dim}] {qkv.dtype}")
+        _i32(block_table, "block_table")
+    _lib.call("tk_qk_norm_rope_write", _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(kv_pool),
+              _ptr(_f32vec(wq, "q_norm weight", head_dim)), _ptr(_f32vec(wk, "k_norm weight", head_dim)),
+              float(eps), _ptr(inv_freq), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(block_table),
+              block_table.stride(0) if block_table is not None else 0, T, heads, kv_heads,
+              head_dim, rot, page, _dtype_code(qkv), _stream())
+    return q
+
+
+def attention_rows() -> int:
+    """Rows (token x query head of one group) a tile of the generic attention kernel holds."""
+    return _lib.call("tk_attn_generic_rows")
+
+
+def attention(q: torch.Tensor, kv_pool: torch.Tensor, positions: torch.Tensor,
+              tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor,
+              tile_ntok: torch.Tensor, tokens_per_tile: int, window: int | None,
+              scale: float) -> torch.Tensor:
+    """Causal (optionally windowed) attention of ``q`` [T, H, D] over the paged cache
+    ``kv_pool`` [pages, 2, Hkv, P, D], which already holds this step's keys. Tiles name runs of
+    at most ``tokens_per_tile`` tokens of one sequence."""
+    _cuda(q, kv_pool, positions, tok_seq, block_table, tile_tok0, tile_ntok)
+    T, H, D = q.shape
+    _, two, Hkv, P, D2 = kv_pool.shape
+    if two != 2 or D2 != D or kv_pool.dtype != q.dtype or not (q.is_contiguous() and kv_pool.is_contiguous()):
+        raise KernelError("attention: q / cache layouts do not match")
+    out = torch.empty_like(q)
+    _lib.call("tk_attn_generic", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
+              block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
+              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), tokens_per_tile, H, Hkv, D, P,
+              int(window or 0), float(scale), _dtype_code(q), _stream())
+    return out
+
+
+def conv_min_tile(width: int) -> int:
+    return _lib.call("tk_conv_min_tile", width)
+
+
+def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+               state: torch.Tensor, cu: torch.Tensor, seq_ctx: torch.Tensor,
+               seq_slot: torch.Tensor, tile_seq: torch.Tensor, tile_off: torch.Tensor,
+               tile_n: torch.Tensor) -> torch.Tensor:
+    """Gated short conv of ``bcx`` [T, 3d] = (B | C | X): returns ``C * conv(B * X)`` [T, d] and
+    replaces each sequence's row of ``state`` [slots, W-1, d]. ``weight`` [d, W] float32."""
+    _cuda(bcx, weight, bias, state, cu, seq_ctx, seq_slot, tile_seq, tile_off, tile_n)
+    T, three_d = bcx.shape
+    d = three_d // 3
+    W = weight.shape[1]
+    if bcx.stride(1) != 1 or three_d != 3 * d:
+        raise KernelError("conv_gated: bcx must be [T, 3d] with contiguous rows")
+    if weight.dtype != torch.float32 or not weight.is_contiguous() or weight.shape[0] != d:
+        raise KernelError("conv_gated: weight must be contiguous float32 [d, W]")
+    if state.dtype != bcx.dtype or not state.is_contiguous() or tuple(state.shape[1:]) != (W - 1, d):
+        raise KernelError(f"conv_gated: state {tuple(state.shape)} does not match [slots, {W - 1}, {d}]")
+    out = torch.empty(T, d, dtype=bcx.dtype, device=bcx.device)
+    _lib.call("tk_conv_gated", _ptr(bcx), bcx.stride(0), d, _ptr(weight), _ptr(_f32vec(bias, "conv bias", d)),
+              _ptr(state), _ptr(out), _ptr(_i32(cu, "cu")), _ptr(_i32(seq_ctx, "seq_ctx")),
+              _ptr(_i32(seq_slot, "seq_slot")), _ptr(_i32(tile_seq, "tile_seq")),
+              _ptr(_i32(tile_off, "tile_off")), _ptr(_i32(tile_n, "tile_n")), tile_seq.numel(), W,
+              _dtype_code(bcx), _stream())
+    return out
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` on the CUDA cores with 32-bit accumulation, any shape.
+    ``x`` [M, K] (row stride free), ``w`` [N, K]; ``bias`` float32 [N]."""
+    _cuda(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or x.dtype != w.dtype or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm: x {tuple(x.shape)} {x.dtype} against w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    _lib.call("tk_gemm_simt", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
+              _ptr(out), N, M, N, K, _dtype_code(x), _dtype_code(out), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
+           top_k: torch.Tensor, min_p: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of ``logits`` [rows, V] float32; the parameters are per-row arrays."""
+    _cuda(logits, temperature, top_p, top_k, min_p, seed, step, out)
+    rows, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with contiguous rows")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_p", top_p, torch.float32),
+                        ("min_p", min_p, torch.float32), ("top_k", top_k, torch.int32),
+                        ("seed", seed, torch.int32), ("step", step, torch.int32)):
+        if t.dtype != dt or t.numel() < rows or not t.is_contiguous():
+            raise KernelError(f"sample: {name} must be a contiguous {dt} array of {rows}")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _lib.call("tk_sample", _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_p),
+              _ptr(top_k), _ptr(min_p), _ptr(seed), _ptr(step), _ptr(out), _stream())
+    return out

@@ -1,0 +1,83 @@
+"""Grouped-query attention mixer over the paged cache.
+
+``qkv = x @ [Wq; Wk; Wv].T``; per head of q and k an RMSNorm over the head (optional) and the
+rotary encoding; the new keys and values go into the cache; every query attends over the cache
+(its own step's keys included) causally, within ``window`` positions when the layer has one;
+optional per-head sigmoid gate from the same input; output projection
+(Tokenomos models/blocks/attention.py:225-259). ``kv_source``: the layer has queries only and
+reads the cache of another call of the layer list.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokenomos_b200 import ops
+from tokenomos_b200.parts.contract import PagedKV, SharedState, StepContext, WindowKV
+from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.registry import Runtime, builder_of, register
+
+
+class Attention:
+    def __init__(self, qkv: Linear, o: Linear, heads: int, kv_heads: int, head_dim: int, rope,
+                 eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                 window: int | None = None, scale: float | None = None,
+                 gate: Linear | None = None, kv_source: int | None = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
+        self.qkv, self.o, self.gate = qkv, o, gate
+        self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
+        self.rope = rope
+        self.eps = float(eps)
+        self.q_norm = q_norm.float().contiguous() if q_norm is not None else None
+        self.k_norm = k_norm.float().contiguous() if k_norm is not None else None
+        self.window = window
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.kv_source = kv_source
+        own_kv = 0 if kv_source is not None else kv_heads
+        if qkv.out_features != (heads + 2 * own_kv) * head_dim:
+            raise ValueError("attention: the fused projection does not match the head counts")
+        if rope.dim != head_dim:
+            # the kernel rotates the first `dim` dims and passes the rest through
+            if rope.dim > head_dim:
+                raise ValueError("attention: rotary width above the head size")
+
+    def state_specs(self) -> dict:
+        if self.kv_source is not None:
+            return {"kv": SharedState(self.kv_source, "kv")}
+        if self.window is None:
+            return {"kv": PagedKV(self.kv_heads, self.head_dim)}
+        return {"kv": WindowKV(self.kv_heads, self.head_dim, self.window)}
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
+        T = x.shape[0]
+        qkv = self.qkv(x)
+        pool = ctx.states[(call, "kv")]
+        table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
+        own_kv = 0 if self.kv_source is not None else self.kv_heads
+        q = ops.qk_norm_rope_write(
+            qkv, pool if own_kv else None, self.q_norm, self.k_norm if own_kv else None,
+            self.eps, self.rope.tables(ctx), ctx.positions, ctx.tok_seq,
+            table if own_kv else None, self.heads, own_kv, self.head_dim, ctx.page_size)
+        rows = ops.attention_rows()
+        group = self.heads // self.kv_heads
+        per_tile = max(1, rows // group)
+        _, tok0, _, ntok = ctx.tiles(per_tile)
+        out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
+                            self.window, self.scale)
+        if self.gate is not None:
+            ops.head_gate(out, self.gate(x).contiguous(), self.heads, self.head_dim)
+        return self.o(out.view(T, self.heads * self.head_dim))
+
+
+@register("mixer", "attention")
+def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
+    rope_spec = params["position"]
+    rope = builder_of("position", rope_spec["kind"])(rope_spec["params"], {}, rt)
+    source = params.get("kv_source")
+    mats = [tensors["q"]] if source is not None else [tensors["q"], tensors["k"], tensors["v"]]
+    gate = Linear(tensors["gate"]) if "gate" in tensors else None
+    return Attention(
+        Linear.fused(mats), Linear(tensors["o"]), params["heads"], params["kv_heads"],
+        params["head_dim"], rope, params["eps"], tensors.get("q_norm"), tensors.get("k_norm"),
+        params.get("window"), params.get("scale"), gate, source)

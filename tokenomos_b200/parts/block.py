@@ -1,0 +1,92 @@
+"""Block arrangements and the stack that runs the layer list.
+
+``PreNormBlock``: ``x = N1(r); r += mixer(x); x = N2(r); r += ffn(x)`` with the residual stream
+carried as ``(h, residual)`` so that each add happens inside the next norm's kernel; with
+sandwich norms the mixer's and the feed-forward's outputs pass a post-norm before the add
+(Tokenomos models/blocks/decoder.py:104-125, 173-180).
+
+``Stack``: embedding, the layer list (data: entries may name a block twice, or read another
+entry's state), final norm and head applied only to the rows whose logits are wanted.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokenomos_b200 import ops
+from tokenomos_b200.parts.contract import SharedState, StateKey, StateSpec, StepContext
+from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.registry import register
+from tokenomos_b200.parts.spec import LayerCall
+
+
+class PreNormBlock:
+    def __init__(self, mixer, ffn, pre_mixer, pre_ffn, post_mixer=None, post_ffn=None):
+        self.mixer, self.ffn = mixer, ffn
+        self.pre_mixer, self.pre_ffn = pre_mixer, pre_ffn
+        self.post_mixer, self.post_ffn = post_mixer, post_ffn
+
+    def forward(self, h, residual, pending, ctx: StepContext, call: int):
+        """``pending``: the previous block's post-norm still to apply to ``h`` before it joins
+        the stream. Returns this block's output, the stream and its own pending post-norm."""
+        x, residual = self.pre_mixer.add_norm(h, residual, pending)
+        m = self.mixer.forward(x, ctx, call)
+        x, residual = self.pre_ffn.add_norm(m, residual, self.post_mixer)
+        return self.ffn.forward(x), residual, self.post_ffn
+
+
+@register("block", "prenorm")
+def build_prenorm(parts: dict) -> PreNormBlock:
+    return PreNormBlock(parts["mixer"], parts["ffn"], parts["pre_mixer_norm"],
+                        parts["pre_ffn_norm"], parts.get("post_mixer_norm"),
+                        parts.get("post_ffn_norm"))
+
+
+class Stack:
+    def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
+                 head: Linear | None):
+        self.embedding = embedding
+        self.blocks = blocks
+        self.order = list(order)
+        self.final_norm = final_norm
+        self.head = head if head is not None else Linear(embedding)
+        self.tied = head is None
+        self.vocab, self.width = embedding.shape
+        self.dtype = embedding.dtype
+        for i, call in enumerate(self.order):
+            if not 0 <= call.block < len(blocks):
+                raise ValueError(f"layer list entry {i} names block {call.block} of {len(blocks)}")
+            if call.state_from is not None and not 0 <= call.state_from < i:
+                raise ValueError(f"layer list entry {i} reads the state of entry {call.state_from}, "
+                                 "which must come earlier in the list")
+
+    def state_specs(self) -> dict[StateKey, StateSpec]:
+        """Per entry of the layer list, the memory its mixer asks for. An entry that reads
+        another's state contributes ``SharedState`` specs pointing at it."""
+        out: dict[StateKey, StateSpec] = {}
+        for i, call in enumerate(self.order):
+            for name, spec in self.blocks[call.block].mixer.state_specs().items():
+                if call.state_from is not None:
+                    spec = SharedState(call.state_from, name)
+                out[(i, name)] = spec
+        return out
+
+    def embed(self, ids: torch.Tensor) -> torch.Tensor:
+        return ops.gather_rows(self.embedding, ids)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext):
+        """Runs the layer list; returns ``(h, residual, pending)`` of the last block: the final
+        norm takes the last add with it, on the wanted rows only (``logits``)."""
+        residual, pending = None, None
+        for i, call in enumerate(self.order):
+            h, residual, pending = self.blocks[call.block].forward(h, residual, pending, ctx, i)
+        return h, residual, pending
+
+    def logits(self, out, rows: torch.Tensor) -> torch.Tensor:
+        """Float32 logits [len(rows), vocab] at token rows ``rows`` (int32) of the step."""
+        h, residual, pending = out
+        h = ops.gather_rows(h, rows)
+        if residual is not None:
+            residual = ops.gather_rows(residual, rows)
+        y, _ = self.final_norm.add_norm(h, residual, pending)
+        return self.head(y, out_dtype=torch.float32)

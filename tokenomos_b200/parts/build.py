@@ -1,0 +1,43 @@
+"""``ModelSpec`` + tensors -> ``Stack``: every part is built by the registry entry of its kind."""
+
+from __future__ import annotations
+
+from tokenomos_b200.parts.block import Stack
+from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.registry import Runtime, builder_of
+from tokenomos_b200.parts.spec import BlockSpec, ModelSpec, PartSpec
+
+# which registry family each slot of a block belongs to
+SLOT_FAMILY = {
+    "mixer": "mixer",
+    "ffn": "feed_forward",
+    "pre_mixer_norm": "norm",
+    "pre_ffn_norm": "norm",
+    "post_mixer_norm": "norm",
+    "post_ffn_norm": "norm",
+}
+
+
+def _part(family: str, spec: PartSpec, tensors: dict, rt: Runtime):
+    mine = {role: tensors[d.name] for role, d in spec.tensors.items() if d.name in tensors}
+    return builder_of(family, spec.kind)(spec.params, mine, rt)
+
+
+def _block(spec: BlockSpec, tensors: dict, rt: Runtime):
+    parts = {}
+    for slot, part in spec.parts.items():
+        if part is None:
+            continue
+        family = SLOT_FAMILY.get(slot)
+        if family is None:
+            raise ValueError(f"block slot {slot!r} has no part family; slots: {sorted(SLOT_FAMILY)}")
+        parts[slot] = _part(family, part, tensors, rt)
+    return builder_of("block", spec.kind)(parts)
+
+
+def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
+    """``tensors``: name -> tensor on ``rt.device``, kept as the weight loader keeps them."""
+    blocks = [_block(b, tensors, rt) for b in spec.blocks]
+    final_norm = _part("norm", spec.final_norm, tensors, rt)
+    head = Linear(tensors[spec.head.name]) if spec.head is not None else None
+    return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head)
