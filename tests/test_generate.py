@@ -1,0 +1,135 @@
+"""Generation through the entry points: greedy replies equal the plain implementation's,
+seeded sampling repeats and is the same alone or in a batch, stop tokens end a reply, running
+out of pages changes nothing but the speed, the command line prints what the API returns."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_lfm3
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def prompts_for(name, lengths, seed=0):
+    vocab = TINY[name]["config"]["vocab_size"]
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def teacher_forced_ok(config, w, prompt, reply, margin):
+    """Never compare free-running streams across implementations: each generated token must be
+    the plain implementation's argmax given the same history, or within ``margin`` of it."""
+    logits = plain_lfm3.forward_logits(config, w, prompt + reply)
+    for i, tok in enumerate(reply):
+        row = logits[len(prompt) + i - 1]
+        if int(row.argmax()) != tok:
+            assert row.max().item() - row[tok].item() <= margin, (i, tok, int(row.argmax()))
+
+
+@pytest.mark.parametrize("work, margin", [("fp32", 1e-4), ("bf16", 0.12)])
+@pytest.mark.parametrize("name, lengths, steps", [("A", [5, 17, 33], 16), ("B", [1, 9, 40, 64], 24)])
+def test_greedy_generation_through_llm(name, lengths, steps, work, margin, model_folders):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders[name][torch.bfloat16]
+    config, w = plain_lfm3.read_folder(folder)
+    prompts = prompts_for(name, lengths)
+    with LLM(str(folder), work=work, page=TINY[name]["page"], max_len=256, slots=4, pages=40,
+             prefill_budget=48) as llm:
+        outs = llm.generate(prompts, SamplingParams(max_tokens=steps))
+    for prompt, out in zip(prompts, outs):
+        assert out.prompt_tokens == len(prompt) and out.finish == "length"
+        assert len(out.token_ids) == steps
+        teacher_forced_ok(config, w, prompt, out.token_ids, margin)
+        if work == "fp32":
+            assert out.token_ids == plain_lfm3.generate_greedy(config, w, prompt, steps)
+
+
+def test_seeded_sampling_repeats_alone_and_in_batches(model_folders):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders["B"][torch.bfloat16]
+    prompts = prompts_for("B", [1, 9, 40, 64], seed=1)
+    p = SamplingParams(max_tokens=24, temperature=0.8, seed=1234)
+    with LLM(str(folder), work="fp32", page=8, max_len=128, slots=4, pages=60) as llm:
+        batch = llm.generate(prompts, p)
+        again = llm.generate(prompts, p)
+        alone = [llm.generate([x], p)[0] for x in prompts]
+        other = llm.generate(prompts, SamplingParams(max_tokens=24, temperature=0.8, seed=99))
+    assert [o.token_ids for o in batch] == [o.token_ids for o in again]
+    assert [o.token_ids for o in batch] == [o.token_ids for o in alone]
+    assert [o.token_ids for o in batch] != [o.token_ids for o in other]
+    greedy_like = sum(o.token_ids == batch[0].token_ids for o in batch)
+    assert greedy_like == 1
+
+
+def test_stop_token_and_refusals(model_folders):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders["A"][torch.bfloat16]
+    prompt = prompts_for("A", [12])[0]
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=2, pages=6) as llm:
+        free = llm.generate([prompt], SamplingParams(max_tokens=12))[0]
+        stop = free.token_ids[5]
+        cut = llm.generate([prompt], SamplingParams(max_tokens=12, stop_token_ids=(stop,)))[0]
+        first = free.token_ids.index(stop)
+        assert cut.finish == "stop" and cut.token_ids == free.token_ids[:first + 1]
+        with pytest.raises(ValueError, match="longest sequence"):
+            llm.generate([prompt], SamplingParams(max_tokens=60))
+        with pytest.raises(ValueError, match="token id"):
+            llm.generate([[10 ** 6]], SamplingParams(max_tokens=2))
+        with pytest.raises(ValueError, match="tokenizer.json"):
+            llm.generate(["text"], SamplingParams(max_tokens=2))
+        # the engine still serves after refusals
+        assert llm.generate([prompt], SamplingParams(max_tokens=12))[0].token_ids == free.token_ids
+
+
+def test_pages_run_out_same_tokens_as_a_roomy_pool(model_folders):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders["A"][torch.bfloat16]
+    prompts = prompts_for("A", [20, 31, 9, 27, 14, 22], seed=3)
+    p = SamplingParams(max_tokens=30, temperature=0.7, seed=5)
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=6, pages=40) as llm:
+        roomy = llm.generate(prompts, p)
+        assert llm.engine.stats.preemptions == 0
+    # 8 usable pages of 16 tokens: the six requests cannot all stay resident
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=6, pages=9) as llm:
+        tight = llm.generate(prompts, p)
+        assert llm.engine.stats.preemptions > 0
+        llm.engine.cache.check()
+        assert llm.engine.cache.free_pages() == 8
+    assert [o.token_ids for o in tight] == [o.token_ids for o in roomy]
+
+
+@pytest.mark.filterwarnings("ignore::pytest.PytestUnhandledThreadExceptionWarning")
+def test_engine_thread_failure_surfaces(model_folders):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders["A"][torch.bfloat16]
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=2, pages=6) as llm:
+        def boom(*a, **k):
+            raise RuntimeError("injected")
+        llm.engine.step = boom
+        with pytest.raises(RuntimeError, match="engine thread failed"):
+            llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2))
+        assert isinstance(llm.failure, RuntimeError)
+
+
+def test_command_line(model_folders, tmp_path):
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders["A"][torch.bfloat16]
+    cmd = [sys.executable, "-m", "tokenomos_b200.generate", "--model", str(folder),
+           "--prompt-ids", "1,2,3,4", "--prompt-ids", "9,8", "--max-tokens", "6",
+           "--arch-kw", '{"work": "fp32"}', "--engine-kw", '{"page": 16, "max_len": 64, "slots": 2, "pages": 8}']
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=2, pages=8) as llm:
+        want = llm.generate([[1, 2, 3, 4], [9, 8]], SamplingParams(max_tokens=6))
+    assert [ln["token_ids"] for ln in lines] == [o.token_ids for o in want]
+    assert [ln["prompt_tokens"] for ln in lines] == [4, 2]

@@ -1,0 +1,443 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same op, at sizes other than
+the engine's tiny models: widths and vocabularies that are no power of two, head sizes in steps
+of 16 (and 24), any number of heads and groups, several page sizes. Where random inputs would
+hide a fault the inputs are made so that it shows: a far key whose score dominates, keys at the
+window's edge, unread cache rows poisoned with NaN."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+def close(got, want, dtype, what="", scale=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    assert torch.isfinite(got).all(), what
+    s = scale if scale is not None else max(want.abs().max().item(), 1e-6)
+    err = (got - want).abs().max().item()
+    assert err <= tol(dtype) * s, f"{what}: error {err:.3e} allowed {tol(dtype) * s:.3e}"
+
+
+def dev(t, dtype=None):
+    return t.to("cuda", dtype) if dtype is not None else t.to("cuda")
+
+
+def i32(values):
+    return torch.tensor(values, dtype=torch.int32, device="cuda")
+
+
+# ---- gather / norm / swiglu / gate -------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [100, 128, 2050])
+def test_gather_rows(dtype, width):
+    from tokenomos_b200 import ops
+    table = torch.randn(37, width).to(dtype)
+    ids = [36, 0, 5, 5, 17]
+    out = ops.gather_rows(dev(table), i32(ids))
+    assert torch.equal(out.cpu(), table[ids])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [100, 2048, 5000])
+@pytest.mark.parametrize("residual, pre", [(False, False), (True, False), (True, True)])
+def test_add_rmsnorm(dtype, width, residual, pre):
+    from tokenomos_b200 import ops
+    rows, eps = 7, 3e-6
+    x = (torch.randn(rows, width) * 3).to(dtype)
+    r = torch.randn(rows, width).to(dtype) if residual else None
+    w = 1 + 0.2 * torch.randn(width)
+    wp = 1 + 0.2 * torch.randn(width)
+
+    def rms(v, weight, e):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + e) * weight.double()
+
+    xd = x.double()
+    if pre:
+        xd = rms(xd, wp, 1e-5)
+    stream = xd + r.double() if residual else xd
+    want = rms(stream, w, eps)
+    y, s = ops.add_rmsnorm(dev(x), dev(r) if residual else None, dev(w), eps,
+                           (dev(wp), 1e-5) if pre else None)
+    close(y, want, dtype, "normed")
+    close(s, stream, dtype, "stream")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_rmsnorm_strided_input(dtype):
+    from tokenomos_b200 import ops
+    big = torch.randn(5, 300).to(dtype)
+    x = big[:, 100:200]
+    w = torch.ones(100)
+    y, _ = ops.add_rmsnorm(dev(big)[:, 100:200], None, dev(w), 1e-5)
+    xd = x.double()
+    close(y, xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + 1e-5), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_head_gate(dtype):
+    from tokenomos_b200 import ops
+    gu = (torch.randn(9, 2 * 77) * 2).to(dtype)
+    out = ops.swiglu(dev(gu))
+    g, u = gu.double()[:, :77], gu.double()[:, 77:]
+    close(out, torch.nn.functional.silu(g) * u, dtype, "swiglu")
+    x = torch.randn(6, 5, 24).to(dtype)
+    gate = torch.randn(6, 5).to(dtype)
+    got = ops.head_gate(dev(x).clone(), dev(gate), 5, 24)
+    close(got, x.double() * torch.sigmoid(gate.double())[:, :, None], dtype, "head gate")
+
+
+# ---- matrix product ----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m, n, k", [(1, 33, 17), (5, 1000, 96), (70, 130, 2048), (64, 64, 16), (129, 65, 200)])
+@pytest.mark.parametrize("in_dtype, out_dtype", [(torch.float32, torch.float32),
+                                                 (torch.bfloat16, torch.bfloat16),
+                                                 (torch.bfloat16, torch.float32)])
+def test_gemm_simt(m, n, k, in_dtype, out_dtype):
+    from tokenomos_b200 import ops
+    x = torch.randn(m, k).to(in_dtype)
+    w = torch.randn(n, k).to(in_dtype)
+    b = torch.randn(n)
+    want = x.double() @ w.double().T + b.double()
+    got = ops.gemm(dev(x), dev(w), dev(b), out_dtype)
+    assert got.dtype == out_dtype
+    close(got, want, out_dtype, f"gemm {m}x{n}x{k}")
+    # a row-strided input (a slice of a wider activation)
+    wide = torch.randn(m, k + 40).to(in_dtype)
+    got = ops.gemm(dev(wide)[:, 8:8 + k], dev(w), None, out_dtype)
+    close(got, wide[:, 8:8 + k].double() @ w.double().T, out_dtype, "strided gemm")
+
+
+def test_gemm_float32_is_not_tf32():
+    """A product whose exact value needs more than TF32's 10 mantissa bits."""
+    from tokenomos_b200 import ops
+    x = torch.full((4, 64), 1.0 + 2.0 ** -12)
+    w = torch.full((8, 64), 1.0 + 2.0 ** -12)
+    got = ops.gemm(dev(x), dev(w)).double().cpu()
+    want = x.double() @ w.double().T
+    assert (got - want).abs().max().item() < 1e-5
+    assert (want - 64.0).abs().min().item() > 1e-2   # TF32 inputs would give exactly 64
+
+
+# ---- q/k norm + rotary + cache write -----------------------------------------------------------
+
+def rope_ref(x, pos, inv_freq, rot):
+    """x [T, H, D] float64; rotate-half on the first ``rot`` dims with float32 angles."""
+    f = pos.to(torch.float32)[:, None] * inv_freq[None, :]
+    emb = torch.cat((f, f), -1).double()
+    cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+    xr, rest = x[..., :rot], x[..., rot:]
+    half = rot // 2
+    rotated = torch.cat((-xr[..., half:], xr[..., :half]), -1)
+    return torch.cat((xr * cos + rotated * sin, rest), -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, Hkv, D, angles, P", [(4, 2, 16, 8, 16), (3, 1, 24, 12, 8), (8, 8, 64, 16, 4),
+                                                  (6, 2, 128, 64, 32), (2, 1, 48, 24, 5)])
+def test_qk_norm_rope_write(dtype, H, Hkv, D, angles, P):
+    from tokenomos_b200 import ops
+    T, eps, theta = 11, 1e-6, 10000.0
+    pos = torch.tensor([0, 1, 2, 3, 4000, 4001, 7, 8, 9, 10, 11])
+    seq = torch.tensor([0, 0, 0, 0, 1, 1, 2, 2, 2, 2, 2])
+    blocks = 4002 // P + 1
+    table = torch.randperm(3 * blocks)[: 3 * blocks].view(3, blocks).to(torch.int32) + 1
+    pages = 3 * blocks + 1
+    qkv = torch.randn(T, (H + 2 * Hkv) * D).to(dtype)
+    wq, wk = 1 + 0.3 * torch.randn(D), 1 + 0.3 * torch.randn(D)
+    inv = 1.0 / (theta ** (torch.arange(0, 2 * angles, 2, dtype=torch.float32) / D))
+    inv = torch.cat((inv, torch.zeros(D // 2 - angles)))
+    pool = torch.full((pages, 2, Hkv, P, D), float("nan"), dtype=dtype, device="cuda")
+    q = ops.qk_norm_rope_write(dev(qkv), pool, dev(wq), dev(wk), eps, dev(inv), i32(pos.tolist()),
+                               i32(seq.tolist()), dev(table), H, Hkv, D, P)
+    x = qkv.double().view(T, H + 2 * Hkv, D)
+
+    def norm(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.double()
+
+    want_q = rope_ref(norm(x[:, :H], wq), pos, inv, D)
+    want_k = rope_ref(norm(x[:, H:H + Hkv], wk), pos, inv, D)
+    want_v = x[:, H + Hkv:]
+    close(q, want_q, dtype, "q")
+    pool = pool.cpu()
+    written = torch.zeros(pages, P, dtype=torch.bool)
+    for t in range(T):
+        page, row = int(table[seq[t], pos[t] // P]), int(pos[t] % P)
+        close(pool[page, 0, :, row], want_k[t], dtype, f"k of token {t}", scale=want_k.abs().max().item())
+        assert torch.equal(pool[page, 1, :, row].double(), want_v[t]), f"v of token {t}"
+        written[page, row] = True
+    # nothing else was touched
+    assert torch.isnan(pool[:, :, :, :, 0].double()[~written[:, None, None, :].expand(-1, 2, Hkv, -1)]).all()
+
+
+# ---- paged attention ---------------------------------------------------------------------------
+
+def attention_case(dtype, H, Hkv, D, P, seqs, window=None, poison=True, boost=None):
+    """``seqs``: list of (ctx, n). Builds a shuffled paged cache holding every sequence's keys
+    for positions [0, ctx + n), runs the kernel for the last n of each, returns (got, want)."""
+    from tokenomos_b200 import ops
+    G = H // Hkv
+    total = [c + n for c, n in seqs]
+    blocks = [-(-t // P) for t in total]
+    width = max(blocks)
+    pages = sum(blocks) + 1
+    perm = (torch.randperm(pages - 1) + 1).tolist()
+    fill = float("nan") if poison else 0.0
+    pool = torch.full((pages, 2, Hkv, P, D), fill, dtype=torch.float64)
+    table = torch.zeros(len(seqs), width, dtype=torch.int32)
+    ks, vs, qs = [], [], []
+    for s, (c, n) in enumerate(seqs):
+        k = torch.randn(total[s], Hkv, D).to(dtype).double()
+        v = torch.randn(total[s], Hkv, D).to(dtype).double()
+        q = torch.randn(n, H, D).to(dtype).double()
+        if boost is not None:
+            boost(s, q, k, v)
+        for b in range(blocks[s]):
+            page = perm.pop()
+            table[s, b] = page
+            rows = min(P, total[s] - b * P)
+            pool[page, 0, :, :rows] = k[b * P:b * P + rows].transpose(0, 1)
+            pool[page, 1, :, :rows] = v[b * P:b * P + rows].transpose(0, 1)
+        ks.append(k), vs.append(v), qs.append(q)
+    positions = [p for (c, n) in seqs for p in range(c, c + n)]
+    tok_seq = [s for s, (c, n) in enumerate(seqs) for _ in range(n)]
+    per_tile = max(1, ops.attention_rows() // G)
+    tok0, ntok, start = [], [], 0
+    for c, n in seqs:
+        for o in range(0, n, per_tile):
+            tok0.append(start + o)
+            ntok.append(min(per_tile, n - o))
+        start += n
+    got = ops.attention(dev(torch.cat(qs), dtype), dev(pool, dtype), i32(positions), i32(tok_seq),
+                        dev(table), i32(tok0), i32(ntok), per_tile, window, D ** -0.5)
+    want = []
+    for s, (c, n) in enumerate(seqs):
+        k = ks[s].repeat_interleave(G, 1)
+        v = vs[s].repeat_interleave(G, 1)
+        sc = torch.einsum("ihd,jhd->hij", qs[s], k) * D ** -0.5
+        i = torch.arange(c, c + n)[:, None]
+        j = torch.arange(total[s])[None, :]
+        vis = j <= i
+        if window:
+            vis &= (i - j) < window
+        sc = sc.masked_fill(~vis[None], float("-inf"))
+        want.append(torch.einsum("hij,jhd->ihd", sc.softmax(-1), v))
+    return got, torch.cat(want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, Hkv, D, P", [(4, 2, 16, 16), (4, 1, 24, 8), (6, 2, 32, 4), (8, 2, 64, 64),
+                                          (5, 5, 48, 16), (32, 1, 16, 16), (2, 1, 128, 32),
+                                          (3, 1, 80, 7), (1, 1, 256, 16)])
+def test_attention_mixed_batches(dtype, H, Hkv, D, P):
+    seqs = [(0, 1), (17, 3), (0, 40), (40, 100), (333, 1), (5, 2)]
+    got, want = attention_case(dtype, H, Hkv, D, P, seqs)
+    close(got, want, dtype, f"attention H{H} Hkv{Hkv} D{D} P{P}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 33])
+def test_attention_window(dtype, window):
+    got, want = attention_case(dtype, 6, 2, 32, 8, [(0, 50), (70, 1), (20, 30), (3, 2)], window=window)
+    close(got, want, dtype, f"window {window}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_far_key_and_window_edge(dtype):
+    """One key's score dominates: far back among hundreds (it must be found on its page), just
+    inside the window (it must be seen) and just outside (it must not)."""
+    D, ctx = 32, 700
+
+    def far(s, q, k, v):
+        q[:] = 0.0
+        k[:] = 0.0
+        q[:, :, 0] = 8.0
+        k[13, :, 0] = 8.0          # position 13 of 701: score 64 * D^-0.5 above all others
+
+    got, want = attention_case(dtype, 4, 2, D, 16, [(ctx, 1)], boost=far)
+    close(got, want, dtype, "far key")
+    assert (got.double().cpu() - want).abs().max().item() < 0.05
+
+    for offset, seen in ((9, True), (10, False)):
+        def edge(s, q, k, v, offset=offset):
+            q[:] = 0.0
+            k[:] = 0.0
+            q[:, :, 0] = 8.0
+            k[ctx - offset, :, 0] = 8.0
+            v[ctx - offset] = 5.0
+
+        got, want = attention_case(dtype, 4, 2, D, 16, [(ctx, 1)], window=10, boost=edge)
+        close(got, want, dtype, f"window edge {offset}")
+        assert (got.double().cpu().mean().item() > 2.0) == seen
+
+
+def test_attention_poison_is_a_real_control():
+    """If the kernel read a row it must not, the NaN would surface: reading one position too
+    many (a table that claims one more token) does surface it."""
+    from tokenomos_b200 import ops
+    D, P = 16, 8
+    pool = torch.full((3, 2, 1, P, D), float("nan"), device="cuda")
+    pool[1, :, :, :5] = 1.0
+    q = torch.ones(1, 1, D, device="cuda")
+    table = i32([[1]])
+    ok = ops.attention(q, pool, i32([4]), i32([0]), table, i32([0]), i32([1]), 16, None, 1.0)
+    assert torch.isfinite(ok).all()
+    bad = ops.attention(q, pool, i32([5]), i32([0]), table, i32([0]), i32([1]), 16, None, 1.0)
+    assert torch.isnan(bad).any()
+
+
+# ---- gated short conv --------------------------------------------------------------------------
+
+def conv_ref(bcx, taps, bias, prev):
+    """One whole sequence: bcx [T, 3d] float64, prev [W-1, d] the inputs before it."""
+    T, d = bcx.shape[0], bcx.shape[1] // 3
+    W = taps.shape[1]
+    u = bcx[:, :d] * bcx[:, 2 * d:]
+    padded = torch.cat((prev, u))
+    y = sum(padded[j:j + T] * taps[:, j][None] for j in range(W))
+    if bias is not None:
+        y = y + bias
+    return bcx[:, d:2 * d] * y, padded[-(W - 1):]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("W, d, with_bias", [(2, 100, True), (3, 64, False), (4, 96, True), (7, 300, False)])
+def test_conv_gated_mixed_batch_and_state(dtype, W, d, with_bias):
+    from tokenomos_b200 import ops
+    slots = 6
+    taps = torch.randn(d, W)
+    bias = torch.randn(d) if with_bias else None
+    # (slot, ctx, n): fresh sequences, continued ones, single tokens, one shorter than W - 1
+    seqs = [(3, 0, 1), (1, 12, 70), (5, 0, 33), (2, 4, 1), (4, 9, 2)]
+    state0 = torch.randn(slots, W - 1, d).to(dtype)
+    state = dev(state0).clone()
+    T = sum(n for _, _, n in seqs)
+    bcx = torch.randn(T, 3 * d).to(dtype)
+    cu = [0]
+    for _, _, n in seqs:
+        cu.append(cu[-1] + n)
+    tile = 32
+    tseq, toff, tn = [], [], []
+    for s, (_, _, n) in enumerate(seqs):
+        for o in range(0, n, tile):
+            tseq.append(s), toff.append(o), tn.append(min(tile, n - o))
+    out = ops.conv_gated(dev(bcx), dev(taps), dev(bias) if with_bias else None, state, i32(cu),
+                         i32([c for _, c, _ in seqs]), i32([s for s, _, _ in seqs]),
+                         i32(tseq), i32(toff), i32(tn))
+    new_state = state.cpu()
+    touched = set()
+    for s, (slot, ctx, n) in enumerate(seqs):
+        prev = state0[slot].double().clone()
+        for k in range(W - 1):                      # inputs before position 0 are zero
+            if ctx - (W - 1) + k < 0:
+                prev[k] = 0.0
+        want, want_state = conv_ref(bcx[cu[s]:cu[s + 1]].double(), taps.double(),
+                                    bias.double() if with_bias else None, prev)
+        close(out[cu[s]:cu[s + 1]], want, dtype, f"conv out of sequence {s}")
+        close(new_state[slot], want_state, dtype, f"conv state of sequence {s}",
+              scale=max(want_state.abs().max().item(), 1.0))
+        touched.add(slot)
+    for slot in range(slots):
+        if slot not in touched:
+            assert torch.equal(new_state[slot], state0[slot])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_conv_gated_cut_anywhere_equals_whole(dtype):
+    """A sequence fed in portions (down to one token) through its state row gives what the whole
+    sequence gives: bit for bit, since every output sums the same values in the same order."""
+    from tokenomos_b200 import ops
+    W, d, T = 4, 72, 57
+    taps, bcx = torch.randn(d, W), torch.randn(T, 3 * d).to(dtype)
+
+    def run(cuts):
+        state = torch.full((2, W - 1, d), float("nan"), dtype=dtype, device="cuda")
+        outs = []
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            n = b - a
+            tiles = [(0, o, min(32, n - o)) for o in range(0, n, 32)]
+            outs.append(ops.conv_gated(dev(bcx[a:b]), dev(taps), None, state, i32([0, n]), i32([a]),
+                                       i32([1]), i32([t[0] for t in tiles]), i32([t[1] for t in tiles]),
+                                       i32([t[2] for t in tiles])))
+        return torch.cat(outs)
+
+    whole = run([0, T])
+    assert torch.isfinite(whole).all()
+    for cuts in ([0, 1, 2, 3, 4, 5, T], [0, 2, 33, 34, 36, T], list(range(T + 1))):
+        assert torch.equal(run(cuts), whole), cuts
+
+
+# ---- sampling ----------------------------------------------------------------------------------
+
+def sample_rows(logits, rows):
+    from tokenomos_b200 import ops
+    n = len(rows)
+    f = lambda i: torch.tensor([r[i] for r in rows], dtype=torch.float32, device="cuda")  # noqa: E731
+    k = lambda i: torch.tensor([r[i] for r in rows], dtype=torch.int32, device="cuda")    # noqa: E731
+    assert logits.shape[0] == n
+    return ops.sample(logits, f(0), f(1), k(2), f(3), k(4), k(5)).cpu()
+
+
+def test_sample_greedy_is_the_first_maximum():
+    V = 1000
+    logits = torch.randn(5, V)
+    logits[0, [400, 17, 900]] = 9.0
+    logits[1, V - 1] = 9.0
+    logits[2, 0] = 9.0
+    got = sample_rows(logits.cuda(), [(0.0, 1.0, 0, 0.0, 0, 0)] * 5)
+    assert got.tolist() == [17, V - 1, 0, int(logits[3].argmax()), int(logits[4].argmax())]
+
+
+@pytest.mark.parametrize("params", [(0.8, 1.0, 0, 0.0), (1.3, 1.0, 7, 0.0), (1.0, 0.6, 0, 0.0),
+                                    (1.0, 1.0, 0, 0.15), (0.7, 0.8, 12, 0.02)])
+def test_sample_distribution(params):
+    """Empirical distribution over many seeds against the float64 restricted softmax."""
+    temp, top_p, top_k, min_p = params
+    V, N = 50, 40000
+    g = torch.Generator().manual_seed(3)
+    row = torch.randn(V, generator=g) * 2
+    x = row.double() / temp
+    keep = torch.ones(V, dtype=torch.bool)
+    if min_p > 0:
+        keep &= x >= x.max() + math.log(min_p)
+    if top_k:
+        kth = torch.sort(x[keep], descending=True).values[min(top_k, int(keep.sum())) - 1]
+        keep &= x >= kth
+    if top_p < 1:
+        p = torch.where(keep, (x - x.max()).exp(), torch.zeros_like(x))
+        order = torch.argsort(p, descending=True)
+        csum = torch.cumsum(p[order], 0) / p.sum()
+        cut = int((csum < top_p).sum()) + 1
+        mask = torch.zeros(V, dtype=torch.bool)
+        mask[order[:cut]] = True
+        keep &= mask
+    want = torch.where(keep, (x - x.max()).exp(), torch.zeros_like(x))
+    want /= want.sum()
+    logits = row[None].repeat(N, 1).cuda()
+    got = sample_rows(logits, [(temp, top_p, top_k, min_p, seed, 0) for seed in range(N)])
+    freq = torch.bincount(got, minlength=V).double() / N
+    assert freq[~keep].sum().item() == 0.0, "a token outside the allowed set was drawn"
+    assert 0.5 * (freq - want).abs().sum().item() < 0.02
+
+
+def test_sample_is_batch_invariant_and_step_dependent():
+    V = 777
+    logits = torch.randn(6, V).cuda()
+    rows = [(0.9, 0.95, 40, 0.0, 11 * i, 3) for i in range(6)]
+    together = sample_rows(logits, rows)
+    alone = [sample_rows(logits[i:i + 1], rows[i:i + 1])[0] for i in range(6)]
+    assert together.tolist() == [int(a) for a in alone]
+    shuffled = sample_rows(logits.flip(0), rows[::-1])
+    assert shuffled.tolist() == together.flip(0).tolist()
+    steps = [sample_rows(logits[:1].repeat(64, 1), [(1.5, 1.0, 0, 0.0, 5, s) for s in range(64)])]
+    assert len(set(steps[0].tolist())) > 8

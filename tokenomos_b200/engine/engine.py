@@ -1,0 +1,146 @@
+"""The engine: cache manager + step function + scheduler + sampler behind ``submit`` / ``run``.
+
+Per host iteration: take new requests off the inbox, let the scheduler plan one mixed step
+(decode tokens and prompt portions under the token budget), run it through the step function,
+sample the rows whose share reached the end of their known tokens, read the sampled tokens
+back, and let the scheduler finish and free. Keyword arguments follow the reference's
+``Engine`` where it has them: ``slots``, ``page``, ``max_len``, ``pages``, ``prefill_budget``,
+``graphs`` (Tokenomos core/engine.py:148-184).
+"""
+
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from tokenomos_b200.cache.manager import CacheManager
+from tokenomos_b200.engine.scheduler import Planned, Request, Scheduler
+from tokenomos_b200.engine.step import StepEntry, StepFunction
+from tokenomos_b200.sampling import sampler
+
+
+@dataclass
+class Result:
+    tokens: list[int]
+    finish: str
+
+
+@dataclass
+class Stats:
+    steps: int = 0
+    decode_steps: int = 0          # steps in which every row brought one token
+    prefill_tokens: int = 0
+    generated: int = 0
+    preemptions: int = 0
+    wall_s: float = 0.0
+    # (perf_counter, rows, tokens) at each step's start
+    stamps: list = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, model, slots: int = 64, page: int = 16, max_len: int = 4096,
+                 pages: int | None = None, prefill_budget: int = 2048, graphs: bool = False,
+                 kv_fraction: float = 0.8, device: str = "cuda"):
+        """``slots``: live requests. ``page``: tokens per cache page. ``max_len``: longest
+        sequence (prompt + reply). ``pages``: pages per cache group, the null page included
+        (None: ``kv_fraction`` of the free memory, at most what ``slots`` sequences of
+        ``max_len`` need). ``prefill_budget``: tokens per step. ``graphs``: decode-only steps
+        replay a CUDA graph per batch-size bucket."""
+        self.model = model
+        self.device = torch.device(device)
+        specs = model.state_specs()
+        if pages is None:
+            probe = CacheManager(specs, page, 2, 1, model.dtype, "meta", max_len)
+            per_page = max(1, probe.bytes_per_page())
+            free = torch.cuda.mem_get_info(self.device)[0]
+            pages = int(free * kv_fraction) // per_page
+            pages = max(2, min(pages, slots * -(-max_len // page) + 1))
+        self.cache = CacheManager(specs, page, pages, slots, model.dtype, self.device, max_len)
+        self.step_fn = StepFunction(model, self.cache)
+        self.scheduler = Scheduler(self.cache, prefill_budget, slots)
+        self.graphs = graphs
+        self.inbox: queue.Queue[Request] = queue.Queue()
+        self.stats = Stats()
+
+    # ---- requests in ----
+
+    def submit(self, req: Request) -> None:
+        """Queue ``req`` (any thread). A request the engine can never serve fails here."""
+        vocab = self.model.vocab
+        if req.prompt and (min(req.prompt) < 0 or max(req.prompt) >= vocab):
+            raise ValueError(f"prompt token id outside 0..{vocab - 1}")
+        self.scheduler.check(req)
+        self.inbox.put(req)
+
+    # ---- one iteration ----
+
+    def _take_inbox(self) -> None:
+        while True:
+            try:
+                self.scheduler.add(self.inbox.get_nowait())
+            except queue.Empty:
+                return
+
+    @torch.no_grad()
+    def step(self) -> list[Request]:
+        """Plan, run and commit one step; returns the requests that finished in it."""
+        planned = self.scheduler.plan()
+        if not planned:
+            return []
+        entries, rows = [], []
+        for p in planned:
+            toks = p.req.tokens[p.start:p.start + p.count]
+            entries.append(StepEntry(p.req.rid, toks, [p.count - 1] if p.sample else []))
+            if p.sample:
+                r = p.req
+                rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed, len(r.output)))
+        tokens_in_step = sum(p.count for p in planned)
+        self.stats.stamps.append((time.perf_counter(), len(planned), tokens_in_step))
+        self.stats.steps += 1
+        if all(p.count == 1 for p in planned):
+            self.stats.decode_steps += 1
+        else:
+            self.stats.prefill_tokens += sum(p.count for p in planned if p.count > 1)
+        sampled: list[int] = []
+        if self.graphs and rows and len(rows) == len(planned) and all(p.count == 1 for p in planned):
+            sampled = self.step_fn.run_decode_graph(entries, rows)
+        else:
+            logits = self.step_fn.run(entries, commit=False)
+            if rows:
+                packed = self.step_fn._upload(sampler.pack_rows(rows))
+                sampled = sampler.sample_packed(logits, packed).tolist()
+        self.stats.generated += len(sampled)
+        finished = self.scheduler.commit(planned, sampled)
+        self.stats.preemptions = self.scheduler.stats["preemptions"]
+        for req in finished:
+            req.result = Result(list(req.output), req.finish)
+            if req.on_done is not None:
+                req.on_done(req)
+        return finished
+
+    def run(self, stop: threading.Event | None = None) -> None:
+        """Serve the inbox until nothing is queued or running (``stop`` None), or until ``stop``
+        is set (a serving thread; it blocks briefly on the inbox while idle)."""
+        start = time.perf_counter()
+        while True:
+            self._take_inbox()
+            if self.scheduler.idle():
+                if stop is None or stop.is_set():
+                    break
+                try:
+                    self.scheduler.add(self.inbox.get(timeout=0.02))
+                except queue.Empty:
+                    continue
+            self.step()
+        self.stats.wall_s += time.perf_counter() - start
+
+    def generate(self, requests: list[Request]) -> list[Result]:
+        """Submit ``requests`` and serve until the engine is idle."""
+        for r in requests:
+            self.submit(r)
+        self.run()
+        return [r.result for r in requests]

@@ -158,13 +158,15 @@ class StepFunction:
         return ctx, d_ids, d_want
 
     @torch.no_grad()
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def run(self, entries: list[StepEntry], commit: bool = True) -> torch.Tensor | None:
         """Run one step; returns float32 logits [wanted, vocab] in the order of the entries and
-        of their ``want`` lists (None when nothing is wanted)."""
+        of their ``want`` lists (None when nothing is wanted). ``commit`` False leaves advancing
+        the requests' lengths to the caller (the scheduler does it when it takes the tokens)."""
         ctx, ids, want = self.layout(entries)
         out = self.model.forward(self.model.embed(ids), ctx)
         logits = self.model.logits(out, want) if want.numel() else None
-        for e in entries:
-            self.cache.commit(e.rid, len(e.tokens))
+        if commit:
+            for e in entries:
+                self.cache.commit(e.rid, len(e.tokens))
         self.steps += 1
         return logits
