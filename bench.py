@@ -1,0 +1,395 @@
+"""Decode and prefill throughput of the LFM3 1.2B-size configuration on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16]
+
+A step is one decode step: every live request brings one token, the engine's captured step
+(embedding to sampled token) runs once. ``value`` is decoded tokens per second at ``--batch``
+requests whose prompts of 2,048 random tokens were prefilled first; it is timed on the device
+with CUDA events around exactly K steps after W warm-up steps. ``e2e`` is the same rate through
+``LLM.generate`` (host token ids in, host token ids out; every step uploads its layout from
+pinned memory and reads its tokens back). The line also carries the prefill of one 2,048-token
+prompt, the decode step's HBM roofline, and decode rates at batch 1 and 64. Weights are random
+(N(0, 0.02), bfloat16), token ids synthetic; there is no dataset or checkpoint behind it.
+Method after the reference's own decode bench (Tokenomos bench/decode.py:90-118,154-177:
+random prompts, greedy, steady-state step time; prefill of 2,048-token prompts).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: the 1.2B-size LFM3 configuration
+CONFIG_1P2B = {
+    "architectures": ["Lfm3ForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 16,
+    "layer_types": ["conv", "conv", "full_attention", "conv", "conv", "full_attention", "conv",
+                    "conv", "full_attention", "conv", "full_attention", "conv", "full_attention",
+                    "conv", "full_attention", "conv"],
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "intermediate_size": 8192, "vocab_size": 65536, "rope_theta": 1000000.0, "norm_eps": 1e-5,
+    "conv_L_cache": 3, "conv_bias": False, "tie_embedding": True,
+}
+PROMPT = 2048
+CONTEXT = 4096
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Clocks:
+    """Samples nvidia-smi while the timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": float(self.samples[0][1]) if self.samples else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def write_folder(folder: Path, layers: int) -> dict:
+    """The configuration's model folder with random weights drawn on the GPU (the same tensor
+    list and order as the random-weights mode; a CPU draw of 1.2 G values takes far longer)."""
+    import torch
+    from safetensors.torch import save_file
+
+    from tokenomos_b200 import models
+    from tokenomos_b200.weights import random_tensors
+
+    config = dict(CONFIG_1P2B)
+    config["layer_types"] = config["layer_types"][:layers]
+    config["num_hidden_layers"] = layers
+    arch = models.architecture_of(config)
+    decls = arch.declare(arch.config_class.from_dict(config)).tensor_decls()
+    tensors = random_tensors(decls, seed=0, std=0.02, dtype=torch.bfloat16, device="cuda")
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file({k: v.cpu() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    return config
+
+
+def weight_bytes(model, cfg) -> int:
+    """Bytes of weights a decode step reads once: every layer's matrices and vectors, the final
+    norm, and the head (the tied embedding matrix is read whole by the head)."""
+    total = 0
+    seen = set()
+
+    def add(t):
+        if t is not None and t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            return t.numel() * t.element_size()
+        return 0
+
+    for block in model.blocks:
+        for part in (block.mixer, block.ffn):
+            for v in vars(part).values():
+                if hasattr(v, "weight") and hasattr(v.weight, "numel"):
+                    total += add(v.weight)
+                elif hasattr(v, "numel"):
+                    total += add(v)
+    total += add(model.head.weight)
+    return total
+
+
+def kv_bytes_per_token(cfg) -> int:
+    n_attn = len(cfg.attention_layers())
+    return n_attn * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+
+
+def make_engine(model, batch: int, page: int):
+    from tokenomos_b200.engine.engine import Engine
+    pages = batch * (CONTEXT // page) + 2
+    return Engine(model, slots=batch, page=page, max_len=CONTEXT, pages=pages, prefill_budget=PROMPT,
+                  graphs=True)
+
+
+def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, seed: int = 0) -> dict:
+    """K decode steps timed on the device: prefill ``batch`` prompts, then replay the captured
+    decode step with the layout advanced on the host each step (the same work ``LLM.generate``
+    does, minus the scheduler)."""
+    import torch
+
+    from tokenomos_b200.engine.step import StepEntry
+    from tokenomos_b200.ops import _lib
+
+    eng = make_engine(model, batch, page)
+    step_fn, cache = eng.step_fn, eng.cache
+    g = torch.Generator().manual_seed(seed)
+    last = []
+    for r in range(batch):
+        ids = torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist()
+        cache.admit(r)
+        step_fn.run([StepEntry(r, ids, [])])
+        last.append(int(ids[-1]))
+    rows = [(0.0, 1.0, 0, 0.0, 0, 0)] * batch
+
+    def one():
+        nonlocal last
+        last = step_fn.run_decode_graph([StepEntry(r, [last[r]], []) for r in range(batch)], rows,
+                                        commit=True)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    ctx_start = cache.length(0)
+    calls0 = _lib.calls()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    graph = step_fn.decode_graph(batch)
+    out = {"ms_per_step": ms, "tok_s": batch / ms * 1e3, "ctx_start": ctx_start,
+           "ctx_end": cache.length(0), "launches_per_step": graph.launches,
+           "host_calls": _lib.calls() - calls0}
+    for r in range(batch):
+        cache.release(r)
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
+def device_prefill(model, cfg, page: int, reps: int = 3) -> dict:
+    import torch
+
+    from tokenomos_b200.engine.step import StepEntry
+
+    eng = make_engine(model, 1, page)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist()
+    times = []
+    for i in range(reps + 2):
+        eng.cache.admit(i)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        eng.step_fn.run([StepEntry(i, ids, [PROMPT - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        eng.cache.release(i)
+        if i >= 2:
+            times.append(start.elapsed_time(end))
+    ms = statistics.median(times)
+    # flops of the step: 2 * tokens * parameters of every matrix the tokens pass (the head runs
+    # on one row), plus causal attention (q.k and p.v over half the square)
+    d, inter, H, Hkv, D = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads,
+                           cfg.num_key_value_heads, cfg.head_dim)
+    flops = 0
+    for kind in cfg.layer_types:
+        per_tok = 3 * d * inter
+        if kind == "conv":
+            per_tok += 3 * d * d + d * d
+        else:
+            per_tok += (H + 2 * Hkv) * D * d + H * D * d
+            flops += 2 * 2 * H * D * PROMPT * (PROMPT + 1) / 2
+        flops += 2 * PROMPT * per_tok
+    flops += 2 * cfg.vocab_size * d
+    del eng
+    torch.cuda.empty_cache()
+    return {"ms": ms, "tokens": PROMPT, "tok_s": PROMPT / ms * 1e3, "flops": flops}
+
+
+def e2e_decode(llm, cfg, batch: int, steps: int, warmup: int) -> dict:
+    """The same decode through the Python entry point: ``LLM.generate`` with host token ids in
+    and out; the engine thread schedules, uploads each step's layout from pinned memory and
+    reads each step's tokens back."""
+    import torch
+
+    from tokenomos_b200.api.llm import SamplingParams
+
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist() for _ in range(batch)]
+    llm.engine.stats.stamps.clear()
+    outs = llm.generate(prompts, SamplingParams(max_tokens=warmup + steps + batch + 1))
+    assert all(len(o.token_ids) == warmup + steps + batch + 1 for o in outs)
+    stamps = llm.engine.stats.stamps
+    decode = [i for i, (_, rows, toks) in enumerate(stamps) if rows == batch and toks == batch]
+    first = decode[warmup]
+    last = decode[min(warmup + steps, len(decode) - 1)]
+    n = last - first
+    seconds = stamps[last][0] - stamps[first][0]
+    graph = llm.engine.step_fn.decode_graph(batch)
+    return {"value": batch * n / seconds, "unit": "tokens/s", "steps": n,
+            "h2d_bytes_per_step": 4 * graph.size, "d2h_bytes_per_step": 4 * graph.rows,
+            "ms_per_step": seconds / n * 1e3}
+
+
+def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page: int) -> None:
+    """A small case for a profiler: ``layers`` layers of the configuration, a cache filled to
+    ``ctx`` positions per request without running a prefill (its contents do not matter to a
+    kernel's duration), then ``steps`` eager decode steps or one prefill of 2,048 tokens."""
+    import tempfile
+
+    import torch
+
+    from tokenomos_b200 import models
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.engine.step import StepEntry, StepFunction
+
+    with tempfile.TemporaryDirectory(prefix="tokenomos_b200_profile_") as tmp:
+        folder = Path(tmp) / "model"
+        write_folder(folder, layers)
+        model = models.load(folder, "cuda", models.configure(folder, work="bf16"))
+    pages = batch * (-(-(ctx + PROMPT + steps) // page)) + 2
+    cache = CacheManager(model.state_specs(), page, pages, batch, torch.bfloat16, "cuda",
+                         max_len=ctx + PROMPT + steps + page)
+    step_fn = StepFunction(model, cache)
+    for r in range(batch):
+        cache.admit(r)
+        if ctx:
+            cache.extend(r, ctx)
+            cache.commit(r, ctx)
+    g = torch.Generator().manual_seed(0)
+    if mode == "decode":
+        for _ in range(steps):
+            step_fn.run([StepEntry(r, [int(torch.randint(0, 1000, (1,), generator=g))], [0])
+                         for r in range(batch)])
+    else:
+        ids = torch.randint(0, model.vocab, (PROMPT,), generator=g).tolist()
+        for _ in range(steps):
+            step_fn.run([StepEntry(0, ids, [PROMPT - 1])])
+            cache.release(0)
+            cache.admit(0)
+    torch.cuda.synchronize()
+    print(f"profile case done: {mode} layers={layers} batch={batch} ctx={ctx} steps={steps}")
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+                    help="run only a small case for a profiler (see profile_case) and exit")
+    ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=16, help="layers of the 16 the configuration has")
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference's wheel needs the maturin build backend and a Rust "
+                          "toolchain (pyproject.toml:1-3); neither is in the offline wheelhouse, so "
+                          "pip install --no-index into baseline/_ref fails"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus > 1 is not built")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+
+    from tokenomos_b200 import ops
+
+    torch.cuda.set_device(0)
+    ops.available()
+    if args.profile:
+        profile_case(args.profile, args.layers, args.batch, args.ctx, args.steps, args.page)
+        return 0
+    pk = peaks()
+    import tempfile
+
+    from tokenomos_b200.api.llm import LLM
+
+    tmp = tempfile.TemporaryDirectory(prefix="tokenomos_b200_bench_")
+    folder = Path(tmp.name) / "lfm3_1p2b_random"
+    write_folder(folder, args.layers)
+    pages = args.batch * (CONTEXT // args.page) + 2
+    llm = LLM(str(folder), work="bf16", slots=args.batch, page=args.page, max_len=CONTEXT,
+              pages=pages, prefill_budget=PROMPT, graphs=True)
+    model, cfg = llm.model, llm.model.config
+    clocks = Clocks()
+    clocks.start()
+    main_run = device_decode(model, cfg, args.batch, args.steps, warmup, args.page)
+    prefill = device_prefill(model, cfg, args.page)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(device_decode(model, cfg, b, min(args.steps, 64), warmup,
+                                                         args.page)["tok_s"], 1)
+    e2e = e2e_decode(llm, cfg, args.batch, args.steps, warmup)
+    clock_report = clocks.stop()
+    llm.close()
+    tmp.cleanup()
+
+    ctx_mid = (main_run["ctx_start"] + main_run["ctx_end"]) / 2
+    conv_layers = sum(k == "conv" for k in cfg.layer_types)
+    step_bytes = (weight_bytes(model, cfg) + args.batch * ctx_mid * kv_bytes_per_token(cfg)
+                  + args.batch * conv_layers * 2 * (cfg.conv_L_cache - 1) * cfg.hidden_size * 2)
+    achieved = step_bytes / (main_run["ms_per_step"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tokens/s (1.2B-size LFM3, batch 8, context 2048+)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": {
+            "model": "LFM3 1.2B-size (BASELINE configs[2])", "global_batch": args.batch,
+            "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
+            "layers": args.layers, "layers_of_config": 16, "hidden_size": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size,
+            "vocab_size": cfg.vocab_size, "conv_L_cache": cfg.conv_L_cache, "page_size": args.page,
+            "decode_ctx_start": main_run["ctx_start"], "decode_ctx_end": main_run["ctx_end"],
+            "l2": "inputs larger than L2 (weights read every step)",
+        },
+        "clocks": clock_report,
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": main_run["launches_per_step"] * args.steps,
+        "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
+                    "frac": round(prefill["flops"] / (prefill["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "peaks": pk["source"]},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -60,10 +60,20 @@ TINY_C = {
                               "partial_rotary_factor": 0.5},
     },
 }
+# a fourth one whose attention takes the tensor-core kernels in bfloat16 (head size 64, groups of
+# four), with a window that spans several pages
+TINY_D = {
+    "architectures": ["Lfm3ForCausalLM"], "hidden_size": 128, "num_hidden_layers": 4,
+    "layer_types": ["full_attention", "conv", "sliding_attention", "full_attention"],
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+    "intermediate_size": 160, "vocab_size": 400, "rope_theta": 500000.0, "norm_eps": 1e-5,
+    "conv_L_cache": 3, "conv_bias": False, "tie_embedding": True, "sliding_window": 40,
+}
 TINY = {
     "A": dict(config=TINY_A, seed=0, std=0.02, norm_std=0.0, page=16),
     "B": dict(config=TINY_B, seed=1, std=0.05, norm_std=0.1, page=8),
     "C": dict(config=TINY_C, seed=2, std=0.08, norm_std=0.2, page=4),
+    "D": dict(config=TINY_D, seed=3, std=0.06, norm_std=0.1, page=16),
 }
 
 

@@ -441,3 +441,122 @@ def test_sample_is_batch_invariant_and_step_dependent():
     assert shuffled.tolist() == together.flip(0).tolist()
     steps = [sample_rows(logits[:1].repeat(64, 1), [(1.5, 1.0, 0, 0.0, 5, s) for s in range(64)])]
     assert len(set(steps[0].tolist())) > 8
+
+
+# ---- tensor-core attention (bfloat16, head sizes 64 and 128) -------------------------------------
+
+def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None):
+    """Like ``attention_case`` but through the tensor-core kernels: multi-token sequences go to
+    the prefill kernel, single-token ones to the decode kernel (split ``nsplit`` ways)."""
+    from tokenomos_b200 import ops
+    dtype = torch.bfloat16
+    assert ops.attention_mma_supported(H, Hkv, D, dtype)
+    G = H // Hkv
+    total = [c + n for c, n in seqs]
+    blocks = [-(-t // P) for t in total]
+    width = max(blocks)
+    pages = sum(blocks) + 1
+    perm = (torch.randperm(pages - 1) + 1).tolist()
+    pool = torch.full((pages, 2, Hkv, P, D), float("nan"), dtype=torch.float64)
+    table = torch.zeros(len(seqs), width, dtype=torch.int32)
+    ks, vs, qs = [], [], []
+    for s, (c, n) in enumerate(seqs):
+        k = torch.randn(total[s], Hkv, D).to(dtype).double()
+        v = torch.randn(total[s], Hkv, D).to(dtype).double()
+        q = torch.randn(n, H, D).to(dtype).double()
+        if boost is not None:
+            boost(s, q, k, v)
+        for b in range(blocks[s]):
+            page = perm.pop()
+            table[s, b] = page
+            rows = min(P, total[s] - b * P)
+            pool[page, 0, :, :rows] = k[b * P:b * P + rows].transpose(0, 1)
+            pool[page, 1, :, :rows] = v[b * P:b * P + rows].transpose(0, 1)
+        ks.append(k), vs.append(v), qs.append(q)
+    positions = [p for (c, n) in seqs for p in range(c, c + n)]
+    tok_seq = [s for s, (c, n) in enumerate(seqs) for _ in range(n)]
+    per_tile = ops.attention_prefill_mma_tokens(H, Hkv)
+    tok0, ntok, singles, start = [], [], [], 0
+    for c, n in seqs:
+        if n == 1:
+            singles.append(start)
+        else:
+            for o in range(0, n, per_tile):
+                tok0.append(start + o)
+                ntok.append(min(per_tile, n - o))
+        start += n
+    q_dev, pool_dev = dev(torch.cat(qs), dtype), dev(pool, dtype)
+    out = torch.full_like(q_dev, float("nan"))
+    if tok0:
+        ops.attention_prefill_mma(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table),
+                                  i32(tok0), i32(ntok), window, D ** -0.5)
+    if singles:
+        ops.attention_decode_mma(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table),
+                                 i32(singles), window, D ** -0.5, nsplit or 1)
+    want = []
+    for s, (c, n) in enumerate(seqs):
+        k = ks[s].repeat_interleave(G, 1)
+        v = vs[s].repeat_interleave(G, 1)
+        sc = torch.einsum("ihd,jhd->hij", qs[s], k) * D ** -0.5
+        i = torch.arange(c, c + n)[:, None]
+        j = torch.arange(total[s])[None, :]
+        vis = j <= i
+        if window:
+            vis &= (i - j) < window
+        sc = sc.masked_fill(~vis[None], float("-inf"))
+        want.append(torch.einsum("hij,jhd->ihd", sc.softmax(-1), v))
+    return out, torch.cat(want)
+
+
+@pytest.mark.parametrize("H, Hkv, D, P", [(32, 8, 64, 16), (8, 8, 64, 64), (4, 2, 128, 32), (16, 1, 64, 8),
+                                          (6, 3, 64, 7), (8, 1, 128, 16)])
+@pytest.mark.parametrize("nsplit", [1, 3, 16])
+def test_attention_mma_mixed_batches(H, Hkv, D, P, nsplit):
+    seqs = [(0, 1), (17, 3), (0, 40), (40, 100), (333, 1), (5, 2), (64, 64), (1000, 1), (0, 130)]
+    got, want = attention_mma_case(H, Hkv, D, P, seqs, nsplit=nsplit)
+    close(got, want, torch.bfloat16, f"mma attention H{H} Hkv{Hkv} D{D} P{P} split {nsplit}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_mma_window(window):
+    seqs = [(0, 150), (70, 1), (20, 30), (3, 2), (500, 1), (63, 1)]
+    got, want = attention_mma_case(8, 2, 64, 16, seqs, window=window, nsplit=2)
+    close(got, want, torch.bfloat16, f"mma window {window}")
+
+
+def test_attention_mma_far_key_and_window_edge():
+    D, ctx = 64, 700
+
+    def far(s, q, k, v):
+        q[:] = 0.0
+        k[:] = 0.0
+        q[:, :, 0] = 8.0
+        k[13, :, 0] = 8.0
+
+    for seqs, nsplit in (([(ctx, 1)], 1), ([(ctx, 1)], 5), ([(ctx - 30, 31)], 1)):
+        got, want = attention_mma_case(8, 2, D, 16, seqs, boost=far, nsplit=nsplit)
+        close(got, want, torch.bfloat16, "far key")
+        assert (got.double().cpu() - want).abs().max().item() < 0.05
+    for offset, seen in ((9, True), (10, False)):
+        def edge(s, q, k, v, offset=offset):
+            q[:] = 0.0
+            k[:] = 0.0
+            q[:, :, 0] = 8.0
+            k[ctx - offset, :, 0] = 8.0
+            v[ctx - offset] = 5.0
+
+        for nsplit in (1, 4):
+            got, want = attention_mma_case(8, 2, D, 16, [(ctx, 1)], window=10, boost=edge, nsplit=nsplit)
+            close(got, want, torch.bfloat16, f"window edge {offset}")
+            assert (got.double().cpu().mean().item() > 2.0) == seen
+
+
+def test_attention_mma_refuses_other_shapes():
+    from tokenomos_b200 import ops
+    assert not ops.attention_mma_supported(4, 1, 24, torch.bfloat16)
+    assert not ops.attention_mma_supported(6, 2, 64, torch.bfloat16)      # group of 3
+    assert not ops.attention_mma_supported(32, 8, 64, torch.float32)
+    q = torch.zeros(1, 4, 24, dtype=torch.bfloat16, device="cuda")
+    pool = torch.zeros(2, 2, 1, 8, 24, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="is not taken"):
+        ops.attention_decode_mma(q, pool, q.clone(), i32([0]), i32([0]), i32([[1]]), i32([0]), None, 1.0, 1)

@@ -42,7 +42,7 @@ def _close(got, want, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixers_and_ffn_alone(name, dtype, model_folders):
     """Every block's mixer and feed-forward, fed the same normed input as the plain functions."""
     from tokenomos_b200 import models

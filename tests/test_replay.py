@@ -22,7 +22,8 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
 TOL_SAME_DTYPE = {"float32": 1e-5, "bfloat16": 2e-2}
 
-LENGTHS = {"A": [5, 17, 33, 70, 96, 41], "B": [1, 9, 40, 64, 130, 57], "C": [3, 26, 75, 50, 110, 38]}
+LENGTHS = {"A": [5, 17, 33, 70, 96, 41], "B": [1, 9, 40, 64, 130, 57], "C": [3, 26, 75, 50, 110, 38],
+           "D": [2, 31, 150, 65, 200, 90]}
 
 
 def requests_for(name: str) -> dict[str, list[int]]:
@@ -59,7 +60,7 @@ def compare(got: dict, want: dict, tol: float, what: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_way_of_cutting(name, dtype, model_folders):
     folder = model_folders[name][torch.bfloat16]
     page = TINY[name]["page"]

@@ -1,0 +1,526 @@
+// Paged attention on the tensor cores for bfloat16 and head sizes 64 and 128 (warp-level
+// mma.sync m16n8k16, cp.async staging, online softmax in 32-bit).
+//
+// Rows of a tile are (token, query head) pairs that share one KV head, so the group's heads
+// reuse every key and value that is loaded.
+//   prefill kernel: a CTA takes up to 64 rows (64/G tokens of one sequence, G heads each), four
+//     warps of 16 rows, and walks the keys in tiles of 64 through a double-buffered cp.async
+//     pipeline; keys come from the paged cache, this step's own keys included.
+//   decode kernel: one token per sequence, its G heads are the (padded) 16 rows; the four warps
+//     of a CTA take alternate 32-key tiles of the CTA's key range, and `nsplit` CTAs split one
+//     sequence's keys so that small batches still fill the GPU. Partial results (row maximum,
+//     row sum, unnormalised output) go to scratch memory and a second kernel merges them.
+// Masking, scale, rounding of P to bfloat16 and the unrounded row sum follow the generic kernel
+// (Tokenomos kernels/attention/paged.py:67-76,150,267; models/blocks/attention.py:31-40,173).
+// Keys past a query's position are never read: their shared-memory rows are zero-filled.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// 16 bytes global -> shared; `valid` false writes zeros instead (nothing is read)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bf16 tile, XOR-swizzled so
+// that the 8 rows an ldmatrix reads fall into different banks
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+    return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Load `rows` keys (or values) starting at key j0 of sequence `seq` into a swizzled tile with
+// `nthreads` threads; keys outside [j_first, j_last] are zero-filled, not read.
+template <int D>
+__device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
+                                          const int* __restrict__ bt_row, int j0, int rows,
+                                          int j_first, int j_last, int kvh, int Hkv, int P, int which,
+                                          int tid, int nthreads) {
+    constexpr int CH = D / 8;
+    for (int i = tid; i < rows * CH; i += nthreads) {
+        const int r = i / CH, c = i % CH;
+        const int j = j0 + r;
+        const bool valid = j >= j_first && j <= j_last;
+        const __nv_bfloat16* src = pool;
+        if (valid) {
+            const int page = bt_row[j / P];
+            src = pool + (((size_t)page * 2 + which) * Hkv + kvh) * (size_t)P * D +
+                  (size_t)(j % P) * D + c * 8;
+        }
+        cp_async16(tile + tile_off<D>(r, c), src, valid);
+    }
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// One 16-row x NK-key block of the online softmax for a warp: S = Q K^T from `ktile`, mask,
+// update (m, l, O) with V from `vtile`. NK is 64 (prefill) or 32 (decode).
+template <int D, int NK>
+__device__ __forceinline__ void warp_block(const uint32_t (&qf)[D / 16][4], uint32_t ktile,
+                                           uint32_t vtile, int j0, int pos_lo, int pos_hi,
+                                           int window, float scale_log2, bool need_mask,
+                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    float s[NK / 8][4];
+#pragma unroll
+    for (int n = 0; n < NK / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+    // S = Q K^T: for each pair of 8-key tiles and each 16-wide slice of the head
+    {
+        const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+        for (int np = 0; np < NK / 16; ++np) {
+            const int key = np * 16 + r + 8 * (mi >> 1);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t b[4];
+                ldmatrix_x4(b, ktile + tile_off<D>(key, ks * 2 + (mi & 1)));
+                mma16816(s[2 * np], qf[ks], b[0], b[1]);
+                mma16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+    }
+    // mask: rows g (position pos_lo) and g + 8 (position pos_hi); key of element e of tile n
+    if (need_mask) {
+#pragma unroll
+        for (int n = 0; n < NK / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + n * 8 + 2 * t + (e & 1);
+                const int pos = (e < 2) ? pos_lo : pos_hi;
+                const bool visible = j <= pos && (window <= 0 || pos - j < window);
+                if (!visible) s[n][e] = -INFINITY;
+            }
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NK / 8; ++n) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float alpha[2], msafe[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float m_new = fmaxf(m[h], mx[h]);
+        msafe[h] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[h] = exp2f((m[h] - msafe[h]) * scale_log2);
+        m[h] = m_new;
+        l[h] *= alpha[h];
+    }
+    uint32_t pf[NK / 16][4];
+#pragma unroll
+    for (int n = 0; n < NK / 8; ++n) {
+        const float p0 = exp2f((s[n][0] - msafe[0]) * scale_log2);
+        const float p1 = exp2f((s[n][1] - msafe[0]) * scale_log2);
+        const float p2 = exp2f((s[n][2] - msafe[1]) * scale_log2);
+        const float p3 = exp2f((s[n][3] - msafe[1]) * scale_log2);
+        l[0] += p0 + p1;
+        l[1] += p2 + p3;
+        // the C layout of two neighbouring 8-key tiles is the A layout of one 16-key step
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= alpha[0];
+        o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1];
+        o[n][3] *= alpha[1];
+    }
+    // O += P V
+    {
+        const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < NK / 16; ++ks) {
+            const int key = ks * 16 + r + 8 * (mi & 1);
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vtile + tile_off<D>(key, dp * 2 + (mi >> 1)));
+                mma16816(o[2 * dp], pf[ks], b[0], b[1]);
+                mma16816(o[2 * dp + 1], pf[ks], b[2], b[3]);
+            }
+        }
+    }
+}
+
+// Query fragments of 16 rows straight from global memory. Row r of the warp is
+// (token tok0 + r / G, head h0 + r % G); rows at or past `rows` read as zero.
+template <int D>
+__device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfloat16* __restrict__ q,
+                                       int row0, int rows, int tok0, int G, int H, int h0) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = row0 + g + 8 * half;
+        const bool ok = r < rows;
+        const __nv_bfloat16* src = q;
+        if (ok) src = q + ((size_t)(tok0 + r / G) * H + h0 + r % G) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t lo = 0u, hi = 0u;
+            if (ok) {
+                lo = *reinterpret_cast<const uint32_t*>(src + ks * 16 + 2 * t);
+                hi = *reinterpret_cast<const uint32_t*>(src + ks * 16 + 8 + 2 * t);
+            }
+            qf[ks][half] = lo;       // a0 (row g) / a1 (row g + 8): columns 2t, 2t + 1
+            qf[ks][half + 2] = hi;   // a2 / a3: columns 2t + 8, 2t + 9
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill: 64 rows per CTA, all keys
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
+                        __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
+                        const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                        int bt_stride, const int* __restrict__ tile_tok0,
+                        const int* __restrict__ tile_ntok, int H, int Hkv, int P, int window,
+                        float scale) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_BYTES = 64 * D * 2;
+    const uint32_t smem = smem_u32(smem_raw);   // [stage][K|V][64][D]
+    const int G = H / Hkv;
+    const int kvh = blockIdx.y;
+    const int tok0 = tile_tok0[blockIdx.x], ntok = tile_ntok[blockIdx.x];
+    const int rows = ntok * G;
+    const int seq = tok_seq[tok0];
+    const int* bt_row = block_table + (size_t)seq * bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2;
+    const int pos_first = positions[tok0];
+    const int pos_last = pos_first + ntok - 1;       // consecutive positions within a tile
+    const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int j_begin = (lo / 64) * 64;
+
+    uint32_t qf[D / 16][4];
+    load_q<D>(qf, q, warp * 16, rows, tok0, G, H, kvh * G);
+    const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+    const int pos_lo = r_lo < rows ? pos_first + r_lo / G : -1;
+    const int pos_hi = r_hi < rows ? pos_first + r_hi / G : -1;
+    // the warp's own key range: nothing above its last row's position, nothing a window hides
+    const int w_last_row = min(rows, warp * 16 + 16) - 1;
+    const int w_pos_max = w_last_row >= warp * 16 ? pos_first + w_last_row / G : -1;
+    const int w_pos_min = pos_first + (warp * 16) / G;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    const float scale_log2 = scale * LOG2E;
+
+    const int n_tiles = (pos_last - j_begin) / 64 + 1;
+    auto issue = [&](int it) {
+        const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
+        const int j0 = j_begin + it * 64;
+        load_tile<D>(base, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
+        load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+        cp_async_commit();
+    };
+    issue(0);
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (it + 1 < n_tiles) issue(it + 1);
+        const int j0 = j_begin + it * 64;
+        const bool active = w_pos_max >= j0 && (window <= 0 || j0 + 63 > w_pos_min - window);
+        if (active) {
+            const bool need_mask = (j0 + 63 > w_pos_min) || (window > 0 && j0 <= w_pos_max - window) ||
+                                   pos_lo < 0 || pos_hi < 0;
+            const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
+            warp_block<D, 64>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                              need_mask, m, l, o);
+        }
+    }
+    // finish: row sums over the 4 threads of a row, normalise, store
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    const int t = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + 8 * half;
+        if (r >= rows) continue;
+        const float inv = l[half] > 0.f ? 1.0f / l[half] : 0.f;
+        __nv_bfloat16* dst = out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode: one token per sequence; CTA (token, kv head, split); warps take alternate 32-key tiles
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
+                       const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                       int bt_stride, const int* __restrict__ tok_index, int H, int Hkv, int P,
+                       int window, float scale, int nsplit, float* __restrict__ part_o,
+                       float* __restrict__ part_ml) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_BYTES = 32 * D * 2;           // one warp's 32 keys
+    const int G = H / Hkv;
+    const int i = blockIdx.x;                        // which decode token
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int tok = tok_index[i];
+    const int seq = tok_seq[tok];
+    const int pos = positions[tok];
+    const int* bt_row = block_table + (size_t)seq * bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int j_begin = (lo / 32) * 32;
+    const int tiles = (pos - j_begin) / 32 + 1;
+    const int per_split = (tiles + nsplit - 1) / nsplit;
+    const int t_begin = split * per_split, t_end = min(tiles, t_begin + per_split);
+
+    uint32_t qf[D / 16][4];
+    load_q<D>(qf, q, 0, G, tok, G, H, kvh * G);      // rows 0..G-1 are the group's heads
+    const int pos_lo = g < G ? pos : -1, pos_hi = g + 8 < G ? pos : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    const float scale_log2 = scale * LOG2E;
+
+    // the warp's private double buffer: [stage][K|V][32][D]
+    const uint32_t wbase = smem_u32(smem_raw) + (uint32_t)warp * 4 * TILE_BYTES;
+    auto issue = [&](int tile, int stage) {
+        const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
+        const int j0 = j_begin + tile * 32;
+        load_tile<D>(base, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 0, lane, 32);
+        load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 1, lane, 32);
+        cp_async_commit();
+    };
+    int stage = 0;
+    if (t_begin + warp < t_end) issue(t_begin + warp, 0);
+    for (int tile = t_begin + warp; tile < t_end; tile += 4) {
+        const bool more = tile + 4 < t_end;
+        if (more) issue(tile + 4, stage ^ 1);
+        if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncwarp();
+        const int j0 = j_begin + tile * 32;
+        const bool need_mask = true;                 // rows past G are always masked
+        const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
+        warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                          need_mask, m, l, o);
+        __syncwarp();
+        stage ^= 1;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    // merge the four warps through shared memory (the K/V buffers are done with)
+    __syncthreads();
+    float* sm_o = reinterpret_cast<float*>(smem_raw);              // [4][16][D]
+    float* sm_ml = sm_o + 4 * 16 * D;                              // [4][16][2]
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + 8 * half;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            sm_o[(warp * 16 + r) * D + n * 8 + 2 * t] = o[n][half * 2];
+            sm_o[(warp * 16 + r) * D + n * 8 + 2 * t + 1] = o[n][half * 2 + 1];
+        }
+        if (t == 0) {
+            sm_ml[(warp * 16 + r) * 2] = m[half];
+            sm_ml[(warp * 16 + r) * 2 + 1] = l[half];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += 128) {
+        const int r = idx / D, c = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_ml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * scale_log2);
+            L += sm_ml[(w * 16 + r) * 2 + 1] * f;
+            acc += sm_o[(w * 16 + r) * D + c] * f;
+        }
+        const int head = kvh * G + r;
+        if (nsplit == 1) {
+            out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t slot = ((size_t)i * H + head) * nsplit + split;
+            part_o[slot * D + c] = acc;
+            if (c == 0) {
+                part_ml[slot * 2] = M;
+                part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+template <int D>
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out,
+                                         const int* __restrict__ tok_index, int H, int nsplit,
+                                         float scale) {
+    const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
+    const size_t base = ((size_t)i * H + head) * nsplit;
+    const float scale_log2 = scale * LOG2E;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        const float f = ms == -INFINITY ? 0.f : exp2f((ms - M) * scale_log2);
+        L += part_ml[(base + s) * 2 + 1] * f;
+        acc += part_o[(base + s) * D + c] * f;
+    }
+    out[((size_t)tok_index[i] * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+bool mma_shape_ok(int H, int Hkv, int D) {
+    if (Hkv <= 0 || H % Hkv) return false;
+    const int G = H / Hkv;
+    return (D == 64 || D == 128) && G >= 1 && G <= 16 && (G & (G - 1)) == 0;
+}
+
+}  // namespace
+
+// 1 when the tensor-core kernels take this shape (bfloat16, head size 64 or 128, a group of
+// 1, 2, 4, 8 or 16 query heads per KV head); otherwise the generic kernel is the one to call.
+TK_API int tk_attn_mma_supported(int H, int Hkv, int D) { return mma_shape_ok(H, Hkv, D) ? 1 : 0; }
+
+// Tokens per tile the prefill kernel expects: 64 rows / G heads.
+TK_API int tk_attn_prefill_mma_tokens(int H, int Hkv) { return 64 / (H / Hkv); }
+
+TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, const int* positions,
+                               const int* tok_seq, const int* block_table, int bt_stride,
+                               const int* tile_tok0, const int* tile_ntok, int n_tiles, int H,
+                               int Hkv, int D, int P, int window, float scale,
+                               cudaStream_t stream) {
+    TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_prefill_mma: shape H=%d Hkv=%d D=%d is not taken "
+                 "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
+    TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_mma: bad page size or tile count");
+    if (n_tiles == 0) return 0;
+    dim3 grid(n_tiles, Hkv);
+    const size_t smem = 2 * 2 * 64 * (size_t)D * 2;
+    auto q_ = (const __nv_bfloat16*)q;
+    auto p_ = (const __nv_bfloat16*)kv_pool;
+    auto o_ = (__nv_bfloat16*)out;
+    if (D == 64) {
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_prefill_mma_kernel<64><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table,
+                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
+    } else {
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_prefill_mma_kernel<128><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table,
+                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
+    }
+    TK_CHECK_LAUNCH("attn_prefill_mma");
+    return 0;
+}
+
+// Floats of scratch the decode kernel needs for `n` tokens split `nsplit` ways:
+// part_o [n, H, nsplit, D] then part_ml [n, H, nsplit, 2] (nothing when nsplit is 1).
+TK_API int64_t tk_attn_decode_mma_scratch(int n, int H, int D, int nsplit) {
+    return nsplit <= 1 ? 0 : (int64_t)n * H * nsplit * (D + 2);
+}
+
+TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, const int* positions,
+                              const int* tok_seq, const int* block_table, int bt_stride,
+                              const int* tok_index, int n, int H, int Hkv, int D, int P, int window,
+                              float scale, int nsplit, float* scratch, cudaStream_t stream) {
+    TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_decode_mma: shape H=%d Hkv=%d D=%d is not taken "
+                 "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
+    TK_CHECK_ARG(P > 0 && n >= 0 && nsplit >= 1 && nsplit <= 65535, "attn_decode_mma: bad sizes");
+    TK_CHECK_ARG(nsplit == 1 || scratch != nullptr, "attn_decode_mma: %d splits need scratch memory", nsplit);
+    if (n == 0) return 0;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n * H * nsplit * D : nullptr;
+    dim3 grid(n, Hkv, nsplit);
+    // K/V staging: 4 warps x 2 stages x (K, V) x 32 keys; the merge reuses it as [4][16][D+2] floats
+    const size_t staging = 4 * 2 * 2 * 32 * (size_t)D * 2;
+    const size_t merge = 4 * 16 * ((size_t)D + 2) * sizeof(float);
+    const size_t smem = staging > merge ? staging : merge;
+    auto q_ = (const __nv_bfloat16*)q;
+    auto p_ = (const __nv_bfloat16*)kv_pool;
+    auto o_ = (__nv_bfloat16*)out;
+    if (D == 64) {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_decode_mma_kernel<64><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
+            attn_decode_merge_kernel<64><<<dim3(n, H), 64, 0, stream>>>(part_o, part_ml, o_, tok_index, H, nsplit, scale);
+    } else {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_decode_mma_kernel<128><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
+            attn_decode_merge_kernel<128><<<dim3(n, H), 128, 0, stream>>>(part_o, part_ml, o_, tok_index, H, nsplit, scale);
+    }
+    TK_CHECK_LAUNCH("attn_decode_merge");
+    return 0;
+}

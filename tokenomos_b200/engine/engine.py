@@ -43,7 +43,7 @@ class Stats:
 
 class Engine:
     def __init__(self, model, slots: int = 64, page: int = 16, max_len: int = 4096,
-                 pages: int | None = None, prefill_budget: int = 2048, graphs: bool = False,
+                 pages: int | None = None, prefill_budget: int = 2048, graphs: bool = True,
                  kv_fraction: float = 0.8, device: str = "cuda"):
         """``slots``: live requests. ``page``: tokens per cache page. ``max_len``: longest
         sequence (prompt + reply). ``pages``: pages per cache group, the null page included

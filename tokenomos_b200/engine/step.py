@@ -13,6 +13,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from tokenomos_b200.cache.manager import CacheManager, OutOfPages
@@ -36,27 +37,132 @@ class _Tiles:
         self.seq_lens, self.device, self.upload = seq_lens, device, upload
         self.cache: dict[int, tuple] = {}
 
-    def tiles(self, size: int):
-        if size not in self.cache:
+    def tiles(self, size: int, which: str = "all"):
+        key = (size, which)
+        if key not in self.cache:
             seq, tok0, off, n = [], [], [], []
             start = 0
             for s, length in enumerate(self.seq_lens):
-                for o in range(0, length, size):
-                    seq.append(s)
-                    tok0.append(start + o)
-                    off.append(o)
-                    n.append(min(size, length - o))
+                if which == "all" or length > 1:
+                    for o in range(0, length, size):
+                        seq.append(s)
+                        tok0.append(start + o)
+                        off.append(o)
+                        n.append(min(size, length - o))
                 start += length
             k = len(seq)
-            flat = self.upload(seq + tok0 + off + n)
-            self.cache[size] = (flat[:k], flat[k:2 * k], flat[2 * k:3 * k], flat[3 * k:])
-        return self.cache[size]
+            if k == 0:
+                empty = torch.empty(0, dtype=torch.int32, device=self.device)
+                self.cache[key] = (empty, empty, empty, empty)
+            else:
+                flat = self.upload(seq + tok0 + off + n)
+                self.cache[key] = (flat[:k], flat[k:2 * k], flat[2 * k:3 * k], flat[3 * k:])
+        return self.cache[key]
+
+    def singles(self):
+        if "singles" not in self.cache:
+            idx, start = [], 0
+            for length in self.seq_lens:
+                if length == 1:
+                    idx.append(start)
+                start += length
+            self.cache["singles"] = (self.upload(idx) if idx else
+                                     torch.empty(0, dtype=torch.int32, device=self.device))
+        return self.cache["singles"]
+
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 96, 128, 192, 256, 384, 512)
+
+
+class _ConstTiles:
+    """Tiles of a decode-only step: one token per sequence, whatever size is asked for."""
+
+    def __init__(self, arange: torch.Tensor, zeros: torch.Tensor, ones: torch.Tensor):
+        self.value = (arange, arange, zeros, ones)
+        self.none = (arange[:0], arange[:0], arange[:0], arange[:0])
+
+    def tiles(self, size: int, which: str = "all"):
+        return self.value if which == "all" else self.none
+
+    def singles(self):
+        return self.value[0]
+
+
+class _DecodeGraph:
+    """One captured decode step for ``rows`` sequences: static layout buffer in, tokens out."""
+
+    def __init__(self, step_fn: "StepFunction", rows: int):
+        cache, dev = step_fn.cache, step_fn.device
+        self.rows = rows
+        self.width = cache.max_blocks
+        groups = list(cache.groups)
+        b = rows
+        # layout of the int32 buffer the host fills each step
+        self.off = {}
+        o = 0
+        for name, n in (("positions", b), ("seq_ctx", b), ("seq_slot", b), ("ids", b),
+                        ("sampling", 6 * b)):
+            self.off[name] = (o, n)
+            o += n
+        for g in groups:
+            self.off[("table", g)] = (o, b * self.width)
+            o += b * self.width
+        self.size = o
+        self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.tokens_host = torch.zeros(b, dtype=torch.int32).pin_memory()
+        arange = torch.arange(b + 1, dtype=torch.int32, device=dev)
+        zeros = torch.zeros(b, dtype=torch.int32, device=dev)
+        ones = torch.ones(b, dtype=torch.int32, device=dev)
+
+        def view(name):
+            a, n = self.off[name]
+            return self.dev[a:a + n]
+
+        self.ctx = StepContext(
+            n_tokens=b, n_seqs=b, positions=view("positions"), tok_seq=arange[:b],
+            cu_seqlens=arange, seq_ctx=view("seq_ctx"), seq_slot=view("seq_slot"),
+            block_tables={g: view(("table", g)).view(b, self.width) for g in groups},
+            states=cache.states, state_groups=cache.state_groups, page_size=cache.page_size,
+            host=HostLayout([1] * b, [0] * b, [0] * b, True, cache.max_len),
+            tile_source=_ConstTiles(arange[:b], zeros, ones))
+        self.ids, self.want, self.sampling = view("ids"), arange[:b], view("sampling")
+        self.graph = None
+        self.launches = 0
+
+    def body(self, model):
+        from tokenomos_b200.sampling import sampler
+
+        out = model.forward(model.embed(self.ids), self.ctx)
+        logits = model.logits(out, self.want)
+        sampler.sample_packed(logits, self.sampling, self.tokens)
+
+    def capture(self, model):
+        from tokenomos_b200.ops import _lib
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.body(model)              # warm-up outside the capture (library handles, sizes)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = _lib.calls()
+        with torch.cuda.graph(graph):
+            self.body(model)
+        self.launches = _lib.calls() - before
+        self.graph = graph
 
 
 class StepFunction:
     def __init__(self, model, cache: CacheManager, staging_ints: int = 1 << 20):
         self.model, self.cache = model, cache
         self.device = cache.device
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
         # pinned staging for the layout, used round-robin so that a copy still in flight is
         # never overwritten (each buffer is reused only after `ring` later uploads)
         self._ring = [torch.empty(staging_ints, dtype=torch.int32).pin_memory()
@@ -81,6 +187,7 @@ class StepFunction:
         buf[:n] = torch.tensor(values, dtype=torch.int32)
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         out.copy_(buf[:n], non_blocking=True)
+        self.h2d_bytes += 4 * n
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -149,7 +256,8 @@ class StepFunction:
         d_pos, d_tok_seq, d_cu = take(T), take(T), take(S + 1)
         d_ctx, d_slot, d_ids, d_want = take(S), take(S), take(T), take(len(want))
         block_tables = {g: take(S * width).view(S, width) for g in groups}
-        host = HostLayout(seq_lens, seq_ctx, seq_slot, all(n == 1 for n in seq_lens))
+        host = HostLayout(seq_lens, seq_ctx, seq_slot, all(n == 1 for n in seq_lens),
+                          max(c + n for c, n in zip(seq_ctx, seq_lens)))
         ctx = StepContext(
             n_tokens=T, n_seqs=S, positions=d_pos, tok_seq=d_tok_seq, cu_seqlens=d_cu,
             seq_ctx=d_ctx, seq_slot=d_slot, block_tables=block_tables, states=cache.states,
@@ -170,3 +278,62 @@ class StepFunction:
                 self.cache.commit(e.rid, len(e.tokens))
         self.steps += 1
         return logits
+
+    # ---- decode-only steps through a CUDA graph ----
+
+    def decode_graph(self, rows: int) -> _DecodeGraph:
+        """The captured decode step of the smallest bucket that holds ``rows`` sequences."""
+        bucket = next((b for b in DECODE_BUCKETS if b >= rows), rows)
+        bucket = min(bucket, max(rows, self.cache.max_requests))
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            g.capture(self.model)
+        return g
+
+    @torch.no_grad()
+    def run_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
+                         commit: bool = False) -> list[int]:
+        """One decode step for entries of one token each: the layout goes up in one copy from
+        pinned memory, the captured graph (embedding to sampled token) replays, the tokens come
+        back in one copy. Rows of the bucket beyond the entries point at the null slot and the
+        null page. Returns the sampled token of each entry."""
+        from tokenomos_b200.sampling import sampler
+
+        cache = self.cache
+        n = len(entries)
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise ValueError("the decode graph takes one token per request")
+            cache.extend(e.rid, 1)
+        g = self.decode_graph(n)
+        h, b, width = g.host_np, g.rows, g.width
+        h[:] = 0
+        lengths = [cache.length(e.rid) for e in entries]
+        o, _ = g.off["positions"]
+        h[o:o + n] = lengths
+        o, _ = g.off["seq_ctx"]
+        h[o:o + n] = lengths
+        o, _ = g.off["seq_slot"]
+        h[o:o + n] = [cache.slot(e.rid) for e in entries]
+        o, _ = g.off["ids"]
+        h[o:o + n] = [e.tokens[0] for e in entries]
+        o, _ = g.off["sampling"]
+        pad = [(0.0, 1.0, 0, 0.0, 0, 0)] * (b - n)
+        h[o:o + 6 * b] = sampler.pack_rows(list(sampling_rows) + pad)
+        for grp in cache.groups:
+            o, _ = g.off[("table", grp)]
+            for i, e in enumerate(entries):
+                row = cache.block_table(e.rid, grp)
+                h[o + i * width:o + i * width + len(row)] = row
+        g.dev.copy_(g.host, non_blocking=True)
+        g.graph.replay()
+        g.tokens_host.copy_(g.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.h2d_bytes += 4 * g.size
+        self.d2h_bytes += 4 * b
+        self.steps += 1
+        if commit:
+            for e in entries:
+                cache.commit(e.rid, 1)
+        return g.tokens_host[:n].tolist()

@@ -15,7 +15,9 @@ from tokenomos_b200.ops._lib import BF16, F32, KernelError
 
 __all__ = [
     "KernelError", "available", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
-    "qk_norm_rope_write", "attention", "attention_rows", "conv_gated", "conv_min_tile",
+    "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
+    "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
+    "conv_gated", "conv_min_tile",
     "gemm", "sample",
 ]
 
@@ -182,6 +184,59 @@ def attention(q: torch.Tensor, kv_pool: torch.Tensor, positions: torch.Tensor,
               _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), tokens_per_tile, H, Hkv, D, P,
               int(window or 0), float(scale), _dtype_code(q), _stream())
     return out
+
+
+def attention_mma_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core attention kernels take this shape (else: ``attention``)."""
+    return dtype == torch.bfloat16 and bool(_lib.call("tk_attn_mma_supported", heads, kv_heads, head_dim))
+
+
+def attention_prefill_mma_tokens(heads: int, kv_heads: int) -> int:
+    """Tokens per tile the tensor-core prefill kernel expects."""
+    return _lib.call("tk_attn_prefill_mma_tokens", heads, kv_heads)
+
+
+def _check_attention(q, kv_pool, name):
+    T, H, D = q.shape
+    _, two, Hkv, P, D2 = kv_pool.shape
+    if (two != 2 or D2 != D or kv_pool.dtype != q.dtype or q.dtype != torch.bfloat16
+            or not (q.is_contiguous() and kv_pool.is_contiguous())):
+        raise KernelError(f"{name}: bfloat16 q [T, H, D] and cache [pages, 2, Hkv, P, D] expected")
+    return T, H, D, Hkv, P
+
+
+def attention_prefill_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
+                          positions: torch.Tensor, tok_seq: torch.Tensor,
+                          block_table: torch.Tensor, tile_tok0: torch.Tensor,
+                          tile_ntok: torch.Tensor, window: int | None, scale: float) -> None:
+    """Tensor-core attention for tiles of ``attention_prefill_mma_tokens`` tokens of one
+    sequence; writes the tiles' rows of ``out`` [T, H, D]."""
+    _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
+    T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_mma")
+    _lib.call("tk_attn_prefill_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
+              block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
+              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
+              float(scale), _stream())
+
+
+def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
+                         positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+                         tok_index: torch.Tensor, window: int | None, scale: float,
+                         nsplit: int) -> None:
+    """Tensor-core attention for sequences that bring one token (``tok_index``: their rows in
+    the packed batch), each split ``nsplit`` ways over its keys; partial results go through
+    scratch memory that this function allocates. Writes those rows of ``out`` [T, H, D]."""
+    _cuda(q, kv_pool, out, positions, tok_seq, block_table, tok_index)
+    T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_decode_mma")
+    n = tok_index.numel()
+    scratch = None
+    if nsplit > 1:
+        scratch = torch.empty(n * H * nsplit * (D + 2), dtype=torch.float32, device=q.device)
+    _lib.call("tk_attn_decode_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
+              block_table.stride(0), _ptr(_i32(tok_index, "tok_index")), n, H, Hkv, D, P,
+              int(window or 0), float(scale), int(nsplit), _ptr(scratch), _stream())
 
 
 def conv_min_tile(width: int) -> int:

@@ -30,6 +30,10 @@ _SIGNATURES = {
     "tk_qk_norm_rope_write": [P, L, P, P, P, P, F, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "tk_attn_generic_rows": [],
     "tk_attn_generic": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P],
+    "tk_attn_mma_supported": [I, I, I],
+    "tk_attn_prefill_mma_tokens": [I, I],
+    "tk_attn_prefill_mma": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
+    "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
@@ -69,9 +73,25 @@ def declare(name: str, args: list) -> None:
         fn.argtypes = args
 
 
+_calls = 0
+
+
+def calls() -> int:
+    """How many kernel entry points have been called in this process (each launches one
+    kernel of this library; queries such as ``tk_conv_min_tile`` are not counted)."""
+    return _calls
+
+
+_QUERIES = {"tk_check_device", "tk_built_for", "tk_attn_generic_rows", "tk_conv_min_tile",
+            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens"}
+
+
 def call(name: str, *args) -> int:
     """Call an entry point; a negative return raises ``KernelError`` with the library's message."""
+    global _calls
     fn = getattr(lib(), name)
+    if name not in _QUERIES:
+        _calls += 1
     rc = fn(*args)
     if rc < 0:
         raise KernelError(f"{name}: {lib().tk_last_error().decode()}")

@@ -59,15 +59,42 @@ class Attention:
             qkv, pool if own_kv else None, self.q_norm, self.k_norm if own_kv else None,
             self.eps, self.rope.tables(ctx), ctx.positions, ctx.tok_seq,
             table if own_kv else None, self.heads, own_kv, self.head_dim, ctx.page_size)
-        rows = ops.attention_rows()
-        group = self.heads // self.kv_heads
-        per_tile = max(1, rows // group)
-        _, tok0, _, ntok = ctx.tiles(per_tile)
-        out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
-                            self.window, self.scale)
+        if ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
+            out = self._attend_mma(q, pool, table, ctx)
+        else:
+            rows = ops.attention_rows()
+            group = self.heads // self.kv_heads
+            per_tile = max(1, rows // group)
+            _, tok0, _, ntok = ctx.tiles(per_tile)
+            out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
+                                self.window, self.scale)
         if self.gate is not None:
             ops.head_gate(out, self.gate(x).contiguous(), self.heads, self.head_dim)
         return self.o(out.view(T, self.heads * self.head_dim))
+
+
+    # CTAs the decode kernel should put on the GPU before it stops splitting keys further
+    DECODE_CTAS = 444
+
+    def _attend_mma(self, q, pool, table, ctx: StepContext) -> torch.Tensor:
+        """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
+        over their keys so that a small batch still fills the GPU."""
+        out = torch.empty_like(q)
+        per_tile = ops.attention_prefill_mma_tokens(self.heads, self.kv_heads)
+        _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
+        if tok0.numel():
+            ops.attention_prefill_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok,
+                                      self.window, self.scale)
+        singles = ctx.singles()
+        if singles.numel():
+            longest = ctx.host.longest
+            if self.window is not None:
+                longest = min(longest, self.window)
+            want = -(-self.DECODE_CTAS // (singles.numel() * self.kv_heads))
+            nsplit = max(1, min(want, -(-longest // 128)))
+            ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
+                                     self.window, self.scale, nsplit)
+        return out
 
 
 @register("mixer", "attention")

@@ -81,6 +81,7 @@ class HostLayout:
     seq_ctx: list[int]           # tokens of each sequence already in the cache
     seq_slot: list[int]          # state row of each sequence
     decode_only: bool            # every sequence brings exactly one token
+    longest: int = 0             # upper bound of (cached + new) tokens over the sequences
 
 
 @dataclass
@@ -112,10 +113,16 @@ class StepContext:
     tile_source: object = None
     scratch: dict = field(default_factory=dict)
 
-    def tiles(self, size: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    def tiles(self, size: int, which: str = "all"):
         """Runs of at most ``size`` tokens of one sequence: device int32 arrays
-        ``(seq, first token in the batch, offset in the sequence's portion, tokens)``."""
-        return self.tile_source.tiles(size)
+        ``(seq, first token in the batch, offset in the sequence's portion, tokens)``.
+        ``which``: ``all`` sequences, or only the ``multi``-token ones (prompt portions)."""
+        return self.tile_source.tiles(size, which)
+
+    def singles(self) -> torch.Tensor:
+        """Device int32 indices (into the packed tokens) of the sequences that bring exactly one
+        token (decoded tokens)."""
+        return self.tile_source.singles()
 
 
 @runtime_checkable
