@@ -560,3 +560,34 @@ def test_attention_mma_refuses_other_shapes():
     pool = torch.zeros(2, 2, 1, 8, 24, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="is not taken"):
         ops.attention_decode_mma(q, pool, q.clone(), i32([0]), i32([0]), i32([[1]]), i32([0]), None, 1.0, 1)
+
+
+# ---- skinny matrix product (decode) ---------------------------------------------------------------
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n, k", [(16, 64), (100, 200), (2056, 2048), (300, 8192), (1000, 96)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny(m, n, k, out_dtype):
+    from tokenomos_b200 import ops
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = torch.randn(n, k).to(torch.bfloat16)
+    b = torch.randn(n)
+    assert ops.gemm_skinny_ok(dev(x), dev(w))
+    got = ops.gemm_skinny(dev(x), dev(w), dev(b), out_dtype)
+    close(got, x.double() @ w.double().T + b.double(), out_dtype, f"skinny {m}x{n}x{k}")
+    # a row-strided view of a wider activation, no bias
+    wide = torch.randn(m, k + 24).to(torch.bfloat16)
+    view = dev(wide)[:, 8:8 + k]
+    assert ops.gemm_skinny_ok(view, dev(w))
+    got = ops.gemm_skinny(view, dev(w), None, out_dtype)
+    close(got, wide[:, 8:8 + k].double() @ w.double().T, out_dtype, "skinny strided")
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take():
+    from tokenomos_b200 import ops
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_skinny_ok(x, w)
+    assert not ops.gemm_skinny_ok(x[:4, :60], w[:, :60])
+    with pytest.raises(ops.KernelError, match="at most 16"):
+        ops.gemm_skinny(x, w)

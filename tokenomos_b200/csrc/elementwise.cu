@@ -85,6 +85,113 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, int64_t x_stride,
         y[(size_t)r * width + i] = from_f<T>(round_as<T>(row[i] * rstd) * w[i]);
 }
 
+// Fast path: the row lives in registers as 16-byte vectors (ITEMS per thread), so the kernel
+// makes one trip to memory: read x (and the residual), write the stream, reduce, write y.
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restrict__ residual,
+                       const float* __restrict__ pre_w, float pre_eps, const float* __restrict__ w,
+                       float eps, T* __restrict__ y, T* __restrict__ stream, int width) {
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const T* xr = x + (size_t)r * x_stride;
+    float v[ITEMS][VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * 256 + threadIdx.x) * VEC;
+        if (c < width) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                v[it][k] = to_f<T>(e[k]);
+                ss += v[it][k] * v[it][k];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[it][k] = 0.f;
+        }
+    }
+    if (pre_w != nullptr) {
+        const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + pre_eps);
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int c = (it * 256 + threadIdx.x) * VEC;
+            if (c < width) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k)
+                    v[it][k] = round_as<T>(round_as<T>(v[it][k] * rstd) * pre_w[c + k]);
+            }
+        }
+    }
+    if (residual != nullptr || pre_w != nullptr) {
+        ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int c = (it * 256 + threadIdx.x) * VEC;
+            if (c < width) {
+                if (residual != nullptr) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(residual + (size_t)r * width + c);
+                    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) v[it][k] = round_as<T>(v[it][k] + to_f<T>(e[k]));
+                }
+                uint4 packed;
+                T* e = reinterpret_cast<T*>(&packed);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    ss += v[it][k] * v[it][k];
+                    e[k] = from_f<T>(v[it][k]);
+                }
+                if (stream != nullptr) *reinterpret_cast<uint4*>(stream + (size_t)r * width + c) = packed;
+            }
+        }
+    }
+    if (w == nullptr) return;
+    const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int c = (it * 256 + threadIdx.x) * VEC;
+        if (c < width) {
+            uint4 packed;
+            T* e = reinterpret_cast<T*>(&packed);
+            const float4* wv = reinterpret_cast<const float4*>(w + c);
+#pragma unroll
+            for (int k = 0; k < VEC; k += 4) {
+                const float4 ww = wv[k / 4];
+                e[k] = from_f<T>(round_as<T>(v[it][k] * rstd) * ww.x);
+                e[k + 1] = from_f<T>(round_as<T>(v[it][k + 1] * rstd) * ww.y);
+                e[k + 2] = from_f<T>(round_as<T>(v[it][k + 2] * rstd) * ww.z);
+                e[k + 3] = from_f<T>(round_as<T>(v[it][k + 3] * rstd) * ww.w);
+            }
+            *reinterpret_cast<uint4*>(y + (size_t)r * width + c) = packed;
+        }
+    }
+}
+
+template <typename T>
+static bool launch_add_rmsnorm_vec(const void* x, int64_t x_stride, const void* residual,
+                                   const float* pre_w, float pre_eps, const float* w, float eps,
+                                   void* y, void* stream_out, int rows, int width,
+                                   cudaStream_t stream) {
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = width % VEC == 0 && x_stride % VEC == 0 && (uintptr_t)x % 16 == 0 &&
+                         (uintptr_t)residual % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+                         (uintptr_t)stream_out % 16 == 0 && (uintptr_t)w % 16 == 0;
+    if (!aligned || width > 4 * 256 * VEC) return false;
+    const int items = (width + 256 * VEC - 1) / (256 * VEC);
+#define TK_NORM_VEC(IT)                                                                           \
+    add_rmsnorm_vec_kernel<T, IT><<<rows, 256, 0, stream>>>((const T*)x, x_stride, (const T*)residual, \
+        pre_w, pre_eps, w, eps, (T*)y, (T*)stream_out, width)
+    if (items <= 1) TK_NORM_VEC(1);
+    else if (items == 2) TK_NORM_VEC(2);
+    else TK_NORM_VEC(4);
+#undef TK_NORM_VEC
+    return true;
+}
+
 TK_API int tk_add_rmsnorm(const void* x, int64_t x_stride, const void* residual,
                           const float* pre_w, float pre_eps, const float* w, float eps, void* y,
                           void* stream_out, int rows, int width, int dtype, cudaStream_t stream) {
@@ -95,6 +202,16 @@ TK_API int tk_add_rmsnorm(const void* x, int64_t x_stride, const void* residual,
     if (rows == 0) return 0;
     const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
     const size_t smem = (size_t)width * sizeof(float);
+    if (dtype == TK_F32 && launch_add_rmsnorm_vec<float>(x, x_stride, residual, pre_w, pre_eps, w, eps, y,
+                                                         stream_out, rows, width, stream)) {
+        TK_CHECK_LAUNCH("add_rmsnorm_vec");
+        return 0;
+    }
+    if (dtype == TK_BF16 && launch_add_rmsnorm_vec<__nv_bfloat16>(x, x_stride, residual, pre_w, pre_eps, w,
+                                                                  eps, y, stream_out, rows, width, stream)) {
+        TK_CHECK_LAUNCH("add_rmsnorm_vec");
+        return 0;
+    }
     if (dtype == TK_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<float>,

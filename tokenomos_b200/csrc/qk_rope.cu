@@ -18,6 +18,7 @@ __global__ void qk_norm_rope_write_kernel(
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int head_first = blockIdx.y * nwarp + warp, head_step = gridDim.y * nwarp;
     float* buf = smem + warp * D;
     const int pos = positions[t];
     const int half = R >> 1;
@@ -28,7 +29,7 @@ __global__ void qk_norm_rope_write_kernel(
         cache_row = (size_t)page * 2 * Hkv * P + (pos % P);  // + (kv*Hkv + kh)*P rows
     }
     const T* row = qkv + (size_t)t * qkv_stride;
-    for (int hh = warp; hh < H + 2 * Hkv; hh += nwarp) {
+    for (int hh = head_first; hh < H + 2 * Hkv; hh += head_step) {
         const T* src = row + (size_t)hh * D;
         T* dst;
         const float* w = nullptr;
@@ -91,12 +92,17 @@ TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_ou
     if (T_ == 0) return 0;
     const int threads = 128;
     const size_t smem = (size_t)(threads / 32) * D * sizeof(float);
+    // one warp per head; with few tokens the heads spread over more blocks so the GPU fills
+    const int heads = H + 2 * Hkv;
+    int per_token = (heads + 3) / 4;
+    if ((long long)T_ * per_token > 4096) per_token = 1 > 4096 / T_ ? 1 : 4096 / T_;
+    const dim3 grid(T_, per_token);
     if (dtype == TK_F32)
-        qk_norm_rope_write_kernel<float><<<T_, threads, smem, stream>>>(
+        qk_norm_rope_write_kernel<float><<<grid, threads, smem, stream>>>(
             (const float*)qkv, qkv_stride, (float*)q_out, (float*)kv_pool, wq, wk, eps, inv_freq,
             positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
     else if (dtype == TK_BF16)
-        qk_norm_rope_write_kernel<__nv_bfloat16><<<T_, threads, smem, stream>>>(
+        qk_norm_rope_write_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
             (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_pool, wq,
             wk, eps, inv_freq, positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
     else

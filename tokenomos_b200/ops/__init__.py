@@ -18,7 +18,7 @@ __all__ = [
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "conv_gated", "conv_min_tile",
-    "gemm", "sample",
+    "gemm", "gemm_skinny", "gemm_skinny_ok", "sample",
 ]
 
 
@@ -281,6 +281,32 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     out = torch.empty(M, N, dtype=out_dtype, device=x.device)
     _lib.call("tk_gemm_simt", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
               _ptr(out), N, M, N, K, _dtype_code(x), _dtype_code(out), _stream())
+    return out
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_skinny`` takes this product: bfloat16, at most 16 rows of ``x``, K and the
+    row strides multiples of 8 elements, 16-byte aligned."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
+            and 0 < x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for at most 16 rows of ``x`` (decode): a weight-streaming kernel."""
+    _cuda(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_skinny: x {tuple(x.shape)} against w {tuple(w.shape)}")
+    out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
+    _lib.call("tk_gemm_skinny", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
+              _ptr(out), N, M, N, K, _dtype_code(out), _stream())
     return out
 
 

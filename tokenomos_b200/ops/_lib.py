@@ -37,6 +37,7 @@ _SIGNATURES = {
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
+    "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, P],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
 }
 

@@ -4,9 +4,10 @@ Routes, by storage type:
 
 - float32: the CUDA-core kernel with 32-bit FMA accumulation (``ops.gemm``). No tensor-core or
   reduced-precision mode can reach it, whatever the process-wide torch flags say.
-- bfloat16: the library GEMM (cuBLAS through ``torch.nn.functional.linear``), as the reference
-  engine does for every 16-bit projection (Tokenomos models/blocks/linear.py:236-254), or the
-  hand-written tensor-core kernels when they are switched on and take the shape.
+- bfloat16 with at most 16 rows (decode): the hand-written weight-streaming kernel
+  (``ops.gemm_skinny``); with more rows the library GEMM (cuBLAS through
+  ``torch.nn.functional.linear``), as the reference engine does for every 16-bit projection
+  (Tokenomos models/blocks/linear.py:236-254).
 - a matrix stored in 32-bit in a 16-bit model stays 32-bit: the activation is widened for it.
 
 Several matrices that read the same input are fused along the output axis at build time
@@ -50,6 +51,8 @@ class Linear:
             return ops.gemm(x, w, self.bias, torch.float32)
         if not x.is_cuda:
             raise ops.KernelError("Linear: CUDA tensors only (there is no CPU path)")
+        if ops.gemm_skinny_ok(x, w):
+            return ops.gemm_skinny(x, w, self.bias, out_dtype)
         if out_dtype == torch.float32:
             return self._float_out(x)
         if self.in_features % 8 or (x.stride(0) % 8 and x.shape[0] > 1):
