@@ -591,3 +591,24 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
     assert not ops.gemm_skinny_ok(x[:4, :60], w[:, :60])
     with pytest.raises(ops.KernelError, match="at most 16"):
         ops.gemm_skinny(x, w)
+
+
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("inter, k", [(64, 128), (8192, 2048), (104, 72)])
+def test_gemm_skinny_fused_swiglu_and_interleaved_layout(m, inter, k):
+    """Gate and up rows alternating in runs of 8: the decode kernel's fused epilogue and the
+    stand-alone activation kernel on the same layout agree with the plain formula."""
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.ffn import interleave_rows
+    x = torch.randn(m, k).to(torch.bfloat16)
+    gate = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    w = interleave_rows(gate, up, 8)
+    assert torch.equal(w[:8], gate[:8]) and torch.equal(w[8:16], up[:8]) and torch.equal(w[16:24], gate[8:16])
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    fused = ops.gemm_skinny(dev(x), dev(w), swiglu=True)
+    assert tuple(fused.shape) == (m, inter)
+    close(fused, want, torch.bfloat16, "fused swiglu")
+    unfused = ops.swiglu(ops.gemm_skinny(dev(x), dev(w)), 8)
+    close(unfused, want, torch.bfloat16, "interleaved swiglu kernel")
+    assert (fused.float() - unfused.float()).abs().max().item() <= 0.02 * want.abs().max().item()

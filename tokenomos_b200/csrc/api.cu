@@ -40,3 +40,13 @@ TK_API int tk_check_device() {
     }
     return 0;
 }
+
+static int g_pdl = 1;
+
+bool tk_pdl_enabled() { return g_pdl != 0; }
+
+// 1: kernels are launched with programmatic stream serialization (the default); 0: plain order.
+TK_API int tk_set_pdl(int on) {
+    g_pdl = on ? 1 : 0;
+    return 0;
+}

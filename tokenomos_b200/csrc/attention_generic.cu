@@ -22,11 +22,13 @@ constexpr int MAX_D = 256;   // head sizes up to 256 (accumulator registers: MAX
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
-attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_pool, T* __restrict__ out,
-                    const int* __restrict__ positions, const int* __restrict__ tok_seq,
-                    const int* __restrict__ block_table, int bt_stride,
-                    const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+attn_generic_kernel(const T* q, const T* kv_pool, T* out,
+                    const int* positions, const int* tok_seq,
+                    const int* block_table, int bt_stride,
+                    const int* tile_tok0, const int* tile_ntok, int H,
                     int Hkv, int D, int P, int window, float scale, int heads_per_chunk) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int DP = D + 1;
     float* Qs = smem;                 // [BM][D+1]
@@ -182,12 +184,12 @@ TK_API int tk_attn_generic(const void* q, const void* kv_pool, void* out, const 
     dim3 grid(n_tiles, Hkv * chunks);
     if (dtype == TK_F32) {
         cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
+        tk_launch(attn_generic_kernel<float>, dim3(grid), dim3(THREADS), smem, stream, 
             (const float*)q, (const float*)kv_pool, (float*)out, positions, tok_seq, block_table,
             bt_stride, tile_tok0, tile_ntok, H, Hkv, D, P, window, scale, heads_per_chunk);
     } else if (dtype == TK_BF16) {
         cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
+        tk_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(THREADS), smem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions,
             tok_seq, block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, D, P, window, scale,
             heads_per_chunk);

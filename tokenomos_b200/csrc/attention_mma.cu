@@ -70,8 +70,8 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 // Load `rows` keys (or values) starting at key j0 of sequence `seq` into a swizzled tile with
 // `nthreads` threads; keys outside [j_first, j_last] are zero-filled, not read.
 template <int D>
-__device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
-                                          const int* __restrict__ bt_row, int j0, int rows,
+__device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* pool,
+                                          const int* bt_row, int j0, int rows,
                                           int j_first, int j_last, int kvh, int Hkv, int P, int which,
                                           int tid, int nthreads) {
     constexpr int CH = D / 8;
@@ -193,7 +193,7 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[D / 16][4], uint
 // Query fragments of 16 rows straight from global memory. Row r of the warp is
 // (token tok0 + r / G, head h0 + r % G); rows at or past `rows` read as zero.
 template <int D>
-__device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfloat16* __restrict__ q,
+__device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfloat16* q,
                                        int row0, int rows, int tok0, int G, int H, int h0) {
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -221,12 +221,14 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfl
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(128)
-attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
-                        __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
-                        const int* __restrict__ tok_seq, const int* __restrict__ block_table,
-                        int bt_stride, const int* __restrict__ tile_tok0,
-                        const int* __restrict__ tile_ntok, int H, int Hkv, int P, int window,
+attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
+                        __nv_bfloat16* out, const int* positions,
+                        const int* tok_seq, const int* block_table,
+                        int bt_stride, const int* tile_tok0,
+                        const int* tile_ntok, int H, int Hkv, int P, int window,
                         float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = 64 * D * 2;
     const uint32_t smem = smem_u32(smem_raw);   // [stage][K|V][64][D]
@@ -310,12 +312,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // ---------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(128)
-attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
-                       __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
-                       const int* __restrict__ tok_seq, const int* __restrict__ block_table,
-                       int bt_stride, const int* __restrict__ tok_index, int H, int Hkv, int P,
-                       int window, float scale, int nsplit, float* __restrict__ part_o,
-                       float* __restrict__ part_ml) {
+attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
+                       __nv_bfloat16* out, const int* positions,
+                       const int* tok_seq, const int* block_table,
+                       int bt_stride, const int* tok_index, int H, int Hkv, int P,
+                       int window, float scale, int nsplit, float* part_o,
+                       float* part_ml) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = 32 * D * 2;           // one warp's 32 keys
     const int G = H / Hkv;
@@ -419,11 +423,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 }
 
 template <int D>
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out,
-                                         const int* __restrict__ tok_index, int H, int nsplit,
+__global__ void attn_decode_merge_kernel(const float* part_o,
+                                         const float* part_ml,
+                                         __nv_bfloat16* out,
+                                         const int* tok_index, int H, int nsplit,
                                          float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
     const size_t base = ((size_t)i * H + head) * nsplit;
     const float scale_log2 = scale * LOG2E;
@@ -470,11 +476,11 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
     auto o_ = (__nv_bfloat16*)out;
     if (D == 64) {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_prefill_mma_kernel<64><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table,
+        tk_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
     } else {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_prefill_mma_kernel<128><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table,
+        tk_launch(attn_prefill_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
                                                                   bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
     }
     TK_CHECK_LAUNCH("attn_prefill_mma");
@@ -508,18 +514,18 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
     auto o_ = (__nv_bfloat16*)out;
     if (D == 64) {
         cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_decode_mma_kernel<64><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+        tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            attn_decode_merge_kernel<64><<<dim3(n, H), 64, 0, stream>>>(part_o, part_ml, o_, tok_index, H, nsplit, scale);
+            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
     } else {
         cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_decode_mma_kernel<128><<<grid, 128, smem, stream>>>(q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+        tk_launch(attn_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
                                                                  tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            attn_decode_merge_kernel<128><<<dim3(n, H), 128, 0, stream>>>(part_o, part_ml, o_, tok_index, H, nsplit, scale);
+            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
     }
     TK_CHECK_LAUNCH("attn_decode_merge");
     return 0;

@@ -139,6 +139,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if proc.returncode != 0:
             raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stderr[-4000:]}")
         os.replace(tmp_lib, target)
+        # libraries of earlier source states are dead weight (each is a few MB)
+        for old in target.parent.parent.iterdir():
+            if old.is_dir() and old != target.parent and (old / LIB_NAME).exists():
+                shutil.rmtree(old, ignore_errors=True)
     finally:
         done.set()
         shutil.rmtree(work, ignore_errors=True)

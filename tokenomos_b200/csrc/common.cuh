@@ -90,3 +90,38 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Every kernel of this library is launched so that it may start while the kernel before it in
+// the stream is still running (its blocks are scheduled as soon as the earlier kernel's blocks
+// have all started), and every kernel calls pdl_wait() before it touches anything an earlier
+// kernel may have written and before its own first global write. What a kernel reads that no
+// kernel writes (weights) may be fetched before the wait: a decode step is a chain of ~100
+// short kernels, and this hides their launch latency and overlaps weight streaming with the
+// previous kernel's tail. tk_set_pdl(0) turns it off (plain stream order).
+// One rule follows for the kernels' signatures: only pointers to data that no kernel ever writes
+// (weights) are `const __restrict__`. Anything an earlier kernel produced must be read with
+// ordinary loads after the wait: the compiler turns `const __restrict__` loads into ld.global.nc,
+// and a line the read-only path cached while the producer was still running would be stale.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+bool tk_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t tk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tk_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -14,14 +14,16 @@
 #include "common.cuh"
 
 template <typename T, int W>
-__global__ void conv_gated_kernel(const T* __restrict__ bcx, int64_t stride, int d,
+__global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
                                   const float* __restrict__ w, const float* __restrict__ bias,
-                                  T* __restrict__ state, T* __restrict__ out,
-                                  const int* __restrict__ cu, const int* __restrict__ seq_ctx,
-                                  const int* __restrict__ seq_slot,
-                                  const int* __restrict__ tile_seq,
-                                  const int* __restrict__ tile_off,
-                                  const int* __restrict__ tile_n) {
+                                  T* state, T* out,
+                                  const int* cu, const int* seq_ctx,
+                                  const int* seq_slot,
+                                  const int* tile_seq,
+                                  const int* tile_off,
+                                  const int* tile_n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= d) return;
     const int s = tile_seq[blockIdx.x];
@@ -89,7 +91,7 @@ static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, c
     dim3 grid(n_tiles, (d + threads - 1) / threads);
 #define TK_CONV_CASE(WW)                                                                         \
     case WW:                                                                                     \
-        conv_gated_kernel<T, WW><<<grid, threads, 0, stream>>>(                                  \
+        tk_launch(conv_gated_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,                                   \
             (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,        \
             tile_seq, tile_off, tile_n);                                                         \
         break;

@@ -8,8 +8,10 @@
 // gather: out[r, :] = table[ids[r], :]  (embedding lookup, and row selection before the head)
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                   T* __restrict__ out, int width, int rows_in_table) {
+__global__ void gather_rows_kernel(const T* table, const int* ids,
+                                   T* out, int width, int rows_in_table) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     int id = ids[r];
     // an id outside the table would read foreign memory: clamp (callers validate on the host)
@@ -33,10 +35,10 @@ TK_API int tk_gather_rows(const void* table, const int* ids, void* out, int rows
     if (rows == 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == TK_F32)
-        gather_rows_kernel<float><<<rows, threads, 0, stream>>>((const float*)table, ids, (float*)out,
+        tk_launch(gather_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)table, ids, (float*)out,
                                                                width, rows_in_table);
     else if (dtype == TK_BF16)
-        gather_rows_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(
+        tk_launch(gather_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, width, rows_in_table);
     else
         TK_CHECK_ARG(false, "gather_rows: unknown dtype %d", dtype);
@@ -49,10 +51,12 @@ TK_API int tk_gather_rows(const void* table, const int* ids, void* out, int rows
 // One block per row; the row lives in shared memory as float. `x` may be a strided view.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void add_rmsnorm_kernel(const T* __restrict__ x, int64_t x_stride,
-                                   const T* __restrict__ residual, const float* __restrict__ pre_w,
+__global__ void add_rmsnorm_kernel(const T* x, int64_t x_stride,
+                                   const T* residual, const float* __restrict__ pre_w,
                                    float pre_eps, const float* __restrict__ w, float eps,
-                                   T* __restrict__ y, T* __restrict__ stream, int width) {
+                                   T* y, T* stream, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float row[];
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -89,9 +93,11 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, int64_t x_stride,
 // makes one trip to memory: read x (and the residual), write the stream, reduce, write y.
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(256)
-add_rmsnorm_vec_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restrict__ residual,
+add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
                        const float* __restrict__ pre_w, float pre_eps, const float* __restrict__ w,
-                       float eps, T* __restrict__ y, T* __restrict__ stream, int width) {
+                       float eps, T* y, T* stream, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -183,7 +189,7 @@ static bool launch_add_rmsnorm_vec(const void* x, int64_t x_stride, const void* 
     if (!aligned || width > 4 * 256 * VEC) return false;
     const int items = (width + 256 * VEC - 1) / (256 * VEC);
 #define TK_NORM_VEC(IT)                                                                           \
-    add_rmsnorm_vec_kernel<T, IT><<<rows, 256, 0, stream>>>((const T*)x, x_stride, (const T*)residual, \
+    tk_launch(add_rmsnorm_vec_kernel<T, IT>, dim3(rows), dim3(256), 0, stream, (const T*)x, x_stride, (const T*)residual, \
         pre_w, pre_eps, w, eps, (T*)y, (T*)stream_out, width)
     if (items <= 1) TK_NORM_VEC(1);
     else if (items == 2) TK_NORM_VEC(2);
@@ -216,14 +222,14 @@ TK_API int tk_add_rmsnorm(const void* x, int64_t x_stride, const void* residual,
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<rows, threads, smem, stream>>>(
+        tk_launch(add_rmsnorm_kernel<float>, dim3(rows), dim3(threads), smem, stream, 
             (const float*)x, x_stride, (const float*)residual, pre_w, pre_eps, w, eps, (float*)y,
             (float*)stream_out, width);
     } else if (dtype == TK_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>(
+        tk_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream, 
             (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)residual, pre_w, pre_eps, w, eps,
             (__nv_bfloat16*)y, (__nv_bfloat16*)stream_out, width);
     } else {
@@ -236,34 +242,42 @@ TK_API int tk_add_rmsnorm(const void* x, int64_t x_stride, const void* residual,
 // ---------------------------------------------------------------------------------------------
 // SwiGLU: out[t, i] = round(round(silu(g[t, i])) * u[t, i]) with gu = [g | u] of width 2*inter
 // ---------------------------------------------------------------------------------------------
+// block == 0: gu = [gate (inter) | up (inter)]; block > 0: gate and up alternate in runs of `block`
+// channels (the layout the decode kernel's fused epilogue wants of the weight rows).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total,
-                              int inter) {
+__global__ void swiglu_kernel(const T* gu, T* out, int64_t total,
+                              int inter, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (; i < total; i += step) {
         const int64_t t = i / inter;
         const int c = (int)(i - t * inter);
-        const float g = to_f<T>(gu[t * 2 * inter + c]);
-        const float u = to_f<T>(gu[t * 2 * inter + inter + c]);
+        const int gi = block > 0 ? (c / block) * 2 * block + c % block : c;
+        const int ui = block > 0 ? gi + block : inter + c;
+        const float g = to_f<T>(gu[t * 2 * inter + gi]);
+        const float u = to_f<T>(gu[t * 2 * inter + ui]);
         const float s = round_as<T>(g / (1.0f + expf(-g)));
         out[i] = from_f<T>(s * u);
     }
 }
 
-TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int dtype,
+TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int block, int dtype,
                      cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    TK_CHECK_ARG(block >= 0 && (block == 0 || inter % block == 0), "swiglu: runs of %d channels do not "
+                 "divide %d", block, inter);
     if (rows == 0) return 0;
     const int64_t total = (int64_t)rows * inter;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                         : 148 * 16);
     if (dtype == TK_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+        tk_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inter, block);
     else if (dtype == TK_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+        tk_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter, block);
     else
         TK_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
     TK_CHECK_LAUNCH("swiglu");
@@ -274,8 +288,10 @@ TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int dtype,
 // per-head sigmoid gate: x[t, h, :] = round(x[t, h, :] * round(sigmoid(g[t, h])))
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int64_t total,
+__global__ void head_gate_kernel(T* x, const T* g, int64_t total,
                                  int head_dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (; i < total; i += step) {
@@ -294,9 +310,9 @@ TK_API int tk_head_gate(void* x, const void* g, int rows, int heads, int head_di
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                         : 148 * 16);
     if (dtype == TK_F32)
-        head_gate_kernel<float><<<blocks, threads, 0, stream>>>((float*)x, (const float*)g, total, head_dim);
+        tk_launch(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, (const float*)g, total, head_dim);
     else if (dtype == TK_BF16)
-        head_gate_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        tk_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             (__nv_bfloat16*)x, (const __nv_bfloat16*)g, total, head_dim);
     else
         TK_CHECK_ARG(false, "head_gate: unknown dtype %d", dtype);

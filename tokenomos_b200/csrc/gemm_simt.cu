@@ -10,9 +10,11 @@ constexpr int TM = 64, TN = 64, TK = 16, GEMM_THREADS = 256;
 
 template <typename TA, typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS)
-gemm_simt_kernel(const TA* __restrict__ A, int64_t lda, const TA* __restrict__ W, int64_t ldw,
-                 const float* __restrict__ bias, TO* __restrict__ C, int64_t ldc, int M, int N,
+gemm_simt_kernel(const TA* A, int64_t lda, const TA* __restrict__ W, int64_t ldw,
+                 const float* __restrict__ bias, TO* C, int64_t ldc, int M, int N,
                  int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[TK][TM + 4];
     __shared__ float Ws[TK][TN + 4];
     const int tid = threadIdx.x;
@@ -74,14 +76,14 @@ TK_API int tk_gemm_simt(const void* A, int64_t lda, const void* W, int64_t ldw, 
     if (M == 0) return 0;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (in_dtype == TK_F32 && out_dtype == TK_F32)
-        gemm_simt_kernel<float, float><<<grid, GEMM_THREADS, 0, stream>>>(
+        tk_launch(gemm_simt_kernel<float, float>, dim3(grid), dim3(GEMM_THREADS), 0, stream, 
             (const float*)A, lda, (const float*)W, ldw, bias, (float*)C, ldc, M, N, K);
     else if (in_dtype == TK_BF16 && out_dtype == TK_BF16)
-        gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, GEMM_THREADS, 0, stream>>>(
+        tk_launch(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(GEMM_THREADS), 0, stream, 
             (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias, (__nv_bfloat16*)C, ldc,
             M, N, K);
     else if (in_dtype == TK_BF16 && out_dtype == TK_F32)
-        gemm_simt_kernel<__nv_bfloat16, float><<<grid, GEMM_THREADS, 0, stream>>>(
+        tk_launch(gemm_simt_kernel<__nv_bfloat16, float>, dim3(grid), dim3(GEMM_THREADS), 0, stream, 
             (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias, (float*)C, ldc, M, N, K);
     else
         TK_CHECK_ARG(false, "gemm_simt: dtype pair (%d, %d) is not built", in_dtype, out_dtype);

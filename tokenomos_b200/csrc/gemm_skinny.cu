@@ -31,27 +31,40 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-__device__ __forceinline__ uint4 ldg_cached(const void* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
+// Activations are written by the kernel before this one, which may still be running when this
+// kernel's blocks become resident: they must not go through the read-only (.nc) path, whose
+// lines are not refreshed by griddepcontrol.wait.
+__device__ __forceinline__ uint4 ld_activation(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
 }
 
 constexpr int ROWS = 16;     // weight rows per CTA
 constexpr int KSLICE = 64;   // K elements a warp takes per iteration (128 bytes of each row)
 constexpr int UNROLL = 4;    // slices whose loads are in flight together
 
-// MT: 8 or 16 tokens (one or two n8 tiles)
-template <int MT, typename TO>
+// MT: 8 or 16 tokens (one or two n8 tiles). R8: the CTA owns 8 weight rows instead of 16 (the
+// upper half of the mma tile stays zero): twice as many CTAs for matrices with few rows.
+// SWIGLU: the weight rows come in blocks of 16, 8 gate rows then the 8 up rows of the same
+// channels, and the CTA writes silu(gate) * up for its 8 channels: out is [M, N / 2].
+template <int MT, typename TO, bool R8, bool SWIGLU>
 __global__ void __launch_bounds__(512)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
+gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                    const __nv_bfloat16* __restrict__ w, int64_t ldw, const float* __restrict__ bias,
-                   TO* __restrict__ out, int64_t ldo, int M, int N, int K) {
+                   TO* out, int64_t ldo, int M, int N, int K) {
     extern __shared__ float red[];                 // [warps][ROWS][MT]
+    pdl_launch_dependents();
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
+    constexpr int CTA_ROWS = R8 ? 8 : ROWS;
+    const int n0 = blockIdx.x * CTA_ROWS;
     const int r0 = n0 + g, r1 = n0 + g + 8;
-    const bool r0_ok = r0 < N, r1_ok = r1 < N;
+    const bool r0_ok = r0 < N, r1_ok = !R8 && r1 < N;
     const __nv_bfloat16* w0 = w + (size_t)(r0_ok ? r0 : 0) * ldw;
     const __nv_bfloat16* w1 = w + (size_t)(r1_ok ? r1 : 0) * ldw;
     constexpr int TG = MT / 8;
@@ -71,6 +84,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int slices = (K + KSLICE - 1) / KSLICE;
+    bool waited = false;
     for (int s0 = warp; s0 < slices; s0 += warps * UNROLL) {
         uint4 wa[UNROLL][2], wb[UNROLL][2];
 #pragma unroll
@@ -84,6 +98,12 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
                 wb[u][h] = (ok && r1_ok) ? ldg_stream(w1 + k) : zero;
             }
         }
+        // the weights do not depend on the kernel before this one: their loads are in flight
+        // while it finishes; the activations do, so wait before the first of them
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int s = s0 + u * warps;
@@ -93,7 +113,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
                 const bool ok = s < slices && k < K;
 #pragma unroll
                 for (int i = 0; i < TG; ++i) {
-                    const uint4 xv = (ok && x_ok[i]) ? ldg_cached(xr[i] + k) : zero;
+                    const uint4 xv = (ok && x_ok[i]) ? ld_activation(xr[i] + k) : zero;
                     // elements 0..3 of the 16 bytes are one mma step, 4..7 the next
                     mma16816(acc[i], wa[u][h].x, wb[u][h].x, wa[u][h].y, wb[u][h].y, xv.x, xv.y);
                     mma16816(acc[i], wa[u][h].z, wb[u][h].z, wa[u][h].w, wb[u][h].w, xv.z, xv.w);
@@ -101,6 +121,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
             }
         }
     }
+    if (!waited) pdl_wait();
     // acc[i]: rows g / g + 8, tokens 8 i + 2 t, + 1
 #pragma unroll
     for (int i = 0; i < TG; ++i) {
@@ -111,13 +132,34 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
         dst[(g + 8) * MT + 8 * i + 2 * t + 1] = acc[i][3];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < ROWS * MT; idx += blockDim.x) {
-        const int tok = idx / ROWS, r = idx % ROWS;      // rows fastest: neighbours in memory
-        if (tok >= M || n0 + r >= N) continue;
-        float v = 0.f;
-        for (int wv = 0; wv < warps; ++wv) v += red[(size_t)wv * ROWS * MT + r * MT + tok];
-        if (bias != nullptr) v += bias[n0 + r];
-        out[(size_t)tok * ldo + n0 + r] = from_f<TO>(v);
+    if constexpr (SWIGLU) {
+        for (int idx = threadIdx.x; idx < 8 * MT; idx += blockDim.x) {
+            const int tok = idx / 8, j = idx % 8;
+            if (tok >= M || n0 + 8 + j >= N) continue;
+            float gate = 0.f, up = 0.f;
+            for (int wv = 0; wv < warps; ++wv) {
+                gate += red[(size_t)wv * ROWS * MT + j * MT + tok];
+                up += red[(size_t)wv * ROWS * MT + (j + 8) * MT + tok];
+            }
+            if (bias != nullptr) {
+                gate += bias[n0 + j];
+                up += bias[n0 + 8 + j];
+            }
+            // the unfused path stores gate and up in the output type, then rounds silu(gate)
+            gate = round_as<TO>(gate);
+            up = round_as<TO>(up);
+            const float act = round_as<TO>(gate / (1.0f + expf(-gate)));
+            out[(size_t)tok * ldo + n0 / 2 + j] = from_f<TO>(act * up);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < CTA_ROWS * MT; idx += blockDim.x) {
+            const int tok = idx / CTA_ROWS, r = idx % CTA_ROWS;   // rows fastest: neighbours in memory
+            if (tok >= M || n0 + r >= N) continue;
+            float v = 0.f;
+            for (int wv = 0; wv < warps; ++wv) v += red[(size_t)wv * ROWS * MT + r * MT + tok];
+            if (bias != nullptr) v += bias[n0 + r];
+            out[(size_t)tok * ldo + n0 + r] = from_f<TO>(v);
+        }
     }
 }
 
@@ -125,32 +167,41 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
 
 // x: [M, K] bfloat16, rows `ldx` apart; w: [N, K] bfloat16, rows `ldw` apart; out: [M, N]
 // bfloat16 or float (out_dtype); M <= 16; K, ldx, ldw multiples of 8 and 16-byte aligned bases.
+// swiglu != 0: w holds blocks of 8 gate rows followed by the 8 up rows of the same channels
+// (N a multiple of 16) and out is [M, N / 2] = silu(gate) * up.
 TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
-                          void* out, int64_t ldo, int M, int N, int K, int out_dtype,
+                          void* out, int64_t ldo, int M, int N, int K, int out_dtype, int swiglu,
                           cudaStream_t stream) {
     TK_CHECK_ARG(M >= 0 && M <= 16 && N > 0 && K > 0, "gemm_skinny: M=%d (at most 16) N=%d K=%d", M, N, K);
     TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_skinny: K and the leading dimensions "
                  "must be multiples of 8 (K=%d)", K);
     TK_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_skinny: operands must be 16-byte aligned");
+    TK_CHECK_ARG(!swiglu || N % 16 == 0, "gemm_skinny: the fused SwiGLU needs N (%d) in blocks of 16", N);
     if (M == 0) return 0;
     const int slices = (K + KSLICE - 1) / KSLICE;
     int warps = (slices + UNROLL - 1) / UNROLL;      // every slice of a warp in flight at once
     warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
     const int threads = warps * 32;
-    const int blocks = (N + ROWS - 1) / ROWS;
+    // few rows: 8 per CTA so that the grid still covers the GPU
+    const bool r8 = !swiglu && (N + ROWS - 1) / ROWS < 296;
+    const int blocks = r8 ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
     const int MT = M <= 8 ? 8 : 16;
     const size_t smem = (size_t)warps * ROWS * MT * sizeof(float);
     auto x_ = (const __nv_bfloat16*)x;
     auto w_ = (const __nv_bfloat16*)w;
-#define TK_SKINNY(MT_, TO_)                                                                         \
-    gemm_skinny_kernel<MT_, TO_><<<blocks, threads, smem, stream>>>(x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K)
-    if (out_dtype == TK_BF16) {
-        if (MT == 8) TK_SKINNY(8, __nv_bfloat16); else TK_SKINNY(16, __nv_bfloat16);
-    } else if (out_dtype == TK_F32) {
-        if (MT == 8) TK_SKINNY(8, float); else TK_SKINNY(16, float);
-    } else {
-        TK_CHECK_ARG(false, "gemm_skinny: output dtype %d", out_dtype);
-    }
+#define TK_SKINNY(MT_, TO_, R8_, SW_)                                                              \
+    tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_>, dim3(blocks), dim3(threads), smem, stream, x_, ldx, \
+              w_, ldw, bias, (TO_*)out, ldo, M, N, K)
+#define TK_SKINNY_T(TO_)                                                                           \
+    do {                                                                                           \
+        if (swiglu) { if (MT == 8) TK_SKINNY(8, TO_, false, true); else TK_SKINNY(16, TO_, false, true); } \
+        else if (r8) { if (MT == 8) TK_SKINNY(8, TO_, true, false); else TK_SKINNY(16, TO_, true, false); } \
+        else { if (MT == 8) TK_SKINNY(8, TO_, false, false); else TK_SKINNY(16, TO_, false, false); }  \
+    } while (0)
+    if (out_dtype == TK_BF16) TK_SKINNY_T(__nv_bfloat16);
+    else if (out_dtype == TK_F32) TK_SKINNY_T(float);
+    else TK_CHECK_ARG(false, "gemm_skinny: output dtype %d", out_dtype);
+#undef TK_SKINNY_T
 #undef TK_SKINNY
     TK_CHECK_LAUNCH("gemm_skinny");
     return 0;

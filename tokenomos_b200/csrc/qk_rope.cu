@@ -10,11 +10,13 @@
 
 template <typename T>
 __global__ void qk_norm_rope_write_kernel(
-    const T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ q_out, T* __restrict__ kv_pool,
+    const T* qkv, int64_t qkv_stride, T* q_out, T* kv_pool,
     const float* __restrict__ wq, const float* __restrict__ wk, float eps,
-    const float* __restrict__ inv_freq, const int* __restrict__ positions,
-    const int* __restrict__ tok_seq, const int* __restrict__ block_table, int bt_stride, int H,
+    const float* __restrict__ inv_freq, const int* positions,
+    const int* tok_seq, const int* block_table, int bt_stride, int H,
     int Hkv, int D, int R, int P) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -98,11 +100,11 @@ TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_ou
     if ((long long)T_ * per_token > 4096) per_token = 1 > 4096 / T_ ? 1 : 4096 / T_;
     const dim3 grid(T_, per_token);
     if (dtype == TK_F32)
-        qk_norm_rope_write_kernel<float><<<grid, threads, smem, stream>>>(
+        tk_launch(qk_norm_rope_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, 
             (const float*)qkv, qkv_stride, (float*)q_out, (float*)kv_pool, wq, wk, eps, inv_freq,
             positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
     else if (dtype == TK_BF16)
-        qk_norm_rope_write_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
+        tk_launch(qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), smem, stream, 
             (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_pool, wq,
             wk, eps, inv_freq, positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P);
     else

@@ -87,10 +87,12 @@ __device__ void mass_count(const float* row, int V, float inv_t, float top, floa
 }  // namespace
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, int64_t stride, int V, const float* __restrict__ temp,
-              const float* __restrict__ top_p, const int* __restrict__ top_k,
-              const float* __restrict__ min_p, const int* __restrict__ seed,
-              const int* __restrict__ step, int* __restrict__ out) {
+sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
+              const float* top_p, const int* top_k,
+              const float* min_p, const int* seed,
+              const int* step, int* out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ Best bred[33];
     __shared__ float fred[33];
     const int r = blockIdx.x;
@@ -153,7 +155,7 @@ TK_API int tk_sample(const float* logits, int64_t stride, int rows, int V, const
                      const int* step, int* out, cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && V > 0 && stride >= V, "sample: bad sizes rows=%d V=%d", rows, V);
     if (rows == 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, V, temp, top_p, top_k, min_p,
+    tk_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, V, temp, top_p, top_k, min_p,
                                                        seed, step, out);
     TK_CHECK_LAUNCH("sample");
     return 0;

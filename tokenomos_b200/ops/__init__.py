@@ -104,14 +104,15 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Te
     return y, stream
 
 
-def swiglu(gu: torch.Tensor) -> torch.Tensor:
-    """``silu(gu[:, :I]) * gu[:, I:]`` for ``gu`` of width ``2 I``."""
+def swiglu(gu: torch.Tensor, block: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gu`` of width ``2 I``: ``gu = [gate | up]`` (``block`` 0), or gate
+    and up alternating in runs of ``block`` channels."""
     _cuda(gu)
     if not gu.is_contiguous() or gu.shape[1] % 2:
         raise KernelError("swiglu: input must be contiguous with an even width")
     rows, inter = gu.shape[0], gu.shape[1] // 2
     out = torch.empty(rows, inter, dtype=gu.dtype, device=gu.device)
-    _lib.call("tk_swiglu", _ptr(gu), _ptr(out), rows, inter, _dtype_code(gu), _stream())
+    _lib.call("tk_swiglu", _ptr(gu), _ptr(out), rows, inter, int(block), _dtype_code(gu), _stream())
     return out
 
 
@@ -297,16 +298,19 @@ def gemm_skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-                out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x @ w.T (+ bias)`` for at most 16 rows of ``x`` (decode): a weight-streaming kernel."""
+                out_dtype: torch.dtype | None = None, swiglu: bool = False) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for at most 16 rows of ``x`` (decode): a weight-streaming kernel.
+    ``swiglu``: the rows of ``w`` alternate in runs of 8 (8 gate rows, the 8 up rows of the same
+    channels) and the result is ``silu(gate) * up`` of width ``N / 2``."""
     _cuda(x, w, bias)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)} against w {tuple(w.shape)}")
-    out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
+    width = N // 2 if swiglu else N
+    out = torch.empty(M, width, dtype=out_dtype or x.dtype, device=x.device)
     _lib.call("tk_gemm_skinny", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
-              _ptr(out), N, M, N, K, _dtype_code(out), _stream())
+              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), _stream())
     return out
 
 

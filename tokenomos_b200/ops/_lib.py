@@ -8,6 +8,7 @@ behind them: if the library cannot be built or loaded, the import of an op raise
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
@@ -23,9 +24,10 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 _SIGNATURES = {
     "tk_check_device": [],
     "tk_built_for": [],
+    "tk_set_pdl": [I],
     "tk_gather_rows": [P, P, P, I, I, I, I, P],
     "tk_add_rmsnorm": [P, L, P, P, F, P, F, P, P, I, I, I, P],
-    "tk_swiglu": [P, P, I, I, I, P],
+    "tk_swiglu": [P, P, I, I, I, I, P],
     "tk_head_gate": [P, P, I, I, I, I, P],
     "tk_qk_norm_rope_write": [P, L, P, P, P, P, F, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "tk_attn_generic_rows": [],
@@ -37,7 +39,7 @@ _SIGNATURES = {
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
-    "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, P],
+    "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
 }
 
@@ -61,6 +63,8 @@ def lib() -> ctypes.CDLL:
                 fn = getattr(loaded, name)
                 fn.restype = c_int
                 fn.argtypes = args
+            if os.environ.get("TOKENOMOS_B200_PDL", "1") == "0":
+                loaded.tk_set_pdl(0)
             _lib = loaded
     return _lib
 
@@ -83,7 +87,7 @@ def calls() -> int:
     return _calls
 
 
-_QUERIES = {"tk_check_device", "tk_built_for", "tk_attn_generic_rows", "tk_conv_min_tile",
+_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens"}
 
 

@@ -73,8 +73,11 @@ class Attention:
         return self.o(out.view(T, self.heads * self.head_dim))
 
 
-    # CTAs the decode kernel should put on the GPU before it stops splitting keys further
-    DECODE_CTAS = 444
+    # CTAs the decode kernel should put on the GPU before it stops splitting keys further: three
+    # fit on an SM (shared memory), and several waves of them even out the last, partial wave
+    DECODE_CTAS = 4 * 444
+    # fewest keys worth a CTA of their own
+    DECODE_MIN_KEYS = 256
 
     def _attend_mma(self, q, pool, table, ctx: StepContext) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
@@ -91,7 +94,7 @@ class Attention:
             if self.window is not None:
                 longest = min(longest, self.window)
             want = -(-self.DECODE_CTAS // (singles.numel() * self.kv_heads))
-            nsplit = max(1, min(want, -(-longest // 128)))
+            nsplit = max(1, min(want, -(-longest // self.DECODE_MIN_KEYS)))
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
                                      self.window, self.scale, nsplit)
         return out

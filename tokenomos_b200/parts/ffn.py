@@ -10,16 +10,39 @@ from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import Runtime, register
 
 
+# channels per run when gate and up rows alternate (what the decode kernel's epilogue pairs up)
+RUN = 8
+
+
 class SwiGLU:
-    def __init__(self, gate_up: Linear, down: Linear):
+    def __init__(self, gate_up: Linear, down: Linear, run: int = 0):
+        """``run`` 0: ``gate_up``'s rows are all gate rows, then all up rows. ``run`` 8: they
+        alternate in runs of 8 channels, so that a decode CTA that owns 16 rows holds gate and up
+        of the same 8 channels and can apply the activation in its epilogue."""
         if gate_up.out_features != 2 * down.in_features:
             raise ValueError("SwiGLU: gate_up must be twice as wide as down's input")
-        self.gate_up, self.down = gate_up, down
+        self.gate_up, self.down, self.run = gate_up, down, run
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down(ops.swiglu(self.gate_up(x)))
+        w = self.gate_up.weight
+        if self.run == RUN and ops.gemm_skinny_ok(x, w):
+            act = ops.gemm_skinny(x, w, self.gate_up.bias, swiglu=True)
+        else:
+            act = ops.swiglu(self.gate_up(x), self.run)
+        return self.down(act)
+
+
+def interleave_rows(gate: torch.Tensor, up: torch.Tensor, run: int) -> torch.Tensor:
+    """[I, K] gate and up -> [2 I, K] with ``run`` gate rows, the ``run`` up rows of the same
+    channels, and so on."""
+    inter, k = gate.shape
+    both = torch.stack((gate.view(inter // run, run, k), up.view(inter // run, run, k)), dim=1)
+    return both.reshape(2 * inter, k).contiguous()
 
 
 @register("feed_forward", "swiglu")
 def build_swiglu(params: dict, tensors: dict, rt: Runtime) -> SwiGLU:
-    return SwiGLU(Linear.fused([tensors["gate"], tensors["up"]]), Linear(tensors["down"]))
+    gate, up = tensors["gate"], tensors["up"]
+    if gate.dtype == torch.bfloat16 and gate.shape[0] % RUN == 0:
+        return SwiGLU(Linear(interleave_rows(gate, up, RUN)), Linear(tensors["down"]), RUN)
+    return SwiGLU(Linear.fused([gate, up]), Linear(tensors["down"]))
