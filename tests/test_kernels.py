@@ -565,7 +565,7 @@ def test_attention_mma_refuses_other_shapes():
 # ---- skinny matrix product (decode) ---------------------------------------------------------------
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n, k", [(16, 64), (100, 200), (2056, 2048), (300, 8192), (1000, 96)])
+@pytest.mark.parametrize("n, k", [(16, 64), (100, 200), (2056, 2048), (300, 8192), (1000, 96), (6144, 2048), (20000, 512)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_skinny(m, n, k, out_dtype):
     from tokenomos_b200 import ops

@@ -1,0 +1,446 @@
+// Tensor-core matrix product for sm_100a: TMA (cp.async.bulk.tensor) stages both operands in
+// shared memory behind mbarriers, one thread issues tcgen05.mma (UMMA, 128 x BN x 16, bfloat16 in,
+// 32-bit accumulator in tensor memory), four warps read the accumulator back with tcgen05.ld for
+// the epilogue.
+//
+//   D[i, j] = sum_k A[i, k] * B[j, k]        A: [rows_a, K], B: [rows_b, K], both K-major bf16
+//
+// Decode ("weights as A"): A = W [N, K], B = x [tokens, K]; the 128-row MMA tile is filled with
+// weight rows and the few tokens are the MMA's N (16..256), so no tensor-core row is wasted on
+// padding the batch; D is stored transposed into out[token, n]. Matrices with few rows are split
+// along K over several CTAs; partial tiles are added into a zeroed 32-bit scratch with
+// red.global.add and the last CTA of a tile (a counter decides) applies the epilogue, writes the
+// 16-bit result and zeroes its scratch entries and counter again, so one kernel does it all.
+// Prefill ("tokens as A"): A = x, B = W, D is stored as it is.
+//
+// Warp roles in a CTA of 192 threads: warp 0 produces (one lane issues TMA), warp 1 allocates
+// tensor memory and issues the MMAs, warps 2..5 are the epilogue (warp w may touch TMEM lanes
+// 32 (w % 4) .. +31). In decode the weight tiles of the first stages are requested before
+// griddepcontrol.wait: they stream while the kernel that produces x is still running.
+//
+// Every wait on an mbarrier is bounded: after about a second the kernel records where it gave
+// up in an error word, skips the rest of its work, frees its tensor memory and returns; the
+// host reads the word through tk_gemm_tc_status().
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows of A per tile (UMMA M)
+constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle atom wide
+constexpr int TC_THREADS = 192;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+
+__device__ int g_tc_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Bounded wait: false (and an error code recorded) if the phase did not complete in ~1 s.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int where) {
+    const long long start = clock64();
+    while (true) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (clock64() - start > 2000000000LL) {
+            atomicCAS(&g_tc_error, 0, where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (the tile base is 1024-byte aligned).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused here)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32, 46)
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// TRANSPOSED: D[i, j] -> out[j, i] (decode, weights as A); otherwise out[i, j] (tokens as A).
+// SWIGLU (decode only): rows of A come in blocks of 16, 8 gate rows then the 8 up rows of the
+// same channels; out[j, c] = silu(gate) * up, out width rows_a / 2.
+template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               TO* out, int64_t ldo, const float* __restrict__ bias, int rows_a, int rows_b, int K,
+               int stages, int splitk, float* scratch, int* counters) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int B_TILE_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + (uint32_t)stages * STAGE_BYTES;   // full[s], empty[s], tmem_full
+    const uint32_t tmem_slot = bars + (2 * stages + 1) * 8;
+    auto full_bar = [&](int s) { return bars + (uint32_t)s * 8; };
+    auto empty_bar = [&](int s) { return bars + (uint32_t)(stages + s) * 8; };
+    const uint32_t tmem_full_bar = bars + (uint32_t)(2 * stages) * 8;
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a_row0 = blockIdx.x * BM, b_row0 = blockIdx.y * BN;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_per = (kb_total + splitk - 1) / splitk;
+    const int kb_begin = blockIdx.z * kb_per;
+    const int kb_end = min(kb_total, kb_begin + kb_per);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---- producer ----
+        if (lane == 0 && n_kb > 0) {
+            int first = 0;
+            if (TRANSPOSED) {
+                // weights first: they do not depend on the kernel before this one
+                first = min(stages, n_kb);
+                for (int i = 0; i < first; ++i) {
+                    mbar_expect_tx(full_bar(i), STAGE_BYTES);
+                    tma_load_2d(smem_base + (uint32_t)i * STAGE_BYTES, &tmap_a, (kb_begin + i) * BK, a_row0,
+                                full_bar(i));
+                }
+                pdl_wait();
+                for (int i = 0; i < first; ++i)
+                    tma_load_2d(smem_base + (uint32_t)i * STAGE_BYTES + A_TILE_BYTES, &tmap_b,
+                                (kb_begin + i) * BK, b_row0, full_bar(i));
+            } else {
+                pdl_wait();
+            }
+            for (int i = first; i < n_kb && ok; ++i) {
+                const int s = i % stages;
+                const uint32_t parity = ((i / stages) & 1) ^ 1;
+                ok = mbar_wait(empty_bar(s), parity, 1);
+                if (!ok) break;
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                const uint32_t dst = smem_base + (uint32_t)s * STAGE_BYTES;
+                tma_load_2d(dst, &tmap_a, (kb_begin + i) * BK, a_row0, full_bar(s));
+                tma_load_2d(dst + A_TILE_BYTES, &tmap_b, (kb_begin + i) * BK, b_row0, full_bar(s));
+            }
+        } else if (lane == 0) {
+            pdl_wait();
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BN);
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % stages;
+                ok = mbar_wait(full_bar(s), (i / stages) & 1, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_base + (uint32_t)s * STAGE_BYTES;
+                const uint64_t adesc = umma_desc(a_addr), bdesc = umma_desc(a_addr + A_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)     // 32 bytes further along K per step
+                    umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty_bar(s));            // the stage is free once these MMAs are done
+            }
+            umma_commit(tmem_full_bar);
+        }
+    } else {
+        // ---- epilogue: warps 2..5, TMEM lanes 32 (warp % 4) .. +31 ----
+        pdl_wait();
+        const int lane_group = warp & 3;
+        const int epi_tid = (warp - 2) * 32 + lane;
+        __shared__ int s_last;
+        ok = n_kb > 0 ? mbar_wait(tmem_full_bar, 0, 3) : true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int i_row = a_row0 + lane_group * 32 + lane;          // row of A / D
+        const bool row_ok = i_row < rows_a;
+        float bias_i = 0.f;
+        if (TRANSPOSED && bias != nullptr && row_ok) bias_i = bias[i_row];
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        // the scratch is [rows_b][rows_a] (decode) or [rows_a][rows_b] floats, zero between calls
+        auto scratch_at = [&](int jj) -> float* {
+            return TRANSPOSED ? scratch + (size_t)jj * rows_a + i_row : scratch + (size_t)i_row * rows_b + jj;
+        };
+        // columns c .. c + 15 of this thread's row, finished: bias, activation, store
+        auto finalize = [&](int c, float (&part)[16]) {
+            if (TRANSPOSED && SWIGLU) {
+                const bool is_gate = (i_row & 15) < 8;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float mine = round_as<TO>(part[e] + bias_i);
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);       // gate <-> up
+                    const int jj = b_row0 + c + e;
+                    if (is_gate && row_ok && i_row + 8 < rows_a && jj < rows_b) {
+                        const float act = round_as<TO>(mine / (1.0f + expf(-mine)));
+                        out[(size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7)] = from_f<TO>(act * other);
+                    }
+                }
+            } else if (TRANSPOSED) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int jj = b_row0 + c + e;
+                    if (row_ok && jj < rows_b) out[(size_t)jj * ldo + i_row] = from_f<TO>(part[e] + bias_i);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int jj = b_row0 + c + e;
+                    if (row_ok && jj < rows_b)
+                        out[(size_t)i_row * ldo + jj] = from_f<TO>(part[e] + (bias != nullptr ? bias[jj] : 0.f));
+                }
+            }
+        };
+        const bool have = ok && n_kb > 0;
+        if (splitk == 1) {
+            for (int c = 0; c < BN; c += 16) {
+                float part[16];
+                if (have) {
+                    tmem_ld16(tmem_d + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c, part);
+                    finalize(c, part);
+                }
+            }
+        } else {
+            // partial sums into the scratch; the tile's last CTA (a counter decides) finishes it
+            for (int c = 0; c < BN; c += 16) {
+                float part[16];
+                if (have) {
+                    tmem_ld16(tmem_d + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c, part);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int jj = b_row0 + c + e;
+                        if (row_ok && jj < rows_b) atomicAdd(scratch_at(jj), part[e]);
+                    }
+                }
+            }
+            __threadfence();
+            epi_bar_sync();
+            if (epi_tid == 0) s_last = atomicAdd(&counters[tile_id], 1) == splitk - 1;
+            epi_bar_sync();
+            if (s_last != 0) {
+                __threadfence();
+                for (int c = 0; c < BN; c += 16) {
+                    float part[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int jj = b_row0 + c + e;
+                        part[e] = 0.f;
+                        if (row_ok && jj < rows_b) {
+                            part[e] = __ldcg(scratch_at(jj));
+                            __stcg(scratch_at(jj), 0.f);     // leave the scratch zero for the next call
+                        }
+                    }
+                    finalize(c, part);
+                }
+                if (epi_tid == 0) counters[tile_id] = 0;
+            }
+        }
+    }
+    // ---- teardown: the tensor memory goes back whatever happened above ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// [rows, K] bfloat16 with rows `ld` elements apart; box = 64 (K) x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
+cudaError_t launch_tc(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& ma,
+                      const CUtensorMap& mb, TO* out, int64_t ldo, const float* bias, int rows_a,
+                      int rows_b, int K, int stages, int splitk, float* scratch, int* counters) {
+    auto kernel = gemm_tc_kernel<BN, TRANSPOSED, SWIGLU, TO>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return tk_launch(kernel, grid, dim3(TC_THREADS), smem, stream, ma, mb, out, ldo, bias, rows_a, rows_b, K,
+                     stages, splitk, scratch, counters);
+}
+
+}  // namespace
+
+// 0 if no tensor-core GEMM on the current device has given up on a barrier since the last call;
+// else the place it gave up (1 producer, 2 MMA issuer, 3 epilogue). Resets the word.
+TK_API int tk_gemm_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}
+
+// Scratch the split-K path needs, in bytes: floats [tokens][n] then int counters (one per tile).
+TK_API int64_t tk_gemm_tc_scratch_bytes(int tokens, int n) {
+    return (int64_t)tokens * n * 4 + ((int64_t)(n + BM - 1) / BM) * ((tokens + 15) / 16) * 4 + 256;
+}
+
+// Decode form: out[tokens, N] = x[tokens, K] . w[N, K]^T (+ bias[N]); tokens <= 256.
+// swiglu: see gemm_skinny (rows of w in runs of 8 gate / 8 up; out is [tokens, N / 2]).
+// scratch: zeroed memory of tk_gemm_tc_scratch_bytes(tokens, N) bytes (kept zero by the kernel),
+// or null to forbid splitting K. out_dtype: bfloat16 or float.
+TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                             void* out, int64_t ldo, int tokens, int N, int K, int out_dtype, int swiglu,
+                             void* scratch, cudaStream_t stream) {
+    TK_CHECK_ARG(tokens > 0 && tokens <= 256 && N > 0 && K > 0, "gemm_tc_decode: tokens=%d (1..256) N=%d K=%d",
+                 tokens, N, K);
+    TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0,
+                 "gemm_tc_decode: K and the leading dimensions must be multiples of 8, bases 16-byte aligned");
+    TK_CHECK_ARG(!swiglu || N % 16 == 0, "gemm_tc_decode: the fused SwiGLU needs N (%d) in blocks of 16", N);
+    const int BN = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256;
+    CUtensorMap ma, mb;
+    TK_CHECK_ARG(make_map(&ma, w, N, K, ldw, BM) && make_map(&mb, x, tokens, K, ldx, BN),
+                 "gemm_tc_decode: cuTensorMapEncodeTiled failed (N=%d K=%d ldw=%lld)", N, K, (long long)ldw);
+    const int a_tiles = (N + BM - 1) / BM;
+    const int kb_total = (K + BK - 1) / BK;
+    int splitk = 1;
+    if (scratch != nullptr) {
+        while (a_tiles * splitk < 2 * 148 && kb_total / (splitk * 2) >= 4) splitk *= 2;
+    }
+    const int kb_per = (kb_total + splitk - 1) / splitk;
+    const int stage_bytes = A_TILE_BYTES + BN * BK * 2;
+    int stages = kb_per < 6 ? kb_per : 6;
+    while (stages > 2 && (size_t)stages * stage_bytes > 160 * 1024) --stages;
+    const size_t smem = (size_t)stages * stage_bytes + (2 * stages + 2) * 8 + 1024 + 64;
+    const dim3 grid(a_tiles, 1, splitk);
+    float* sc = (float*)scratch;
+    int* counters = scratch ? (int*)((char*)scratch + (size_t)tokens * N * 4) : nullptr;
+    cudaError_t err = cudaSuccess;
+#define TK_TC(BN_, SW_, TO_)                                                                        \
+    err = launch_tc<BN_, true, SW_, TO_>(grid, smem, stream, ma, mb, (TO_*)out, ldo, bias, N, tokens, K, \
+                                         stages, splitk, sc, counters)
+#define TK_TC_BN(SW_, TO_)                                                                          \
+    switch (BN) {                                                                                   \
+        case 16: TK_TC(16, SW_, TO_); break;                                                        \
+        case 32: TK_TC(32, SW_, TO_); break;                                                        \
+        case 64: TK_TC(64, SW_, TO_); break;                                                        \
+        case 128: TK_TC(128, SW_, TO_); break;                                                      \
+        default: TK_TC(256, SW_, TO_); break;                                                       \
+    }
+    if (out_dtype == TK_BF16) {
+        if (swiglu) { TK_TC_BN(true, __nv_bfloat16) } else { TK_TC_BN(false, __nv_bfloat16) }
+    } else if (out_dtype == TK_F32) {
+        if (swiglu) { TK_TC_BN(true, float) } else { TK_TC_BN(false, float) }
+    } else {
+        TK_CHECK_ARG(false, "gemm_tc_decode: output dtype %d", out_dtype);
+    }
+#undef TK_TC_BN
+#undef TK_TC
+    if (err != cudaSuccess) {
+        tk_set_error("gemm_tc_decode: launch failed: %s (tiles %d, splitk %d, stages %d, smem %zu)",
+                     cudaGetErrorString(err), a_tiles, splitk, stages, smem);
+        cudaGetLastError();
+        return -2;
+    }
+    return 0;
+}

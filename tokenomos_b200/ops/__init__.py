@@ -18,7 +18,7 @@ __all__ = [
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "conv_gated", "conv_min_tile",
-    "gemm", "gemm_skinny", "gemm_skinny_ok", "sample",
+    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample",
 ]
 
 
@@ -312,6 +312,57 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     _lib.call("tk_gemm_skinny", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
               _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), _stream())
     return out
+
+
+TC_MAX_TOKENS = 256
+_TC_SCRATCH_BYTES = 40 << 20
+_tc_scratch: dict = {}
+
+
+def _scratch_for(device: torch.device, tokens: int, n: int) -> torch.Tensor | None:
+    """The zeroed scratch the split-K path of ``gemm_tc`` adds partial tiles into (the kernel
+    leaves it zero again). One buffer per device, made at first use; a product too large for it
+    runs without splitting K."""
+    need = tokens * n * 4 + ((n + 127) // 128) * ((tokens + 15) // 16) * 4 + 256
+    if need > _TC_SCRATCH_BYTES:
+        return None
+    buf = _tc_scratch.get(device)
+    if buf is None:
+        buf = _tc_scratch[device] = torch.zeros(_TC_SCRATCH_BYTES, dtype=torch.uint8, device=device)
+    return buf
+
+
+def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_tc`` takes this product: bfloat16, at most 256 rows of ``x``, K and the row
+    strides multiples of 8 elements, 16-byte aligned bases."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda
+            and 0 < x.shape[0] <= TC_MAX_TOKENS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+            out_dtype: torch.dtype | None = None, swiglu: bool = False,
+            split_k: bool = True) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` through TMA, tcgen05.mma and tensor memory, the weight rows on the
+    MMA's M axis (decode: up to 256 rows of ``x``). ``swiglu`` as in ``gemm_skinny``."""
+    _cuda(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_tc: x {tuple(x.shape)} against w {tuple(w.shape)}")
+    width = N // 2 if swiglu else N
+    out = torch.empty(M, width, dtype=out_dtype or x.dtype, device=x.device)
+    scratch = _scratch_for(x.device, M, N) if split_k else None
+    _lib.call("tk_gemm_tc_decode", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
+              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), _ptr(scratch), _stream())
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or where a tensor-core GEMM gave up waiting on a barrier since the last call (the
+    kernels bound every wait instead of hanging)."""
+    return _lib.call("tk_gemm_tc_status")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,

@@ -41,6 +41,8 @@ _SIGNATURES = {
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
+    "tk_gemm_tc_status": [],
+    "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
 }
 
 
@@ -88,7 +90,7 @@ def calls() -> int:
 
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_attn_generic_rows", "tk_conv_min_tile",
-            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens"}
+            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status"}
 
 
 def call(name: str, *args) -> int:
