@@ -5,7 +5,8 @@
 A step is one decode step: every live request brings one token, the engine's captured step
 (embedding to sampled token) runs once. ``value`` is decoded tokens per second at ``--batch``
 requests whose prompts of 2,048 random tokens were prefilled first; it is timed on the device
-with CUDA events around exactly K steps after W warm-up steps. ``e2e`` is the same rate through
+with CUDA events around exactly K steps after W warm-up steps (each step's layout is packed and
+uploaded by the host and its tokens are read back, one step behind the device as in serving). ``e2e`` is the same rate through
 ``LLM.generate`` (host token ids in, host token ids out; every step uploads its layout from
 pinned memory and reads its tokens back). The line also carries the prefill of one 2,048-token
 prompt, the decode step's HBM roofline, and decode rates at batch 1 and 64. Weights are random
@@ -162,13 +163,17 @@ def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, se
         step_fn.run([StepEntry(r, ids, [])])
         last.append(int(ids[-1]))
     rows = [(0.0, 1.0, 0, 0.0, 0, 0)] * batch
+    pending = []
 
-    def one():
-        nonlocal last
-        last = step_fn.run_decode_graph([StepEntry(r, [last[r]], []) for r in range(batch)], rows,
-                                        commit=True)
+    def one(first=False):
+        # queue a step before the one before it has been read: its tokens are fed on the device
+        entries = [StepEntry(r, [last[r]] if first else [0], []) for r in range(batch)]
+        pending.append(step_fn.launch_decode_graph(entries, rows, [not first] * batch, commit=True))
+        while len(pending) > 1:
+            pending.pop(0).tokens()
 
-    for _ in range(warmup):
+    one(first=True)
+    for _ in range(warmup - 1):
         one()
     torch.cuda.synchronize()
     ctx_start = cache.length(0)
@@ -179,6 +184,8 @@ def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, se
         one()
     end.record()
     torch.cuda.synchronize()
+    while pending:
+        pending.pop(0).tokens()
     ms = start.elapsed_time(end) / steps
     graph = step_fn.decode_graph(batch)
     out = {"ms_per_step": ms, "tok_s": batch / ms * 1e3, "ctx_start": ctx_start,

@@ -612,3 +612,45 @@ def test_gemm_skinny_fused_swiglu_and_interleaved_layout(m, inter, k):
     unfused = ops.swiglu(ops.gemm_skinny(dev(x), dev(w)), 8)
     close(unfused, want, torch.bfloat16, "interleaved swiglu kernel")
     assert (fused.float() - unfused.float()).abs().max().item() <= 0.02 * want.abs().max().item()
+
+
+# ---- TMA + tcgen05 matrix product -----------------------------------------------------------------
+
+@pytest.mark.parametrize("m, n, k, split", [(8, 128, 64, False), (1, 256, 512, False), (16, 2048, 2048, True),
+                                            (3, 6144, 2048, True), (8, 2048, 8192, True), (8, 200, 72, False),
+                                            (40, 1000, 200, True), (64, 3072, 2048, True), (130, 512, 512, True),
+                                            (256, 384, 1024, True), (5, 70000, 256, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tc(m, n, k, split, out_dtype):
+    from tokenomos_b200 import ops
+    x = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    b = torch.randn(n)
+    assert ops.gemm_tc_ok(dev(x), dev(w))
+    want = x.double() @ w.double().T + b.double()
+    for _ in range(2):         # twice: the split-K scratch must be clean again after a call
+        got = ops.gemm_tc(dev(x), dev(w), dev(b), out_dtype, split_k=split)
+        close(got, want, out_dtype, f"tc {m}x{n}x{k}")
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m, inter, k", [(13, 128, 128), (8, 8192, 2048), (64, 1024, 512)])
+def test_gemm_tc_fused_swiglu(m, inter, k):
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.ffn import interleave_rows
+    x = torch.randn(m, k).to(torch.bfloat16)
+    gate = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    got = ops.gemm_tc(dev(x), dev(interleave_rows(gate, up, 8)), swiglu=True)
+    close(got, want, torch.bfloat16, "tc fused swiglu")
+    assert ops.gemm_tc_status() == 0
+
+
+def test_swiglu_vectorised_path_matches_the_scalar_one():
+    from tokenomos_b200 import ops
+    gu = (torch.randn(33, 2 * 256) * 2).to(torch.bfloat16)
+    for block in (0, 8):
+        fast = ops.swiglu(dev(gu), block)                      # 16-byte path
+        slow = ops.swiglu(dev(gu.float()), block)              # float32 goes through the scalar kernel
+        assert (fast.float() - slow).abs().max().item() <= 0.02 * slow.abs().max().item()

@@ -82,6 +82,7 @@ class RequestState:
     length: int = 0                                   # tokens in the cache
     reserved: int = 0                                 # tokens pages are held for (>= length)
     tables: dict[tuple, list[int]] = field(default_factory=dict)  # group -> page per block (0: none)
+    epoch: int = 0                                    # distinguishes two lives of one request id
 
 
 class CacheManager:
@@ -152,7 +153,8 @@ class CacheManager:
             raise CacheError(f"request {rid!r} is already live")
         if not len(self.slots):
             raise OutOfPages("no free slot")
-        st = RequestState(self.slots.take(), tables={k: [] for k in self.groups})
+        self._epoch = getattr(self, "_epoch", 0) + 1
+        st = RequestState(self.slots.take(), tables={k: [] for k in self.groups}, epoch=self._epoch)
         self.requests[rid] = st
         return st
 

@@ -263,6 +263,35 @@ __global__ void swiglu_kernel(const T* gu, T* out, int64_t total,
     }
 }
 
+// 16 bytes of gate and of up per thread (block == 0 or block a multiple of 8 channels)
+__global__ void swiglu_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int64_t vecs, int inter,
+                                  int block) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    const int per_row = inter / 8;
+    for (; i < vecs; i += step) {
+        const int64_t t = i / per_row;
+        const int c = (int)(i - t * per_row) * 8;
+        const int gi = block > 0 ? (c / block) * 2 * block + c % block : c;
+        const int ui = block > 0 ? gi + block : inter + c;
+        const uint4 graw = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + gi);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + ui);
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&graw);
+        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uraw);
+        uint4 packed;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float gf = __bfloat162float(g[k]);
+            const float s = round_as<__nv_bfloat16>(gf / (1.0f + expf(-gf)));
+            o[k] = __float2bfloat16_rn(s * __bfloat162float(u[k]));
+        }
+        *reinterpret_cast<uint4*>(out + t * inter + c) = packed;
+    }
+}
+
 TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int block, int dtype,
                      cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
@@ -271,6 +300,16 @@ TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int block, 
     if (rows == 0) return 0;
     const int64_t total = (int64_t)rows * inter;
     const int threads = 256;
+    if (dtype == TK_BF16 && inter % 8 == 0 && (block == 0 || block % 8 == 0) && (uintptr_t)gu % 16 == 0 &&
+        (uintptr_t)out % 16 == 0) {
+        const int64_t vecs = total / 8;
+        const int vblocks = (int)((vecs + threads - 1) / threads < 148 * 32 ? (vecs + threads - 1) / threads
+                                                                            : 148 * 32);
+        tk_launch(swiglu_vec_kernel, dim3(vblocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
+                  (__nv_bfloat16*)out, vecs, inter, block);
+        TK_CHECK_LAUNCH("swiglu_vec");
+        return 0;
+    }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                         : 148 * 16);
     if (dtype == TK_F32)

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
               const float* top_p, const int* top_k,
               const float* min_p, const int* seed,
-              const int* step, int* out) {
+              const int* step, int* out, const int* scatter_index, int* scatter_out) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ Best bred[33];
@@ -102,7 +102,10 @@ sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
     b = block_best(b, bred);
     const float t = temp[r];
     if (t <= 0.f) {
-        if (threadIdx.x == 0) out[r] = b.i;
+        if (threadIdx.x == 0) {
+            out[r] = b.i;
+            if (scatter_out != nullptr) scatter_out[scatter_index[r]] = b.i;
+        }
         return;
     }
     const float inv_t = 1.0f / t;
@@ -146,17 +149,43 @@ sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
         }
     }
     g = block_best(g, bred);
-    if (threadIdx.x == 0) out[r] = g.i == 0x7fffffff ? b.i : g.i;
+    if (threadIdx.x == 0) {
+        const int tok = g.i == 0x7fffffff ? b.i : g.i;
+        out[r] = tok;
+        if (scatter_out != nullptr) scatter_out[scatter_index[r]] = tok;
+    }
+}
+
+// ids[i] = use_prev[i] ? last_token[slot[i]] : ids_host[i]: a decode step takes the token the
+// step before it sampled straight from device memory when the host has not read it yet.
+__global__ void select_ids_kernel(const int* ids_host, const int* use_prev, const int* last_token,
+                                  const int* slot, int* ids, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[i] = use_prev[i] ? last_token[slot[i]] : ids_host[i];
+}
+
+TK_API int tk_select_ids(const int* ids_host, const int* use_prev, const int* last_token, const int* slot,
+                         int* ids, int n, cudaStream_t stream) {
+    TK_CHECK_ARG(n >= 0, "select_ids: n=%d", n);
+    if (n == 0) return 0;
+    tk_launch(select_ids_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids_host, use_prev, last_token,
+              slot, ids, n);
+    TK_CHECK_LAUNCH("select_ids");
+    return 0;
 }
 
 // logits: [rows, V] float with row stride `stride`; parameter arrays: [rows]; out: [rows] int32.
+// scatter_out (optional): also scatter_out[scatter_index[r]] = token of row r.
 TK_API int tk_sample(const float* logits, int64_t stride, int rows, int V, const float* temp,
                      const float* top_p, const int* top_k, const float* min_p, const int* seed,
-                     const int* step, int* out, cudaStream_t stream) {
+                     const int* step, int* out, const int* scatter_index, int* scatter_out,
+                     cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && V > 0 && stride >= V, "sample: bad sizes rows=%d V=%d", rows, V);
     if (rows == 0) return 0;
     tk_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, V, temp, top_p, top_k, min_p,
-                                                       seed, step, out);
+                                                       seed, step, out, scatter_index, scatter_out);
     TK_CHECK_LAUNCH("sample");
     return 0;
 }

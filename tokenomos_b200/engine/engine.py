@@ -18,7 +18,9 @@ from dataclasses import dataclass, field
 import torch
 
 from tokenomos_b200.cache.manager import CacheManager
-from tokenomos_b200.engine.scheduler import Planned, Request, Scheduler
+from collections import deque
+
+from tokenomos_b200.engine.scheduler import NeedsDrain, Planned, Request, Scheduler
 from tokenomos_b200.engine.step import StepEntry, StepFunction
 from tokenomos_b200.sampling import sampler
 
@@ -63,6 +65,9 @@ class Engine:
         self.step_fn = StepFunction(model, self.cache)
         self.scheduler = Scheduler(self.cache, prefill_budget, slots)
         self.graphs = graphs
+        # decode steps queued on the device whose tokens the host has not read: (plan, handle)
+        self._inflight: deque = deque()
+        self.depth = 1
         self.inbox: queue.Queue[Request] = queue.Queue()
         self.stats = Stats()
 
@@ -85,19 +90,59 @@ class Engine:
             except queue.Empty:
                 return
 
+    def _finish(self, finished: list[Request]) -> list[Request]:
+        for req in finished:
+            req.result = Result(list(req.output), req.finish)
+            if req.on_done is not None:
+                req.on_done(req)
+        return finished
+
+    def _drain(self) -> list[Request]:
+        finished = []
+        while self._inflight:
+            planned, handle = self._inflight.popleft()
+            finished += self.scheduler.deliver(planned, handle.tokens())
+        return finished
+
+    def drain(self) -> list[Request]:
+        """Read every step in flight: after this the host knows every sampled token."""
+        return self._finish(self._drain())
+
     @torch.no_grad()
     def step(self) -> list[Request]:
-        """Plan, run and commit one step; returns the requests that finished in it."""
-        planned = self.scheduler.plan()
+        """Plan and queue one step; returns the requests that finished meanwhile. A step in
+        which every request decodes one token replays a CUDA graph and is not waited for: its
+        tokens are read while the next step runs (the host stays one step behind the device, as
+        the reference's loop does, Tokenomos core/engine.py:1-14); a request that a stop token
+        ends therefore decodes one token too many, which is dropped. Any other step (prompt
+        portions, a preemption) first reads what is in flight and then runs synchronously."""
+        finished: list[Request] = []
+        try:
+            planned = self.scheduler.plan()
+        except NeedsDrain:
+            finished += self._drain()
+            if self.scheduler.idle():
+                return self._finish(finished)
+            planned = self.scheduler.plan()
         if not planned:
-            return []
+            return self._finish(finished + self._drain())
+        decode_only = all(p.count == 1 and p.sample for p in planned)
+        if not (self.graphs and decode_only) and (self._inflight or any(p.fed_on_device for p in planned)):
+            # the eager path needs every token on the host: undo nothing (pages stay held), read
+            # what is in flight, and plan again with the tokens known
+            finished += self._drain()
+            planned = self.scheduler.plan() if not self.scheduler.idle() else []
+            if not planned:
+                return self._finish(finished)
+            decode_only = all(p.count == 1 and p.sample for p in planned)
         entries, rows = [], []
         for p in planned:
-            toks = p.req.tokens[p.start:p.start + p.count]
-            entries.append(StepEntry(p.req.rid, toks, [p.count - 1] if p.sample else []))
+            r = p.req
+            toks = [0] if p.fed_on_device else r.tokens[p.start:p.start + p.count]
+            entries.append(StepEntry(r.rid, toks, [p.count - 1] if p.sample else []))
             if p.sample:
-                r = p.req
-                rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed, len(r.output)))
+                rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed,
+                             len(r.output) + r.inflight))
         tokens_in_step = sum(p.count for p in planned)
         self.stats.stamps.append((time.perf_counter(), len(planned), tokens_in_step))
         self.stats.steps += 1
@@ -105,22 +150,25 @@ class Engine:
             self.stats.decode_steps += 1
         else:
             self.stats.prefill_tokens += sum(p.count for p in planned if p.count > 1)
-        sampled: list[int] = []
-        if self.graphs and rows and len(rows) == len(planned) and all(p.count == 1 for p in planned):
-            sampled = self.step_fn.run_decode_graph(entries, rows)
+        if self.graphs and decode_only:
+            handle = self.step_fn.launch_decode_graph(entries, rows, [p.fed_on_device for p in planned])
+            self.scheduler.launch(planned)
+            self._inflight.append((planned, handle))
+            self.stats.generated += len(rows)
+            while len(self._inflight) > self.depth:
+                old_planned, old_handle = self._inflight.popleft()
+                finished += self.scheduler.deliver(old_planned, old_handle.tokens())
         else:
             logits = self.step_fn.run(entries, commit=False)
+            sampled: list[int] = []
             if rows:
                 packed = self.step_fn._upload(sampler.pack_rows(rows))
-                sampled = sampler.sample_packed(logits, packed).tolist()
-        self.stats.generated += len(sampled)
-        finished = self.scheduler.commit(planned, sampled)
+                slots = self.step_fn._upload([self.cache.slot(p.req.rid) for p in planned if p.sample])
+                sampled = sampler.sample_packed(logits, packed, scatter=(slots, self.step_fn.last_token)).tolist()
+            self.stats.generated += len(sampled)
+            finished += self.scheduler.commit(planned, sampled)
         self.stats.preemptions = self.scheduler.stats["preemptions"]
-        for req in finished:
-            req.result = Result(list(req.output), req.finish)
-            if req.on_done is not None:
-                req.on_done(req)
-        return finished
+        return self._finish(finished)
 
     def run(self, stop: threading.Event | None = None) -> None:
         """Serve the inbox until nothing is queued or running (``stop`` None), or until ``stop``
@@ -129,6 +177,7 @@ class Engine:
         while True:
             self._take_inbox()
             if self.scheduler.idle():
+                self.drain()
                 if stop is None or stop.is_set():
                     break
                 try:

@@ -57,27 +57,46 @@ class Request:
     preemptions: int = 0
     arrival: int = -1
     result: object = None
+    # tokens sampled on the device whose values the host has not read yet (a step in flight)
+    inflight: int = 0
 
     @property
     def tokens(self) -> list[int]:
         return self.prompt + self.output
 
     @property
+    def total(self) -> int:
+        """Tokens of the sequence so far, those still in flight included."""
+        return len(self.prompt) + len(self.output) + self.inflight
+
+    @property
     def pending(self) -> int:
-        """Tokens known but not yet in the cache."""
-        return len(self.prompt) + len(self.output) - self.computed
+        """Tokens (known or in flight) not yet in the cache."""
+        return self.total - self.computed
+
+    @property
+    def sampled_all(self) -> bool:
+        """Every token the request may generate has been sampled (some may be in flight)."""
+        return len(self.output) + self.inflight >= self.max_new
 
 
 @dataclass
 class Planned:
     """One request's share of the next step: tokens ``[start, start + count)`` of prompt +
     output; ``sample``: the share reaches the end of what is known, so its last position's
-    logits are sampled."""
+    logits are sampled. ``fed_on_device``: the share is the one token an earlier step sampled
+    and the host has not read yet; the device feeds it."""
 
     req: Request
     start: int
     count: int
     sample: bool
+    fed_on_device: bool = False
+
+
+class NeedsDrain(Exception):
+    """The plan needs token values that are still in flight (a preemption, or a share that is
+    not a single decoded token): read the steps in flight first, then plan again."""
 
 
 class Scheduler:
@@ -139,8 +158,11 @@ class Scheduler:
         total = 0
         for req in self.running:
             held = self._pages_for(self.cache.requests[req.rid].reserved)
-            total += max(0, self._pages_for(len(req.tokens) + 1) - held)
+            total += max(0, self._pages_for(req.total + 1) - held)
         return total
+
+    def inflight(self) -> bool:
+        return any(r.inflight for r in self.running)
 
     def plan(self) -> list[Planned]:
         """Decide the next step and hold its pages (``CacheManager.extend``)."""
@@ -155,7 +177,11 @@ class Scheduler:
             if budget <= 0:
                 break
             count = min(req.pending, budget)
+            if count <= 0:
+                continue                      # everything is sampled; waiting for its tokens
             while not cache.can_extend(req.rid, count):
+                if self.inflight():
+                    raise NeedsDrain("a preemption needs every token value on the host")
                 victim = self.running[-1]
                 if victim is req and len(self.running) == 1:
                     raise OutOfPages(f"request {req.rid} cannot get its pages although it is "
@@ -165,8 +191,12 @@ class Scheduler:
                     break
             if req not in self.running:
                 continue
+            fed = req.inflight > 0
+            if fed and not (count == 1 and req.inflight == 1):
+                raise NeedsDrain("only a single decoded token can be fed on the device")
             cache.extend(req.rid, count)
-            planned.append(Planned(req, req.computed, count, req.computed + count == len(req.tokens)))
+            sample = req.computed + count == req.total and not req.sampled_all
+            planned.append(Planned(req, req.computed, count, sample, fed))
             budget -= count
         # 3: admissions, in arrival order (a preempted request is at the front)
         while self.waiting and budget > 0 and len(self.running) < self.max_seqs:
@@ -183,23 +213,36 @@ class Scheduler:
             planned.append(Planned(req, 0, count, count == len(req.tokens)))
             budget -= count
         if not planned and (self.running or self.waiting):
+            if self.inflight():
+                raise NeedsDrain("nothing to run until the steps in flight are read")
             raise OutOfPages("the scheduler can run nothing: the pool is too small for the "
                              "oldest request")
         self.stats["steps"] += bool(planned)
         return planned
 
-    def commit(self, planned: list[Planned], sampled: list[int]) -> list[Request]:
-        """The step ran: advance every planned request, append the sampled tokens (one per
-        planned share with ``sample``, in order), finish and free what is done."""
+    def launch(self, planned: list[Planned]) -> None:
+        """The step has been handed to the device: advance every planned request's length; the
+        tokens it samples are in flight until ``deliver``."""
+        for p in planned:
+            self.cache.commit(p.req.rid, p.count)
+            p.req.computed += p.count
+            if p.sample:
+                p.req.inflight += 1
+
+    def deliver(self, planned: list[Planned], sampled: list[int]) -> list[Request]:
+        """The sampled tokens of a launched step (one per share with ``sample``, in order):
+        append them, finish and free what is done. A request that an earlier delivery finished
+        (a stop token seen one step late) drops its token."""
         it = iter(sampled)
         finished = []
         for p in planned:
-            req = p.req
-            self.cache.commit(req.rid, p.count)
-            req.computed += p.count
             if not p.sample:
                 continue
+            req = p.req
             tok = int(next(it))
+            req.inflight -= 1
+            if req.finish is not None:
+                continue
             req.output.append(tok)
             if req.on_tokens is not None:
                 req.on_tokens([tok])
@@ -213,3 +256,8 @@ class Scheduler:
                 self.stats["finished"] += 1
                 finished.append(req)
         return finished
+
+    def commit(self, planned: list[Planned], sampled: list[int]) -> list[Request]:
+        """``launch`` and ``deliver`` in one call, for a step whose tokens are read at once."""
+        self.launch(planned)
+        return self.deliver(planned, sampled)

@@ -89,33 +89,44 @@ class _ConstTiles:
 
 
 class _DecodeGraph:
-    """One captured decode step for ``rows`` sequences: static layout buffer in, tokens out."""
+    """One captured decode step for ``rows`` sequences: a static layout buffer in, tokens out.
+
+    The token a row feeds is either given by the host or, when the step that sampled it is still
+    in flight, taken on the device from ``last_token[slot]``, which the sampler of every step
+    writes; so the host may queue a step before it has read the tokens of the one before."""
+
+    RING = 2     # host staging buffers: step n + 1 is packed while step n's copy may be pending
 
     def __init__(self, step_fn: "StepFunction", rows: int):
         cache, dev = step_fn.cache, step_fn.device
         self.rows = rows
         self.width = cache.max_blocks
-        groups = list(cache.groups)
+        self.groups = list(cache.groups)
         b = rows
         # layout of the int32 buffer the host fills each step
         self.off = {}
         o = 0
-        for name, n in (("positions", b), ("seq_ctx", b), ("seq_slot", b), ("ids", b),
-                        ("sampling", 6 * b)):
+        for name, n in (("positions", b), ("seq_ctx", b), ("seq_slot", b), ("ids_host", b),
+                        ("use_prev", b), ("sampling", 6 * b)):
             self.off[name] = (o, n)
             o += n
-        for g in groups:
+        for g in self.groups:
             self.off[("table", g)] = (o, b * self.width)
             o += b * self.width
         self.size = o
-        self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
-        self.host_np = self.host.numpy()
+        self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        # what each staging buffer's block-table rows hold: (request, entries written) per row
+        self.host_rows = [{g: [(None, 0)] * b for g in self.groups} for _ in range(self.RING)]
+        self.tokens_host = [torch.zeros(b, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.turn = 0
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.ids = torch.zeros(b, dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(b, dtype=torch.int32, device=dev)
-        self.tokens_host = torch.zeros(b, dtype=torch.int32).pin_memory()
         arange = torch.arange(b + 1, dtype=torch.int32, device=dev)
         zeros = torch.zeros(b, dtype=torch.int32, device=dev)
         ones = torch.ones(b, dtype=torch.int32, device=dev)
+        self.last_token = step_fn.last_token
 
         def view(name):
             a, n = self.off[name]
@@ -124,20 +135,24 @@ class _DecodeGraph:
         self.ctx = StepContext(
             n_tokens=b, n_seqs=b, positions=view("positions"), tok_seq=arange[:b],
             cu_seqlens=arange, seq_ctx=view("seq_ctx"), seq_slot=view("seq_slot"),
-            block_tables={g: view(("table", g)).view(b, self.width) for g in groups},
+            block_tables={g: view(("table", g)).view(b, self.width) for g in self.groups},
             states=cache.states, state_groups=cache.state_groups, page_size=cache.page_size,
             host=HostLayout([1] * b, [0] * b, [0] * b, True, cache.max_len),
             tile_source=_ConstTiles(arange[:b], zeros, ones))
-        self.ids, self.want, self.sampling = view("ids"), arange[:b], view("sampling")
+        self.ids_host, self.use_prev = view("ids_host"), view("use_prev")
+        self.want, self.sampling = arange[:b], view("sampling")
         self.graph = None
         self.launches = 0
 
     def body(self, model):
+        from tokenomos_b200 import ops
         from tokenomos_b200.sampling import sampler
 
+        ops.select_ids(self.ids_host, self.use_prev, self.last_token, self.ctx.seq_slot, self.ids)
         out = model.forward(model.embed(self.ids), self.ctx)
         logits = model.logits(out, self.want)
-        sampler.sample_packed(logits, self.sampling, self.tokens)
+        sampler.sample_packed(logits, self.sampling, self.tokens,
+                              scatter=(self.ctx.seq_slot, self.last_token))
 
     def capture(self, model):
         from tokenomos_b200.ops import _lib
@@ -156,11 +171,27 @@ class _DecodeGraph:
         self.graph = graph
 
 
+class DecodeHandle:
+    """A decode step in flight: ``tokens()`` waits for it and returns the sampled tokens."""
+
+    def __init__(self, event, host_tokens: torch.Tensor, n: int):
+        self.event, self.host_tokens, self.n = event, host_tokens, n
+        self._tokens = None
+
+    def tokens(self) -> list[int]:
+        if self._tokens is None:
+            self.event.synchronize()
+            self._tokens = self.host_tokens[:self.n].tolist()
+        return self._tokens
+
+
 class StepFunction:
     def __init__(self, model, cache: CacheManager, staging_ints: int = 1 << 20):
         self.model, self.cache = model, cache
         self.device = cache.device
         self._graphs: dict[int, _DecodeGraph] = {}
+        # the token each request's last step sampled, by state slot (slot 0: padded rows)
+        self.last_token = torch.zeros(cache.max_requests + 1, dtype=torch.int32, device=self.device)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         # pinned staging for the layout, used round-robin so that a copy still in flight is
@@ -292,12 +323,15 @@ class StepFunction:
         return g
 
     @torch.no_grad()
-    def run_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
-                         commit: bool = False) -> list[int]:
-        """One decode step for entries of one token each: the layout goes up in one copy from
-        pinned memory, the captured graph (embedding to sampled token) replays, the tokens come
-        back in one copy. Rows of the bucket beyond the entries point at the null slot and the
-        null page. Returns the sampled token of each entry."""
+    def launch_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
+                            fed_on_device: list[bool] | None = None,
+                            commit: bool = False) -> DecodeHandle:
+        """Queue one decode step for entries of one token each and return at once: the layout
+        goes up in one copy from pinned memory, the captured graph (token select, embedding ...
+        sampled token) replays, the tokens come back in one copy; ``handle.tokens()`` waits for
+        them. ``fed_on_device[i]``: entry i's token is the one its previous step sampled, which
+        the host may not have read yet; the device takes it from ``last_token``. Rows of the
+        bucket beyond the entries point at the null slot and the null page."""
         from tokenomos_b200.sampling import sampler
 
         cache = self.cache
@@ -307,33 +341,55 @@ class StepFunction:
                 raise ValueError("the decode graph takes one token per request")
             cache.extend(e.rid, 1)
         g = self.decode_graph(n)
-        h, b, width = g.host_np, g.rows, g.width
-        h[:] = 0
-        lengths = [cache.length(e.rid) for e in entries]
-        o, _ = g.off["positions"]
-        h[o:o + n] = lengths
-        o, _ = g.off["seq_ctx"]
-        h[o:o + n] = lengths
-        o, _ = g.off["seq_slot"]
-        h[o:o + n] = [cache.slot(e.rid) for e in entries]
-        o, _ = g.off["ids"]
-        h[o:o + n] = [e.tokens[0] for e in entries]
+        turn = g.turn
+        g.turn = (turn + 1) % g.RING
+        h, rows_held, b, width = g.host_np[turn], g.host_rows[turn], g.rows, g.width
+        states = [cache.requests[e.rid] for e in entries]
+        lengths = [st.length for st in states]
+        for name, values in (("positions", lengths), ("seq_ctx", lengths),
+                             ("seq_slot", [st.slot for st in states]),
+                             ("ids_host", [e.tokens[0] for e in entries]),
+                             ("use_prev", [int(f) for f in fed_on_device] if fed_on_device else [0] * n)):
+            o, _ = g.off[name]
+            h[o:o + n] = values
+            h[o + n:o + b] = 0
         o, _ = g.off["sampling"]
-        pad = [(0.0, 1.0, 0, 0.0, 0, 0)] * (b - n)
-        h[o:o + 6 * b] = sampler.pack_rows(list(sampling_rows) + pad)
-        for grp in cache.groups:
+        sampler.pack_rows_into(h[o:o + 6 * b], sampling_rows, b)
+        # block tables: a row that held the same request the last time this staging buffer was
+        # used only gets its new entries (a window group's entries also turn to 0: rewritten)
+        for grp in g.groups:
             o, _ = g.off[("table", grp)]
-            for i, e in enumerate(entries):
-                row = cache.block_table(e.rid, grp)
-                h[o + i * width:o + i * width + len(row)] = row
-        g.dev.copy_(g.host, non_blocking=True)
+            held = rows_held[grp]
+            incremental = cache.groups[grp].window is None
+            for i, (e, st) in enumerate(zip(entries, states)):
+                row = st.tables[grp]
+                base = o + i * width
+                held_rid, held_len = held[i]
+                if incremental and held_rid == (e.rid, st.epoch) and held_len <= len(row):
+                    if held_len < len(row):
+                        h[base + held_len:base + len(row)] = row[held_len:]
+                else:
+                    h[base:base + len(row)] = row
+                    h[base + len(row):base + width] = 0
+                held[i] = ((e.rid, st.epoch), len(row))
+            for i in range(n, b):
+                if held[i][0] is not None:
+                    h[o + i * width:o + (i + 1) * width] = 0
+                    held[i] = (None, 0)
+        g.dev.copy_(g.host[turn], non_blocking=True)
         g.graph.replay()
-        g.tokens_host.copy_(g.tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        g.tokens_host[turn].copy_(g.tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
         self.h2d_bytes += 4 * g.size
         self.d2h_bytes += 4 * b
         self.steps += 1
         if commit:
             for e in entries:
                 cache.commit(e.rid, 1)
-        return g.tokens_host[:n].tolist()
+        return DecodeHandle(event, g.tokens_host[turn], n)
+
+    def run_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
+                         commit: bool = False) -> list[int]:
+        """``launch_decode_graph`` and wait: the sampled token of each entry."""
+        return self.launch_decode_graph(entries, sampling_rows, None, commit).tokens()

@@ -18,7 +18,7 @@ __all__ = [
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "conv_gated", "conv_min_tile",
-    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample",
+    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "select_ids",
 ]
 
 
@@ -365,10 +365,25 @@ def gemm_tc_status() -> int:
     return _lib.call("tk_gemm_tc_status")
 
 
+def select_ids(ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
+               slot: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[i] = last_token[slot[i]] if use_prev[i] else ids_host[i]`` (all int32)."""
+    _cuda(ids_host, use_prev, last_token, slot, out)
+    n = out.numel()
+    for name, t in (("ids_host", ids_host), ("use_prev", use_prev), ("slot", slot)):
+        if _i32(t, name).numel() < n:
+            raise KernelError(f"select_ids: {name} is shorter than the output")
+    _lib.call("tk_select_ids", _ptr(ids_host), _ptr(use_prev), _ptr(_i32(last_token, "last_token")),
+              _ptr(slot), _ptr(_i32(out, "out")), n, _stream())
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
            top_k: torch.Tensor, min_p: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
-           out: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row of ``logits`` [rows, V] float32; the parameters are per-row arrays."""
+           out: torch.Tensor | None = None, scatter: tuple[torch.Tensor, torch.Tensor] | None = None
+           ) -> torch.Tensor:
+    """One token per row of ``logits`` [rows, V] float32; the parameters are per-row arrays.
+    ``scatter`` = (index [rows] int32, target int32): also ``target[index[r]] = token``."""
     _cuda(logits, temperature, top_p, top_k, min_p, seed, step, out)
     rows, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
@@ -380,6 +395,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
             raise KernelError(f"sample: {name} must be a contiguous {dt} array of {rows}")
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    idx, target = scatter if scatter is not None else (None, None)
+    if scatter is not None:
+        _cuda(idx, target)
+        _i32(idx, "scatter index"), _i32(target, "scatter target")
     _lib.call("tk_sample", _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_p),
-              _ptr(top_k), _ptr(min_p), _ptr(seed), _ptr(step), _ptr(out), _stream())
+              _ptr(top_k), _ptr(min_p), _ptr(seed), _ptr(step), _ptr(out), _ptr(idx), _ptr(target),
+              _stream())
     return out

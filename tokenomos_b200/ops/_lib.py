@@ -40,7 +40,8 @@ _SIGNATURES = {
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
-    "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P],
+    "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
+    "tk_select_ids": [P, P, P, P, P, I, P],
     "tk_gemm_tc_status": [],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
 }

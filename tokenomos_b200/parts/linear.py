@@ -4,10 +4,10 @@ Routes, by storage type:
 
 - float32: the CUDA-core kernel with 32-bit FMA accumulation (``ops.gemm``). No tensor-core or
   reduced-precision mode can reach it, whatever the process-wide torch flags say.
-- bfloat16 with at most 16 rows (decode): the hand-written weight-streaming kernel
-  (``ops.gemm_skinny``); with more rows the library GEMM (cuBLAS through
-  ``torch.nn.functional.linear``), as the reference engine does for every 16-bit projection
-  (Tokenomos models/blocks/linear.py:236-254).
+- bfloat16: by shape (``route``): the hand-written weight-streaming kernel for a few rows
+  (``ops.gemm_skinny``), the TMA + tcgen05 kernel for very tall matrices (``ops.gemm_tc``), else
+  the library GEMM (cuBLAS through ``torch.nn.functional.linear``), as the reference engine does
+  for every 16-bit projection (Tokenomos models/blocks/linear.py:236-254).
 - a matrix stored in 32-bit in a 16-bit model stays 32-bit: the activation is widened for it.
 
 Several matrices that read the same input are fused along the output axis at build time
@@ -51,13 +51,30 @@ class Linear:
             return ops.gemm(x, w, self.bias, torch.float32)
         if not x.is_cuda:
             raise ops.KernelError("Linear: CUDA tensors only (there is no CPU path)")
-        if ops.gemm_skinny_ok(x, w):
+        route = self.route(x)
+        if route == "tc":
+            return ops.gemm_tc(x, w, self.bias, out_dtype)
+        if route == "skinny":
             return ops.gemm_skinny(x, w, self.bias, out_dtype)
         if out_dtype == torch.float32:
             return self._float_out(x)
         if self.in_features % 8 or (x.stride(0) % 8 and x.shape[0] > 1):
             return ops.gemm(x, w, self.bias, out_dtype or x.dtype)
         return F.linear(x, w, self._bias_lp)
+
+    def route(self, x: torch.Tensor) -> str:
+        """Which kernel takes ``x`` [M, in]: measured on a B200 with 2048- to 8192-wide matrices
+        in CUDA graphs, the register-streaming kernel is the fastest up to 8 rows (and up to 16
+        for matrices of a few thousand rows), the TMA + tcgen05 kernel for very tall matrices
+        (the head), the library elsewhere."""
+        m, n = x.shape[0], self.out_features
+        if not ops.gemm_skinny_ok(x[:1], self.weight):
+            return "library"
+        if n >= 32768 and m <= 32:
+            return "tc"
+        if m <= 8 or (m <= 16 and n <= 4096):
+            return "skinny"
+        return "library"
 
     def _float_out(self, x: torch.Tensor) -> torch.Tensor:
         """16-bit operands, 32-bit result (the head: logits are not rounded to 16-bit)."""

@@ -32,9 +32,29 @@ def pack_rows(rows: list[tuple[float, float, int, float, int, int]]) -> list[int
     return out
 
 
-def sample_packed(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | None = None):
+def pack_rows_into(dst, rows: list[tuple[float, float, int, float, int, int]], n: int) -> None:
+    """``pack_rows`` straight into ``dst``, a numpy int32 view of ``6 * n`` words; rows beyond
+    ``len(rows)`` are greedy padding."""
+    import numpy as np
+
+    k = len(rows)
+    f = dst.view(np.float32)
+    dst[:] = 0
+    f[n:2 * n] = 1.0
+    if k:
+        cols = list(zip(*rows))
+        f[0:k] = cols[0]
+        f[n:n + k] = cols[1]
+        dst[2 * n:2 * n + k] = cols[2]
+        f[3 * n:3 * n + k] = cols[3]
+        dst[4 * n:4 * n + k] = [int(v) & 0x7FFFFFFF for v in cols[4]]
+        dst[5 * n:5 * n + k] = cols[5]
+
+
+def sample_packed(logits: torch.Tensor, packed: torch.Tensor, out: torch.Tensor | None = None,
+                  scatter=None):
     """``packed``: device int32 [6 * rows] from ``pack_rows``."""
     n = logits.shape[0]
     f = packed.view(torch.float32)
     return ops.sample(logits, f[:n], f[n:2 * n], packed[2 * n:3 * n], f[3 * n:4 * n],
-                      packed[4 * n:5 * n], packed[5 * n:6 * n], out)
+                      packed[4 * n:5 * n], packed[5 * n:6 * n], out, scatter)
