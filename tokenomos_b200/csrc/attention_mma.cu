@@ -530,3 +530,50 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
     TK_CHECK_LAUNCH("attn_decode_merge");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Split decode attention for callers that must not allocate (declared in no_alloc.h).
+//
+// tk_attn_decode_mma wants its scratch (the per-split partial results) from the caller, who
+// normally gets it from an allocator. Some callers cannot: code that runs inside a CUDA stream
+// capture it does not own, a latency-critical serving loop that has promised its memory pool
+// to someone else, a host language binding without an allocator of its own. For them the same
+// kernel runs on a fixed scratch that lives in the library image: a file-scope __device__ array.
+// The array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, asked for once per device at that device's first call.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr long long NOALLOC_SCRATCH_FLOATS = 2ll << 20;           // 8 MiB per device
+static __device__ __align__(256) float g_decode_scratch[NOALLOC_SCRATCH_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_decode_scratch_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+TK_API long long tk_attn_decode_mma_static_capacity() { return NOALLOC_SCRATCH_FLOATS; }
+
+TK_API int tk_attn_decode_mma_static(const void* q, const void* kv_pool, void* out,
+                                     const int* positions, const int* tok_seq,
+                                     const int* block_table, int bt_stride, const int* tok_index,
+                                     int n, int H, int Hkv, int D, int P, int window, float scale,
+                                     int nsplit, cudaStream_t stream) {
+    TK_CHECK_ARG(n >= 0 && H > 0 && D > 0 && nsplit >= 1, "attn_decode_mma_static: bad sizes");
+    const long long need = tk_attn_decode_mma_scratch(n, H, D, nsplit);
+    TK_CHECK_ARG(need <= NOALLOC_SCRATCH_FLOATS,
+                 "attn_decode_mma_static: %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of "
+                 "scratch, the built-in array holds %lld; use fewer splits or tk_attn_decode_mma with "
+                 "your own scratch", n, H, nsplit, D, need, (long long)NOALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    TK_CHECK_ARG(e == cudaSuccess && dev >= 0 && dev < NOALLOC_MAX_DEVICES,
+                 "attn_decode_mma_static: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    if (g_decode_scratch_ptr[dev] == nullptr) {
+        // once per device, with that device current: the symbol's address on *this* device
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+        TK_CHECK_ARG(e == cudaSuccess && p != nullptr, "attn_decode_mma_static: cudaGetSymbolAddress: %s",
+                     cudaGetErrorString(e));
+        g_decode_scratch_ptr[dev] = p;
+    }
+    return tk_attn_decode_mma(q, kv_pool, out, positions, tok_seq, block_table, bt_stride, tok_index, n, H,
+                              Hkv, D, P, window, scale, nsplit, g_decode_scratch_ptr[dev], stream);
+}
