@@ -91,6 +91,14 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* po
 
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x on the special-function unit (about 2 ulp in 32-bit, far below the bfloat16 rounding of P);
+// -inf gives 0, which the masking relies on
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // One 16-row x NK-key block of the online softmax for a warp: S = Q K^T from `ktile`, mask,
 // update (m, l, O) with V from `vtile`. NK is 64 (prefill) or 32 (decode).
 template <int D, int NK>
@@ -149,17 +157,17 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[D / 16][4], uint
     for (int h = 0; h < 2; ++h) {
         const float m_new = fmaxf(m[h], mx[h]);
         msafe[h] = m_new == -INFINITY ? 0.f : m_new;
-        alpha[h] = exp2f((m[h] - msafe[h]) * scale_log2);
+        alpha[h] = fast_exp2((m[h] - msafe[h]) * scale_log2);
         m[h] = m_new;
         l[h] *= alpha[h];
     }
     uint32_t pf[NK / 16][4];
 #pragma unroll
     for (int n = 0; n < NK / 8; ++n) {
-        const float p0 = exp2f((s[n][0] - msafe[0]) * scale_log2);
-        const float p1 = exp2f((s[n][1] - msafe[0]) * scale_log2);
-        const float p2 = exp2f((s[n][2] - msafe[1]) * scale_log2);
-        const float p3 = exp2f((s[n][3] - msafe[1]) * scale_log2);
+        const float p0 = fast_exp2((s[n][0] - msafe[0]) * scale_log2);
+        const float p1 = fast_exp2((s[n][1] - msafe[0]) * scale_log2);
+        const float p2 = fast_exp2((s[n][2] - msafe[1]) * scale_log2);
+        const float p3 = fast_exp2((s[n][3] - msafe[1]) * scale_log2);
         l[0] += p0 + p1;
         l[1] += p2 + p3;
         // the C layout of two neighbouring 8-key tiles is the A layout of one 16-key step
@@ -404,7 +412,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = sm_ml[(w * 16 + r) * 2];
-            const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * scale_log2);
+            const float f = mw == -INFINITY ? 0.f : fast_exp2((mw - M) * scale_log2);
             L += sm_ml[(w * 16 + r) * 2 + 1] * f;
             acc += sm_o[(w * 16 + r) * D + c] * f;
         }
@@ -438,7 +446,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
     float L = 0.f, acc = 0.f;
     for (int s = 0; s < nsplit; ++s) {
         const float ms = part_ml[(base + s) * 2];
-        const float f = ms == -INFINITY ? 0.f : exp2f((ms - M) * scale_log2);
+        const float f = ms == -INFINITY ? 0.f : fast_exp2((ms - M) * scale_log2);
         L += part_ml[(base + s) * 2 + 1] * f;
         acc += part_o[(base + s) * D + c] * f;
     }

@@ -92,7 +92,7 @@ __global__ void add_rmsnorm_kernel(const T* x, int64_t x_stride,
 // Fast path: the row lives in registers as 16-byte vectors (ITEMS per thread), so the kernel
 // makes one trip to memory: read x (and the residual), write the stream, reduce, write y.
 template <typename T, int ITEMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
                        const float* __restrict__ pre_w, float pre_eps, const float* __restrict__ w,
                        float eps, T* y, T* stream, int width) {
@@ -106,7 +106,7 @@ add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
     float ss = 0.f;
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
-        const int c = (it * 256 + threadIdx.x) * VEC;
+        const int c = (it * 128 + threadIdx.x) * VEC;
         if (c < width) {
             const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
             const T* e = reinterpret_cast<const T*>(&raw);
@@ -124,7 +124,7 @@ add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
         const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + pre_eps);
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) {
-            const int c = (it * 256 + threadIdx.x) * VEC;
+            const int c = (it * 128 + threadIdx.x) * VEC;
             if (c < width) {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k)
@@ -136,7 +136,7 @@ add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
         ss = 0.f;
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) {
-            const int c = (it * 256 + threadIdx.x) * VEC;
+            const int c = (it * 128 + threadIdx.x) * VEC;
             if (c < width) {
                 if (residual != nullptr) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(residual + (size_t)r * width + c);
@@ -159,7 +159,7 @@ add_rmsnorm_vec_kernel(const T* x, int64_t x_stride, const T* residual,
     const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
-        const int c = (it * 256 + threadIdx.x) * VEC;
+        const int c = (it * 128 + threadIdx.x) * VEC;
         if (c < width) {
             uint4 packed;
             T* e = reinterpret_cast<T*>(&packed);
@@ -186,14 +186,15 @@ static bool launch_add_rmsnorm_vec(const void* x, int64_t x_stride, const void* 
     const bool aligned = width % VEC == 0 && x_stride % VEC == 0 && (uintptr_t)x % 16 == 0 &&
                          (uintptr_t)residual % 16 == 0 && (uintptr_t)y % 16 == 0 &&
                          (uintptr_t)stream_out % 16 == 0 && (uintptr_t)w % 16 == 0;
-    if (!aligned || width > 4 * 256 * VEC) return false;
-    const int items = (width + 256 * VEC - 1) / (256 * VEC);
+    if (!aligned || width > 8 * 128 * VEC) return false;
+    const int items = (width + 128 * VEC - 1) / (128 * VEC);
 #define TK_NORM_VEC(IT)                                                                           \
-    tk_launch(add_rmsnorm_vec_kernel<T, IT>, dim3(rows), dim3(256), 0, stream, (const T*)x, x_stride, (const T*)residual, \
+    tk_launch(add_rmsnorm_vec_kernel<T, IT>, dim3(rows), dim3(128), 0, stream, (const T*)x, x_stride, (const T*)residual, \
         pre_w, pre_eps, w, eps, (T*)y, (T*)stream_out, width)
     if (items <= 1) TK_NORM_VEC(1);
     else if (items == 2) TK_NORM_VEC(2);
-    else TK_NORM_VEC(4);
+    else if (items <= 4) TK_NORM_VEC(4);
+    else TK_NORM_VEC(8);
 #undef TK_NORM_VEC
     return true;
 }

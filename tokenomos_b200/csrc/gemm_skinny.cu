@@ -45,13 +45,13 @@ __device__ __forceinline__ uint4 ld_activation(const void* p) {
 
 constexpr int ROWS = 16;     // weight rows per CTA
 constexpr int KSLICE = 64;   // K elements a warp takes per iteration (128 bytes of each row)
-constexpr int UNROLL = 4;    // slices whose loads are in flight together
 
 // MT: 8 or 16 tokens (one or two n8 tiles). R8: the CTA owns 8 weight rows instead of 16 (the
 // upper half of the mma tile stays zero): twice as many CTAs for matrices with few rows.
 // SWIGLU: the weight rows come in blocks of 16, 8 gate rows then the 8 up rows of the same
 // channels, and the CTA writes silu(gate) * up for its 8 channels: out is [M, N / 2].
-template <int MT, typename TO, bool R8, bool SWIGLU>
+// UNROLL: slices whose loads a warp has in flight together (registers: 8 per slice and row half)
+template <int MT, typename TO, bool R8, bool SWIGLU, int UNROLL>
 __global__ void __launch_bounds__(512)
 gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                    const __nv_bfloat16* __restrict__ w, int64_t ldw, const float* __restrict__ bias,
@@ -165,6 +165,23 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
 
 }  // namespace
 
+// Tuning knobs (tk_gemm_skinny_tune; 0 = choose by shape): slices in flight per warp (2 or 4), the
+// most warps a CTA may have, and the number of 16-row CTAs below which a matrix is cut into
+// 8-row CTAs instead. Measured on a B200 in CUDA graphs at 1 and 8 tokens (2048- and 8192-wide K):
+// two slices in flight beat four (54 instead of 104 registers: four CTAs per SM, whose load,
+// compute and reduce phases overlap); a tall matrix (300 or more CTAs) wants 8 warps per CTA, a
+// short one 16 (more of K in flight per CTA); 8-row CTAs only pay below half a wave.
+static int g_unroll = 0, g_max_warps = 0, g_r8_below = -1;
+
+TK_API int tk_gemm_skinny_tune(int unroll, int max_warps, int r8_below) {
+    TK_CHECK_ARG((unroll == 0 || unroll == 2 || unroll == 4) && max_warps >= 0 && max_warps <= 16,
+                 "gemm_skinny_tune: unroll 0, 2 or 4; 0..16 warps");
+    g_unroll = unroll;
+    g_max_warps = max_warps;
+    g_r8_below = r8_below;
+    return 0;
+}
+
 // x: [M, K] bfloat16, rows `ldx` apart; w: [N, K] bfloat16, rows `ldw` apart; out: [M, N]
 // bfloat16 or float (out_dtype); M <= 16; K, ldx, ldw multiples of 8 and 16-byte aligned bases.
 // swiglu != 0: w holds blocks of 8 gate rows followed by the 8 up rows of the same channels
@@ -179,19 +196,28 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
     TK_CHECK_ARG(!swiglu || N % 16 == 0, "gemm_skinny: the fused SwiGLU needs N (%d) in blocks of 16", N);
     if (M == 0) return 0;
     const int slices = (K + KSLICE - 1) / KSLICE;
-    int warps = (slices + UNROLL - 1) / UNROLL;      // every slice of a warp in flight at once
-    warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
+    const int ctas16 = (N + ROWS - 1) / ROWS;
+    const int unroll = g_unroll ? g_unroll : 2;
+    const int max_warps = g_max_warps ? g_max_warps : (ctas16 >= 296 ? 8 : 16);
+    int warps = (slices + unroll - 1) / unroll;      // every slice of a warp in flight at once
+    warps = warps < 1 ? 1 : (warps > max_warps ? max_warps : warps);
     const int threads = warps * 32;
-    // few rows: 8 per CTA so that the grid still covers the GPU
-    const bool r8 = !swiglu && (N + ROWS - 1) / ROWS < 296;
+    // very few rows: 8 per CTA so that the grid still covers the GPU
+    const bool r8 = !swiglu && ctas16 < (g_r8_below >= 0 ? g_r8_below : 74);
     const int blocks = r8 ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
     const int MT = M <= 8 ? 8 : 16;
     const size_t smem = (size_t)warps * ROWS * MT * sizeof(float);
     auto x_ = (const __nv_bfloat16*)x;
     auto w_ = (const __nv_bfloat16*)w;
 #define TK_SKINNY(MT_, TO_, R8_, SW_)                                                              \
-    tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_>, dim3(blocks), dim3(threads), smem, stream, x_, ldx, \
-              w_, ldw, bias, (TO_*)out, ldo, M, N, K)
+    do {                                                                                           \
+        if (unroll == 2)                                                                           \
+            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 2>, dim3(blocks), dim3(threads), smem, stream, \
+                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K);                            \
+        else                                                                                       \
+            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 4>, dim3(blocks), dim3(threads), smem, stream, \
+                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K);                            \
+    } while (0)
 #define TK_SKINNY_T(TO_)                                                                           \
     do {                                                                                           \
         if (swiglu) { if (MT == 8) TK_SKINNY(8, TO_, false, true); else TK_SKINNY(16, TO_, false, true); } \

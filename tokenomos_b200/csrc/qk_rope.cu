@@ -97,7 +97,6 @@ TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_ou
     // one warp per head; with few tokens the heads spread over more blocks so the GPU fills
     const int heads = H + 2 * Hkv;
     int per_token = (heads + 3) / 4;
-    if ((long long)T_ * per_token > 4096) per_token = 1 > 4096 / T_ ? 1 : 4096 / T_;
     const dim3 grid(T_, per_token);
     if (dtype == TK_F32)
         tk_launch(qk_norm_rope_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, 

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
+    "tk_gemm_skinny_tune": [I, I, I],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_select_ids": [P, P, P, P, P, I, P],
     "tk_gemm_tc_status": [],
@@ -90,7 +91,7 @@ def calls() -> int:
     return _calls
 
 
-_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_attn_generic_rows", "tk_conv_min_tile",
+_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status"}
 
 
