@@ -289,7 +289,12 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
             cache.extend(r, ctx)
             cache.commit(r, ctx)
     g = torch.Generator().manual_seed(0)
-    if mode == "decode":
+    if mode == "decode_graph":
+        # the captured decode step exactly as serving replays it (token select ... sampling)
+        rows = [(0.0, 1.0, 0, 0.0, 0, 0)] * batch
+        for _ in range(steps):
+            step_fn.run_decode_graph([StepEntry(r, [1 + r], []) for r in range(batch)], rows, commit=True)
+    elif mode == "decode":
         for _ in range(steps):
             step_fn.run([StepEntry(r, [int(torch.randint(0, 1000, (1,), generator=g))], [0])
                          for r in range(batch)])
@@ -305,7 +310,7 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+    ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill"],
                     help="run only a small case for a profiler (see profile_case) and exit")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
     ap.add_argument("--gpus", type=int, default=1)

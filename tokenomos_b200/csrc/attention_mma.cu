@@ -89,6 +89,49 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* po
     }
 }
 
+// The same load for page sizes that are a power of two, which is what the engine uses: a thread
+// owns one 16-byte column of ROWS / (NT / CH) rows of every tile, so everything but the page
+// lookup is computed once per kernel instead of once per 16 bytes. Keys and values of a row share
+// the lookup (the value row lies a constant distance behind the key row).
+template <int D, int ROWS, int NT>
+struct PagedLoader {
+    static constexpr int CH = D / 8;
+    static constexpr int STEP = NT / CH;          // rows between a thread's consecutive rows
+    static constexpr int PER = ROWS / STEP;       // rows per thread per tile
+    uint32_t dst[PER];                            // swizzled byte offsets inside a tile
+    int r0;
+    size_t head_off, v_delta, page_stride;
+    int p_shift, p_mask;
+
+    __device__ __forceinline__ void init(int tid, int kvh, int Hkv, int P, int shift) {
+        const int c = tid % CH;
+        r0 = tid / CH;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) dst[k] = tile_off<D>(r0 + k * STEP, c);
+        head_off = (size_t)kvh * P * D + (size_t)c * 8;
+        v_delta = (size_t)Hkv * P * D;
+        page_stride = (size_t)2 * Hkv * P * D;
+        p_shift = shift;
+        p_mask = P - 1;
+    }
+
+    __device__ __forceinline__ void issue(uint32_t ktile, uint32_t vtile, const __nv_bfloat16* pool,
+                                          const int* bt_row, int j0, int j_first, int j_last) const {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int j = j0 + r0 + k * STEP;
+            const bool valid = j >= j_first && j <= j_last;
+            const __nv_bfloat16* src = pool;
+            if (valid) {
+                const int page = bt_row[j >> p_shift];
+                src = pool + (size_t)page * page_stride + head_off + (size_t)(j & p_mask) * D;
+            }
+            cp_async16(ktile + dst[k], src, valid);
+            cp_async16(vtile + dst[k], valid ? src + v_delta : src, valid);
+        }
+    }
+};
+
 constexpr float LOG2E = 1.4426950408889634f;
 
 // 2^x on the special-function unit (about 2 ulp in 32-bit, far below the bfloat16 rounding of P);
@@ -210,7 +253,8 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfl
         const int r = row0 + g + 8 * half;
         const bool ok = r < rows;
         const __nv_bfloat16* src = q;
-        if (ok) src = q + ((size_t)(tok0 + r / G) * H + h0 + r % G) * D;
+        const int gs = 31 - __clz(G);                 // the group size is a power of two
+        if (ok) src = q + ((size_t)(tok0 + (r >> gs)) * H + h0 + (r & (G - 1))) * D;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             uint32_t lo = 0u, hi = 0u;
@@ -234,7 +278,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                         const int* tok_seq, const int* block_table,
                         int bt_stride, const int* tile_tok0,
                         const int* tile_ntok, int H, int Hkv, int P, int window,
-                        float scale) {
+                        float scale, int p_shift) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -272,11 +316,17 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const float scale_log2 = scale * LOG2E;
 
     const int n_tiles = (pos_last - j_begin) / 64 + 1;
+    PagedLoader<D, 64, 128> loader;
+    loader.init(tid, kvh, Hkv, P, p_shift);
     auto issue = [&](int it) {
         const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
         const int j0 = j_begin + it * 64;
-        load_tile<D>(base, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
-        load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+        if (p_shift >= 0) {
+            loader.issue(base, base + TILE_BYTES, pool, bt_row, j0, lo, pos_last);
+        } else {
+            load_tile<D>(base, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
+            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+        }
         cp_async_commit();
     };
     issue(0);
@@ -325,7 +375,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                        const int* tok_seq, const int* block_table,
                        int bt_stride, const int* tok_index, int H, int Hkv, int P,
                        int window, float scale, int nsplit, float* part_o,
-                       float* part_ml) {
+                       float* part_ml, int p_shift) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -358,11 +408,17 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
 
     // the warp's private double buffer: [stage][K|V][32][D]
     const uint32_t wbase = smem_u32(smem_raw) + (uint32_t)warp * 4 * TILE_BYTES;
+    PagedLoader<D, 32, 32> loader;
+    loader.init(lane, kvh, Hkv, P, p_shift);
     auto issue = [&](int tile, int stage) {
         const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
         const int j0 = j_begin + tile * 32;
-        load_tile<D>(base, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 0, lane, 32);
-        load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 1, lane, 32);
+        if (p_shift >= 0) {
+            loader.issue(base, base + TILE_BYTES, pool, bt_row, j0, lo, pos);
+        } else {
+            load_tile<D>(base, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 0, lane, 32);
+            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 1, lane, 32);
+        }
         cp_async_commit();
     };
     int stage = 0;
@@ -453,6 +509,14 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
     out[((size_t)tok_index[i] * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
+// log2 of a power-of-two page size, else -1 (the kernels then divide per 16-byte request)
+int page_shift(int P) {
+    if (P <= 0 || (P & (P - 1))) return -1;
+    int s = 0;
+    while ((1 << s) < P) ++s;
+    return s;
+}
+
 bool mma_shape_ok(int H, int Hkv, int D) {
     if (Hkv <= 0 || H % Hkv) return false;
     const int G = H / Hkv;
@@ -485,11 +549,11 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
     if (D == 64) {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
+                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P));
     } else {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale);
+                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P));
     }
     TK_CHECK_LAUNCH("attn_prefill_mma");
     return 0;
@@ -523,14 +587,14 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
     if (D == 64) {
         cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
+                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
             tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
     } else {
         cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml);
+                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
             tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);

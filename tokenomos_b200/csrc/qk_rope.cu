@@ -21,9 +21,19 @@ __global__ void qk_norm_rope_write_kernel(
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int head_first = blockIdx.y * nwarp + warp, head_step = gridDim.y * nwarp;
-    float* buf = smem + warp * D;
     const int pos = positions[t];
     const int half = R >> 1;
+    // cos / sin of this token's angles, once per block (they do not depend on the head)
+    float* cs = smem;
+    float* sn = smem + half;
+    float* buf = smem + 2 * half + warp * D;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s_, c_;
+        sincosf((float)pos * inv_freq[i], &s_, &c_);
+        cs[i] = round_as<T>(c_);
+        sn[i] = round_as<T>(s_);
+    }
+    __syncthreads();
     size_t cache_row = 0;
     if (Hkv > 0) {
         const int s = tok_seq[t];
@@ -68,10 +78,8 @@ __global__ void qk_norm_rope_write_kernel(
             float o = buf[c];
             if (c < R) {
                 const int i = c < half ? c : c - half;
-                const float f = (float)pos * inv_freq[i];
-                const float cs = round_as<T>(cosf(f)), sn = round_as<T>(sinf(f));
                 const float rot = c < half ? -buf[c + half] : buf[c - half];
-                o = o * cs + rot * sn;
+                o = o * cs[i] + rot * sn[i];
             }
             dst[c] = from_f<T>(o);
         }
@@ -92,11 +100,13 @@ TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_ou
     TK_CHECK_ARG((wq == nullptr) == (wk == nullptr) || Hkv == 0,
                  "qk_norm_rope_write: q and k norms come together");
     if (T_ == 0) return 0;
-    const int threads = 128;
-    const size_t smem = (size_t)(threads / 32) * D * sizeof(float);
-    // one warp per head; with few tokens the heads spread over more blocks so the GPU fills
+    // one warp per head at a time; with few tokens the heads spread over more blocks so the GPU
+    // fills, with many one block takes all heads of a token (the angles are computed once)
     const int heads = H + 2 * Hkv;
-    int per_token = (heads + 3) / 4;
+    const int threads = T_ >= 1024 ? 256 : 128;
+    const int warps = threads / 32;
+    const int per_token = T_ >= 1024 ? 1 : (heads + warps - 1) / warps;
+    const size_t smem = ((size_t)R + (size_t)warps * D) * sizeof(float);
     const dim3 grid(T_, per_token);
     if (dtype == TK_F32)
         tk_launch(qk_norm_rope_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, 

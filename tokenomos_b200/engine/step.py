@@ -203,8 +203,9 @@ class StepFunction:
         self._ring_pos = 0
         self.steps = 0
 
-    def _upload(self, values: list[int]) -> torch.Tensor:
-        """Host ints -> device int32 tensor through pinned memory, without a sync."""
+    def _upload(self, values) -> torch.Tensor:
+        """Host ints (a list, or a numpy int32 array) -> device int32 tensor through pinned
+        memory, without a sync."""
         n = len(values)
         i = self._ring_pos
         self._ring_pos = (i + 1) % len(self._ring)
@@ -215,7 +216,7 @@ class StepFunction:
             self._ring_events[i] = None
         if self._ring_events[i] is not None:
             self._ring_events[i].synchronize()
-        buf[:n] = torch.tensor(values, dtype=torch.int32)
+        buf.numpy()[:n] = values
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         out.copy_(buf[:n], non_blocking=True)
         self.h2d_bytes += 4 * n
@@ -262,20 +263,25 @@ class StepFunction:
         cu = [0]
         for n in seq_lens:
             cu.append(cu[-1] + n)
-        positions, tok_seq, ids, want = [], [], [], []
+        want = []
         for s, e in enumerate(entries):
-            positions.extend(range(seq_ctx[s], seq_ctx[s] + seq_lens[s]))
-            tok_seq.extend([s] * seq_lens[s])
-            ids.extend(e.tokens)
             want.extend(cu[s] + w for w in e.want)
+        lens_np = np.asarray(seq_lens, dtype=np.int32)
+        starts = np.repeat(np.asarray(seq_ctx, dtype=np.int32) - np.asarray(cu[:-1], dtype=np.int32), lens_np)
+        positions = np.arange(T, dtype=np.int32) + starts
+        tok_seq = np.repeat(np.arange(S, dtype=np.int32), lens_np)
+        ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=T)
         groups = list(cache.groups)
         width = max(1, max(-(-(c + n) // cache.page_size) for c, n in zip(seq_ctx, seq_lens)))
-        tables = []
-        for g in groups:
-            for e in entries:
+        tables = np.zeros((len(groups), S, width), dtype=np.int32)
+        for gi, g in enumerate(groups):
+            for si, e in enumerate(entries):
                 row = cache.block_table(e.rid, g)
-                tables.extend(row[:width] + [0] * (width - len(row)))
-        flat = self._upload(positions + tok_seq + cu + seq_ctx + seq_slot + ids + want + tables)
+                tables[gi, si, :min(width, len(row))] = row[:width]
+        flat = self._upload(np.concatenate((
+            positions, tok_seq, np.asarray(cu, dtype=np.int32), np.asarray(seq_ctx, dtype=np.int32),
+            np.asarray(seq_slot, dtype=np.int32), ids, np.asarray(want, dtype=np.int32),
+            tables.reshape(-1))))
         o = 0
 
         def take(n):
