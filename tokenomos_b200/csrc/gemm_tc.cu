@@ -21,9 +21,12 @@
 // Every wait on an mbarrier is bounded: after about a second the kernel records where it gave
 // up in an error word, skips the rest of its work, frees its tensor memory and returns; the
 // host reads the word through tk_gemm_tc_status().
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -132,7 +135,7 @@ template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                TO* out, int64_t ldo, const float* __restrict__ bias, int rows_a, int rows_b, int K,
-               int stages, int splitk, float* scratch, int* counters) {
+               int stages, int splitk, float* scratch, int* counters, int cluster_k) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int B_TILE_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
@@ -273,7 +276,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         };
         const bool have = ok && n_kb > 0;
-        if (splitk == 1) {
+        if (cluster_k > 1) {
+            // split K over a cluster: this CTA's partial tile goes to its own shared memory
+            // (the pipeline stages are done with: every MMA that read them has completed)
+            float* mine = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            const int row_local = lane_group * 32 + lane;
+            for (int c = 0; c < BN; c += 16) {
+                float part[16];
+                if (have) {
+                    tmem_ld16(tmem_d + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c, part);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) part[e] = 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) mine[(c + e) * BM + row_local] = part[e];
+            }
+        } else if (splitk == 1) {
             for (int c = 0; c < BN; c += 16) {
                 float part[16];
                 if (have) {
@@ -316,6 +335,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (epi_tid == 0) counters[tile_id] = 0;
             }
         }
+    }
+    if (cluster_k > 1) {
+        // every CTA of the cluster holds a partial [BN][128] tile; rank r sums rows
+        // [r * 128 / k, (r + 1) * 128 / k) over all ranks through distributed shared memory
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (warp >= 2) {
+            float* mine = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            const int share = BM / cluster_k;
+            const int row_begin = (int)cluster.block_rank() * share;
+            const int epi_tid = (warp - 2) * 32 + lane;
+            auto total = [&](int row, int col) -> float {
+                float v = 0.f;
+                for (int r = 0; r < cluster_k; ++r) v += cluster.map_shared_rank(mine, r)[col * BM + row];
+                return v;
+            };
+            if (TRANSPOSED && SWIGLU) {
+                const int gates = share / 2;               // gate rows in the share (8 of every 16)
+                for (int idx = epi_tid; idx < gates * BN; idx += 128) {
+                    const int col = idx / gates, gi = idx % gates;
+                    const int row = row_begin + (gi / 8) * 16 + gi % 8;
+                    const int i_row = a_row0 + row, jj = b_row0 + col;
+                    if (i_row + 8 < rows_a && jj < rows_b) {
+                        float gate = total(row, col), up = total(row + 8, col);
+                        if (bias != nullptr) {
+                            gate += bias[i_row];
+                            up += bias[i_row + 8];
+                        }
+                        gate = round_as<TO>(gate);
+                        up = round_as<TO>(up);
+                        const float act = round_as<TO>(gate / (1.0f + expf(-gate)));
+                        out[(size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7)] = from_f<TO>(act * up);
+                    }
+                }
+            } else {
+                for (int idx = epi_tid; idx < share * BN; idx += 128) {
+                    const int col = idx / share, row = row_begin + idx % share;   // rows fastest
+                    const int i_row = a_row0 + row, jj = b_row0 + col;
+                    if (i_row < rows_a && jj < rows_b) {
+                        float v = total(row, col);
+                        if (TRANSPOSED) {
+                            if (bias != nullptr) v += bias[i_row];
+                            out[(size_t)jj * ldo + i_row] = from_f<TO>(v);
+                        } else {
+                            if (bias != nullptr) v += bias[jj];
+                            out[(size_t)i_row * ldo + jj] = from_f<TO>(v);
+                        }
+                    }
+                }
+            }
+        }
+        cluster.sync();      // nobody's shared memory goes away while a peer still reads it
     }
     // ---- teardown: the tensor memory goes back whatever happened above ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -361,15 +432,45 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t ld, i
 template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
 cudaError_t launch_tc(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& ma,
                       const CUtensorMap& mb, TO* out, int64_t ldo, const float* bias, int rows_a,
-                      int rows_b, int K, int stages, int splitk, float* scratch, int* counters) {
+                      int rows_b, int K, int stages, int splitk, float* scratch, int* counters,
+                      int cluster_k) {
     auto kernel = gemm_tc_kernel<BN, TRANSPOSED, SWIGLU, TO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    return tk_launch(kernel, grid, dim3(TC_THREADS), smem, stream, ma, mb, out, ldo, bias, rows_a, rows_b, K,
-                     stages, splitk, scratch, counters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (tk_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_k > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = cluster_k;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, out, ldo, bias, rows_a, rows_b, K, stages, splitk, scratch,
+                              counters, cluster_k);
 }
 
 }  // namespace
+
+// How K is split: 0 = by cluster when it fits (default), 1 = always through the scratch
+// (atomics), 2 = never split. For measurements.
+static int g_tc_split_mode = 0;
+TK_API int tk_gemm_tc_split_mode(int mode) {
+    g_tc_split_mode = mode;
+    return 0;
+}
 
 // 0 if no tensor-core GEMM on the current device has given up on a barrier since the last call;
 // else the place it gave up (1 producer, 2 MMA issuer, 3 epilogue). Resets the word.
@@ -403,22 +504,31 @@ TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t 
                  "gemm_tc_decode: cuTensorMapEncodeTiled failed (N=%d K=%d ldw=%lld)", N, K, (long long)ldw);
     const int a_tiles = (N + BM - 1) / BM;
     const int kb_total = (K + BK - 1) / BK;
+    // split K until there are about two CTAs per SM or slices of 4 k-blocks. Up to 8 ways the
+    // partial tiles are reduced inside a cluster (distributed shared memory: no scratch, no
+    // atomics); beyond that, through the scratch.
     int splitk = 1;
-    if (scratch != nullptr) {
-        while (a_tiles * splitk < 2 * 148 && kb_total / (splitk * 2) >= 4) splitk *= 2;
+    const int max_split = (g_tc_split_mode == 1 && scratch != nullptr) ? 64 : 8;
+    while (splitk < max_split && a_tiles * splitk < 2 * 148 && kb_total / (splitk * 2) >= 4) splitk *= 2;
+    int cluster_k = (splitk > 1 && g_tc_split_mode != 1) ? splitk : 0;
+    if (cluster_k == 0 && scratch == nullptr) splitk = 1;
+    if (g_tc_split_mode == 2) {
+        splitk = 1;
+        cluster_k = 0;
     }
     const int kb_per = (kb_total + splitk - 1) / splitk;
     const int stage_bytes = A_TILE_BYTES + BN * BK * 2;
     int stages = kb_per < 6 ? kb_per : 6;
     while (stages > 2 && (size_t)stages * stage_bytes > 160 * 1024) --stages;
-    const size_t smem = (size_t)stages * stage_bytes + (2 * stages + 2) * 8 + 1024 + 64;
+    size_t smem = (size_t)stages * stage_bytes + (2 * stages + 2) * 8 + 1024 + 64;
+    if (smem < (size_t)BN * BM * 4 + 1024 + 256) smem = (size_t)BN * BM * 4 + 1024 + 256;
     const dim3 grid(a_tiles, 1, splitk);
     float* sc = (float*)scratch;
     int* counters = scratch ? (int*)((char*)scratch + (size_t)tokens * N * 4) : nullptr;
     cudaError_t err = cudaSuccess;
 #define TK_TC(BN_, SW_, TO_)                                                                        \
     err = launch_tc<BN_, true, SW_, TO_>(grid, smem, stream, ma, mb, (TO_*)out, ldo, bias, N, tokens, K, \
-                                         stages, splitk, sc, counters)
+                                         stages, splitk, sc, counters, splitk == 1 ? 0 : cluster_k)
 #define TK_TC_BN(SW_, TO_)                                                                          \
     switch (BN) {                                                                                   \
         case 16: TK_TC(16, SW_, TO_); break;                                                        \

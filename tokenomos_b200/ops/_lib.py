@@ -44,6 +44,7 @@ _SIGNATURES = {
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_select_ids": [P, P, P, P, P, I, P],
     "tk_gemm_tc_status": [],
+    "tk_gemm_tc_split_mode": [I],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
 }
 
@@ -92,7 +93,7 @@ def calls() -> int:
 
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
-            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status"}
+            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status", "tk_gemm_tc_split_mode"}
 
 
 def call(name: str, *args) -> int:
