@@ -42,6 +42,20 @@ CONFIG_1P2B = {
 PROMPT = 2048
 CONTEXT = 4096
 
+# BASELINE.json configs[3] and configs[4]: serving workloads on the 350M- and 2.6B-size models
+ATTN_AT_16 = (2, 5, 8, 10, 12, 14)
+ATTN_AT_30 = (2, 6, 10, 14, 18, 21, 24, 27)
+WORKLOADS = {
+    "mixed350m": dict(
+        config={**CONFIG_1P2B, "hidden_size": 1024, "num_attention_heads": 16, "intermediate_size": 4608,
+                "layer_types": ["full_attention" if i in ATTN_AT_16 else "conv" for i in range(16)]},
+        requests=256, prompt=(64, 2048), new_tokens=256, max_len=4096, slots=256, budget=2048),
+    "chunked2p6b": dict(
+        config={**CONFIG_1P2B, "num_hidden_layers": 30, "intermediate_size": 10752,
+                "layer_types": ["full_attention" if i in ATTN_AT_30 else "conv" for i in range(30)]},
+        requests=64, prompt=(4096, 4096), new_tokens=64, max_len=8192, slots=64, budget=512),
+}
+
 
 def peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
@@ -88,7 +102,7 @@ class Clocks:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def write_folder(folder: Path, layers: int) -> dict:
+def write_folder(folder: Path, layers: int, config: dict | None = None) -> dict:
     """The configuration's model folder with random weights drawn on the GPU (the same tensor
     list and order as the random-weights mode; a CPU draw of 1.2 G values takes far longer)."""
     import torch
@@ -97,9 +111,9 @@ def write_folder(folder: Path, layers: int) -> dict:
     from tokenomos_b200 import models
     from tokenomos_b200.weights import random_tensors
 
-    config = dict(CONFIG_1P2B)
+    config = dict(config or CONFIG_1P2B)
     config["layer_types"] = config["layer_types"][:layers]
-    config["num_hidden_layers"] = layers
+    config["num_hidden_layers"] = len(config["layer_types"])
     arch = models.architecture_of(config)
     decls = arch.declare(arch.config_class.from_dict(config)).tensor_decls()
     tensors = random_tensors(decls, seed=0, std=0.02, dtype=torch.bfloat16, device="cuda")
@@ -308,8 +322,61 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
     print(f"profile case done: {mode} layers={layers} batch={batch} ctx={ctx} steps={steps}")
 
 
+def run_workload(name: str, page: int) -> int:
+    """A whole serving workload through ``LLM.generate`` (continuous batching: prompts are cut
+    into portions under the token budget and run beside the decoding requests): wall-clock
+    tokens per second, prompt and generated."""
+    import tempfile
+
+    import torch
+
+    from tokenomos_b200.api.llm import LLM, SamplingParams
+
+    w = WORKLOADS[name]
+    tmp = tempfile.TemporaryDirectory(prefix="tokenomos_b200_bench_")
+    folder = Path(tmp.name) / name
+    write_folder(folder, len(w["config"]["layer_types"]), w["config"])
+    g = torch.Generator().manual_seed(0)
+    lo, hi = w["prompt"]
+    lengths = torch.randint(lo, hi + 1, (w["requests"],), generator=g).tolist()
+    vocab = w["config"]["vocab_size"]
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+    pages = sum(-(-(n + w["new_tokens"] + 1) // page) for n in lengths) + 2
+    llm = LLM(str(folder), work="bf16", slots=w["slots"], page=page, max_len=w["max_len"], pages=pages,
+              prefill_budget=w["budget"], graphs=True)
+    clocks = Clocks()
+    try:
+        llm.generate(prompts[:2], SamplingParams(max_tokens=4))          # warm-up: builds, library handles
+        clocks.start()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, SamplingParams(max_tokens=w["new_tokens"]))
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+    finally:
+        clock_report = clocks.stop()
+        stats = llm.engine.stats
+        llm.close()
+        tmp.cleanup()
+    generated = sum(len(o.token_ids) for o in outs)
+    print(json.dumps({
+        "workload": name, "metric": "tokens/s over the whole call (prompt + generated)",
+        "value": round((sum(lengths) + generated) / seconds, 1), "unit": "tokens/s",
+        "generated_per_s": round(generated / seconds, 1), "seconds": round(seconds, 3),
+        "requests": w["requests"], "prompt_tokens": sum(lengths), "generated": generated,
+        "steps": stats.steps, "decode_steps": stats.decode_steps, "preemptions": stats.preemptions,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": {"layers": len(w["config"]["layer_types"]), "hidden_size": w["config"]["hidden_size"],
+                   "intermediate_size": w["config"]["intermediate_size"], "max_len": w["max_len"],
+                   "slots": w["slots"], "token_budget": w["budget"], "page_size": page},
+        "clocks": clock_report}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="run a whole serving workload of BASELINE.json (configs[3] / configs[4]) instead")
     ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill"],
                     help="run only a small case for a profiler (see profile_case) and exit")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
@@ -342,6 +409,8 @@ def main() -> int:
     if args.profile:
         profile_case(args.profile, args.layers, args.batch, args.ctx, args.steps, args.page)
         return 0
+    if args.workload:
+        return run_workload(args.workload, args.page)
     pk = peaks()
     import tempfile
 

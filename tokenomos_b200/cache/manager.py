@@ -83,6 +83,9 @@ class RequestState:
     reserved: int = 0                                 # tokens pages are held for (>= length)
     tables: dict[tuple, list[int]] = field(default_factory=dict)  # group -> page per block (0: none)
     epoch: int = 0                                    # distinguishes two lives of one request id
+    # per group: blocks below this index have been given back (a window has passed them); every
+    # block from here to the end of the table holds a page
+    first_live: dict[tuple, int] = field(default_factory=dict)
 
 
 class CacheManager:
@@ -170,9 +173,9 @@ class CacheManager:
         end_block = -(-(st.length + n_new) // self.page_size)
         need = {}
         for k, g in self.groups.items():
-            table = st.tables[k]
-            lo = self._first_needed_block(g, st.length)
-            have = sum(1 for b in range(lo, min(len(table), end_block)) if table[b])
+            # blocks [first_live, len(table)) hold pages; the step needs [lo, end_block)
+            lo = max(self._first_needed_block(g, st.length), st.first_live.get(k, 0))
+            have = max(0, min(len(st.tables[k]), end_block) - lo)
             need[k] = max(0, end_block - lo - have)
         return need
 
@@ -195,12 +198,9 @@ class CacheManager:
         end_block = -(-(st.length + n_new) // self.page_size)
         for k, g in self.groups.items():
             table = st.tables[k]
-            lo = self._first_needed_block(g, st.length)
-            while len(table) < end_block:
-                table.append(0)
-            for b in range(lo, end_block):
-                if not table[b]:
-                    table[b] = g.pages.take()
+            # a table only grows at its end: blocks behind a window were given back for good
+            for _ in range(len(table), end_block):
+                table.append(g.pages.take())
         st.reserved = max(st.reserved, st.length + n_new)
 
     def commit(self, rid, n_new: int) -> None:
@@ -213,10 +213,11 @@ class CacheManager:
             if g.window is None:
                 continue
             table = st.tables[k]
-            for b in range(min(self._first_needed_block(g, st.length), len(table))):
-                if table[b]:
-                    g.pages.give(table[b])
-                    table[b] = 0
+            passed = min(self._first_needed_block(g, st.length), len(table))
+            for b in range(st.first_live.get(k, 0), passed):
+                g.pages.give(table[b])
+                table[b] = 0
+            st.first_live[k] = max(st.first_live.get(k, 0), passed)
 
     def release(self, rid) -> None:
         """The request ended: its pages and its slot go back."""

@@ -35,7 +35,7 @@ from tokenomos_b200.cache.manager import CacheManager, OutOfPages
 MAX_STOPS = 8
 
 
-@dataclass
+@dataclass(eq=False)      # requests are compared by identity (membership tests in the queues)
 class Request:
     """One generation request (names as Tokenomos core/engine.py:50-66)."""
 

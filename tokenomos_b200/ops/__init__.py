@@ -47,7 +47,8 @@ def _ptr(t: torch.Tensor | None):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of torch's current stream (a capture's side stream included)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _i32(t: torch.Tensor, name: str) -> torch.Tensor:

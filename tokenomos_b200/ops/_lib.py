@@ -96,13 +96,18 @@ _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tun
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status", "tk_gemm_tc_split_mode"}
 
 
+_fns: dict = {}
+
+
 def call(name: str, *args) -> int:
     """Call an entry point; a negative return raises ``KernelError`` with the library's message."""
     global _calls
-    fn = getattr(lib(), name)
-    if name not in _QUERIES:
+    fn = _fns.get(name)
+    if fn is None:
+        fn = _fns[name] = (getattr(lib(), name), name not in _QUERIES)
+    if fn[1]:
         _calls += 1
-    rc = fn(*args)
+    rc = fn[0](*args)
     if rc < 0:
         raise KernelError(f"{name}: {lib().tk_last_error().decode()}")
     return rc
