@@ -459,7 +459,8 @@ def main() -> int:
             "l2": "inputs larger than L2 (weights read every step)",
         },
         "clocks": clock_report,
-        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "e2e": {k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v)
+                for k, v in e2e.items()},
         "gpu_launches": main_run["launches_per_step"] * args.steps,
         "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
                     "frac": round(prefill["flops"] / (prefill["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
