@@ -51,7 +51,15 @@ class Attention:
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
-        qkv = self.qkv(x)
+        out = self._core(self.qkv(x), ctx, call)
+        if self.gate is not None:
+            ops.head_gate(out, self.gate(x).contiguous(), self.heads, self.head_dim)
+        return self.o(out.view(T, self.heads * self.head_dim))
+
+    def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+        """From the fused projection's output to the heads' outputs [T, H, D] (into ``out`` if
+        given): q/k norm, rotation, cache write, attention over the cache."""
         pool = ctx.states[(call, "kv")]
         table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
         own_kv = 0 if self.kv_source is not None else self.kv_heads
@@ -60,18 +68,17 @@ class Attention:
             self.eps, self.rope.tables(ctx), ctx.positions, ctx.tok_seq,
             table if own_kv else None, self.heads, own_kv, self.head_dim, ctx.page_size)
         if ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
-            out = self._attend_mma(q, pool, table, ctx)
-        else:
-            rows = ops.attention_rows()
-            group = self.heads // self.kv_heads
-            per_tile = max(1, rows // group)
-            _, tok0, _, ntok = ctx.tiles(per_tile)
-            out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
-                                self.window, self.scale)
-        if self.gate is not None:
-            ops.head_gate(out, self.gate(x).contiguous(), self.heads, self.head_dim)
-        return self.o(out.view(T, self.heads * self.head_dim))
-
+            return self._attend_mma(q, pool, table, ctx, out)
+        rows = ops.attention_rows()
+        group = self.heads // self.kv_heads
+        per_tile = max(1, rows // group)
+        _, tok0, _, ntok = ctx.tiles(per_tile)
+        res = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
+                            self.window, self.scale)
+        if out is None:
+            return res
+        out.copy_(res.view_as(out))
+        return out
 
     # CTAs the decode kernel should put on the GPU before it stops splitting keys further: three
     # fit on an SM (shared memory), and several waves of them even out the last, partial wave
@@ -79,10 +86,11 @@ class Attention:
     # fewest keys worth a CTA of their own
     DECODE_MIN_KEYS = 256
 
-    def _attend_mma(self, q, pool, table, ctx: StepContext) -> torch.Tensor:
+    def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
         over their keys so that a small batch still fills the GPU."""
-        out = torch.empty_like(q)
+        if out is None:
+            out = torch.empty_like(q)
         per_tile = ops.attention_prefill_mma_tokens(self.heads, self.kv_heads)
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
         if tok0.numel():
