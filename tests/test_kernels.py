@@ -49,6 +49,21 @@ def test_gather_rows(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [100, 2048])
+def test_gather_rows_select(dtype, width):
+    """Row r reads the id the host gave, or the one an earlier step left for its slot."""
+    from tokenomos_b200 import ops
+    table = torch.randn(41, width).to(dtype)
+    ids_host = [3, 40, 7, 0, 9]
+    use_prev = [0, 1, 1, 0, 1]
+    slot = [2, 5, 1, 4, 3]
+    last = [11, 12, 13, 14, 15, 16, 17]
+    out = ops.gather_rows_select(dev(table), i32(ids_host), i32(use_prev), i32(last), i32(slot))
+    want = [last[slot[r]] if use_prev[r] else ids_host[r] for r in range(5)]
+    assert torch.equal(out.cpu(), table[want])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [100, 2048, 5000])
 @pytest.mark.parametrize("residual, pre", [(False, False), (True, False), (True, True)])
 def test_add_rmsnorm(dtype, width, residual, pre):

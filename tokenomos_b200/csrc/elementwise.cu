@@ -46,6 +46,50 @@ TK_API int tk_gather_rows(const void* table, const int* ids, void* out, int rows
     return 0;
 }
 
+// The decode step's embedding lookup with the choice of the id in the same kernel: row r reads
+// the token the step before sampled for its sequence (last_token[slot[r]]) when use_prev[r] is
+// set, else the id the host gave; so a step can be queued before the host has seen that token.
+template <typename T>
+__global__ void gather_rows_select_kernel(const T* table, const int* ids_host, const int* use_prev,
+                                          const int* last_token, const int* slot, T* out, int width,
+                                          int rows_in_table) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    int id = use_prev[r] ? last_token[slot[r]] : ids_host[r];
+    id = id < 0 ? 0 : (id >= rows_in_table ? rows_in_table - 1 : id);
+    const T* src = table + (size_t)id * width;
+    T* dst = out + (size_t)r * width;
+    constexpr int VEC = 16 / sizeof(T);
+    if (width % VEC == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < width / VEC; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+TK_API int tk_gather_rows_select(const void* table, const int* ids_host, const int* use_prev,
+                                 const int* last_token, const int* slot, void* out, int rows, int width,
+                                 int rows_in_table, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0 && rows_in_table > 0, "gather_rows_select: bad sizes rows=%d width=%d table=%d",
+                 rows, width, rows_in_table);
+    if (rows == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == TK_F32)
+        tk_launch(gather_rows_select_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)table,
+                  ids_host, use_prev, last_token, slot, (float*)out, width, rows_in_table);
+    else if (dtype == TK_BF16)
+        tk_launch(gather_rows_select_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream,
+                  (const __nv_bfloat16*)table, ids_host, use_prev, last_token, slot, (__nv_bfloat16*)out, width,
+                  rows_in_table);
+    else
+        TK_CHECK_ARG(false, "gather_rows_select: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("gather_rows_select");
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // add + RMSNorm: stream = round(residual + [prenorm](x)); y = round(round(stream*rstd) * w)
 // One block per row; the row lives in shared memory as float. `x` may be a strided view.

@@ -268,41 +268,83 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int share = BM / cluster_k;
             const int row_begin = (int)cluster.block_rank() * share;
             const int epi_tid = (warp - 2) * 32 + lane;
-            auto total = [&](int row, int col) -> float {
-                float v = 0.f;
-                for (int r = 0; r < cluster_k; ++r) v += cluster.map_shared_rank(mine, r)[col * BM + row];
-                return v;
+            // four consecutive rows of one column, summed over the ranks: the remote loads of a
+            // thread are independent 16-byte reads, all in flight together
+            auto total4 = [&](int row, int col, float (&v)[4]) {
+                float4 part[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (r < cluster_k)
+                        part[r] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(mine, r) + col * BM + row);
+                v[0] = v[1] = v[2] = v[3] = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (r < cluster_k) {
+                        v[0] += part[r].x;
+                        v[1] += part[r].y;
+                        v[2] += part[r].z;
+                        v[3] += part[r].w;
+                    }
+            };
+            // four consecutive elements of a row of `out`
+            auto store4 = [&](TO* dst, const float (&v)[4], int n_ok) {
+                if (n_ok == 4 && ((uintptr_t)dst % (4 * sizeof(TO))) == 0) {
+                    if constexpr (sizeof(TO) == 2) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                        uint2 raw;
+                        raw.x = *reinterpret_cast<uint32_t*>(&lo);
+                        raw.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(dst) = raw;
+                    } else {
+                        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                    }
+                } else {
+                    for (int e = 0; e < n_ok; ++e) dst[e] = from_f<TO>(v[e]);
+                }
             };
             if (TRANSPOSED && SWIGLU) {
-                const int gates = share / 2;               // gate rows in the share (8 of every 16)
-                for (int idx = epi_tid; idx < gates * BN; idx += 128) {
-                    const int col = idx / gates, gi = idx % gates;
-                    const int row = row_begin + (gi / 8) * 16 + gi % 8;
+                const int groups = share / 8;              // runs of 4 gate rows in the share
+                for (int idx = epi_tid; idx < groups * BN; idx += 128) {
+                    const int col = idx / groups, g = idx % groups;
+                    const int row = row_begin + (g >> 1) * 16 + (g & 1) * 4;
                     const int i_row = a_row0 + row, jj = b_row0 + col;
                     if (i_row + 8 < rows_a && jj < rows_b) {
-                        float gate = total(row, col), up = total(row + 8, col);
-                        if (bias != nullptr) {
-                            gate += bias[i_row];
-                            up += bias[i_row + 8];
+                        float gate[4], up[4], res[4];
+                        total4(row, col, gate);
+                        total4(row + 8, col, up);
+                        int n_ok = 0;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (i_row + e + 8 >= rows_a) break;
+                            float gv = gate[e], uv = up[e];
+                            if (bias != nullptr) {
+                                gv += bias[i_row + e];
+                                uv += bias[i_row + e + 8];
+                            }
+                            gv = round_as<TO>(gv);
+                            uv = round_as<TO>(uv);
+                            res[e] = round_as<TO>(gv / (1.0f + expf(-gv))) * uv;
+                            ++n_ok;
                         }
-                        gate = round_as<TO>(gate);
-                        up = round_as<TO>(up);
-                        const float act = round_as<TO>(gate / (1.0f + expf(-gate)));
-                        out[(size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7)] = from_f<TO>(act * up);
+                        store4(out + (size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7), res, n_ok);
                     }
                 }
             } else {
-                for (int idx = epi_tid; idx < share * BN; idx += 128) {
-                    const int col = idx / share, row = row_begin + idx % share;   // rows fastest
+                const int groups = share / 4;
+                for (int idx = epi_tid; idx < groups * BN; idx += 128) {
+                    const int col = idx / groups, row = row_begin + (idx % groups) * 4;   // rows fastest
                     const int i_row = a_row0 + row, jj = b_row0 + col;
                     if (i_row < rows_a && jj < rows_b) {
-                        float v = total(row, col);
+                        float v[4];
+                        total4(row, col, v);
+                        const int n_ok = rows_a - i_row < 4 ? rows_a - i_row : 4;
                         if (TRANSPOSED) {
-                            if (bias != nullptr) v += bias[i_row];
-                            out[(size_t)jj * ldo + i_row] = from_f<TO>(v);
+                            if (bias != nullptr)
+                                for (int e = 0; e < n_ok; ++e) v[e] += bias[i_row + e];
+                            store4(out + (size_t)jj * ldo + i_row, v, n_ok);
                         } else {
-                            if (bias != nullptr) v += bias[jj];
-                            out[(size_t)i_row * ldo + jj] = from_f<TO>(v);
+                            const float bj = bias != nullptr ? bias[jj] : 0.f;
+                            for (int e = 0; e < n_ok; ++e) out[(size_t)(i_row + e) * ldo + jj] = from_f<TO>(v[e] + bj);
                         }
                     }
                 }
@@ -364,6 +406,19 @@ TK_API int tk_gemm_tc_split_mode(int mode) {
     return 0;
 }
 
+// Split heuristic, for measurements: K is split further while the grid has fewer than
+// `target_ctas` CTAs and a slice keeps at least `min_kb` K blocks of 64; the pipeline's stages
+// take at most `stage_kb` KB of shared memory. 0 keeps a value, a negative target restores the
+// default by batch size.
+static int g_tc_target_ctas = 0, g_tc_min_kb = 4, g_tc_stage_kb = 100;
+TK_API int tk_gemm_tc_tune(int target_ctas, int min_kb, int stage_kb) {
+    if (target_ctas > 0) g_tc_target_ctas = target_ctas;
+    if (target_ctas < 0) g_tc_target_ctas = 0;
+    if (min_kb > 0) g_tc_min_kb = min_kb;
+    if (stage_kb > 0) g_tc_stage_kb = stage_kb;
+    return 0;
+}
+
 // 0 if no tensor-core GEMM on the current device has given up on a barrier since the last call;
 // else the place it gave up (1 producer, 2 MMA issuer, 3 epilogue). Resets the word.
 TK_API int tk_gemm_tc_status() {
@@ -401,7 +456,13 @@ TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t 
     // atomics); beyond that, through the scratch.
     int splitk = 1;
     const int max_split = (g_tc_split_mode == 1 && scratch != nullptr) ? 64 : 8;
-    while (splitk < max_split && a_tiles * splitk < 2 * 148 && kb_total / (splitk * 2) >= 4) splitk *= 2;
+    // Measured on a B200 (2048- to 8192-wide matrices, CUDA graphs): up to 16 tokens two CTAs per
+    // SM's worth of slices is best; wider token tiles do better with one. The pipeline takes at
+    // most ~100 KB so that two CTAs share an SM: one CTA's prologue and epilogue hide behind the
+    // other's loads (head at 64 tokens: 64.8 us with one CTA per SM, 49.1 us with two).
+    const int target = g_tc_target_ctas > 0 ? g_tc_target_ctas : (BN <= 16 ? 2 * 148 : 148);
+    while (splitk < max_split && a_tiles * splitk < target && kb_total / (splitk * 2) >= g_tc_min_kb)
+        splitk *= 2;
     int cluster_k = (splitk > 1 && g_tc_split_mode != 1) ? splitk : 0;
     if (cluster_k == 0 && scratch == nullptr) splitk = 1;
     if (g_tc_split_mode == 2) {
@@ -411,7 +472,7 @@ TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t 
     const int kb_per = (kb_total + splitk - 1) / splitk;
     const int stage_bytes = A_TILE_BYTES + BN * BK * 2;
     int stages = kb_per < 6 ? kb_per : 6;
-    while (stages > 2 && (size_t)stages * stage_bytes > 160 * 1024) --stages;
+    while (stages > 2 && (size_t)stages * stage_bytes > (size_t)g_tc_stage_kb * 1024) --stages;
     size_t smem = (size_t)stages * stage_bytes + (2 * stages + 2) * 8 + 1024 + 64;
     if (smem < (size_t)BN * BM * 4 + 1024 + 256) smem = (size_t)BN * BM * 4 + 1024 + 256;
     const dim3 grid(a_tiles, 1, splitk);

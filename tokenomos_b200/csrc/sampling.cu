@@ -191,26 +191,6 @@ sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
     }
 }
 
-// ids[i] = use_prev[i] ? last_token[slot[i]] : ids_host[i]: a decode step takes the token the
-// step before it sampled straight from device memory when the host has not read it yet.
-__global__ void select_ids_kernel(const int* ids_host, const int* use_prev, const int* last_token,
-                                  const int* slot, int* ids, int n) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) ids[i] = use_prev[i] ? last_token[slot[i]] : ids_host[i];
-}
-
-TK_API int tk_select_ids(const int* ids_host, const int* use_prev, const int* last_token, const int* slot,
-                         int* ids, int n, cudaStream_t stream) {
-    TK_CHECK_ARG(n >= 0, "select_ids: n=%d", n);
-    if (n == 0) return 0;
-    tk_launch(select_ids_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids_host, use_prev, last_token,
-              slot, ids, n);
-    TK_CHECK_LAUNCH("select_ids");
-    return 0;
-}
-
 // logits: [rows, V] float with row stride `stride`; parameter arrays: [rows]; out: [rows] int32.
 // scatter_out (optional): also scatter_out[scatter_index[r]] = token of row r.
 TK_API int tk_sample(const float* logits, int64_t stride, int rows, int V, const float* temp,

@@ -121,7 +121,6 @@ class _DecodeGraph:
         self.tokens_host = [torch.zeros(b, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.turn = 0
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
-        self.ids = torch.zeros(b, dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(b, dtype=torch.int32, device=dev)
         arange = torch.arange(b + 1, dtype=torch.int32, device=dev)
         zeros = torch.zeros(b, dtype=torch.int32, device=dev)
@@ -140,7 +139,7 @@ class _DecodeGraph:
             host=HostLayout([1] * b, [0] * b, [0] * b, True, cache.max_len),
             tile_source=_ConstTiles(arange[:b], zeros, ones))
         self.ids_host, self.use_prev = view("ids_host"), view("use_prev")
-        self.want, self.sampling = arange[:b], view("sampling")
+        self.sampling = view("sampling")
         self.graph = None
         self.launches = 0
 
@@ -148,9 +147,9 @@ class _DecodeGraph:
         from tokenomos_b200 import ops
         from tokenomos_b200.sampling import sampler
 
-        ops.select_ids(self.ids_host, self.use_prev, self.last_token, self.ctx.seq_slot, self.ids)
-        out = model.forward(model.embed(self.ids), self.ctx)
-        logits = model.logits(out, self.want)
+        h = model.embed_fed(self.ids_host, self.use_prev, self.last_token, self.ctx.seq_slot)
+        out = model.forward(h, self.ctx)
+        logits = model.logits(out, None)          # every row is wanted, in order
         sampler.sample_packed(logits, self.sampling, self.tokens,
                               scatter=(self.ctx.seq_slot, self.last_token))
 

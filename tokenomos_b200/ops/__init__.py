@@ -18,7 +18,7 @@ __all__ = [
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "conv_gated", "conv_min_tile",
-    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "select_ids",
+    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "gather_rows_select",
 ]
 
 
@@ -76,6 +76,24 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None
         out = torch.empty(rows, width, dtype=table.dtype, device=table.device)
     _lib.call("tk_gather_rows", _ptr(table), _ptr(_i32(ids, "ids")), _ptr(out), rows, width,
               table.shape[0], _dtype_code(table), _stream())
+    return out
+
+
+def gather_rows_select(table: torch.Tensor, ids_host: torch.Tensor, use_prev: torch.Tensor,
+                       last_token: torch.Tensor, slot: torch.Tensor) -> torch.Tensor:
+    """``out[r] = table[last_token[slot[r]] if use_prev[r] else ids_host[r]]`` (ids int32): the
+    decode step's embedding lookup, fed on the device by the step before."""
+    _cuda(table, ids_host, use_prev, last_token, slot)
+    rows, width = ids_host.numel(), table.shape[1]
+    if not table.is_contiguous():
+        raise KernelError("gather_rows_select: the table must be contiguous")
+    for name, t in (("use_prev", use_prev), ("slot", slot)):
+        if _i32(t, name).numel() < rows:
+            raise KernelError(f"gather_rows_select: {name} is shorter than ids_host")
+    out = torch.empty(rows, width, dtype=table.dtype, device=table.device)
+    _lib.call("tk_gather_rows_select", _ptr(table), _ptr(_i32(ids_host, "ids_host")), _ptr(use_prev),
+              _ptr(_i32(last_token, "last_token")), _ptr(slot), _ptr(out), rows, width, table.shape[0],
+              _dtype_code(table), _stream())
     return out
 
 
@@ -364,19 +382,6 @@ def gemm_tc_status() -> int:
     """0, or where a tensor-core GEMM gave up waiting on a barrier since the last call (the
     kernels bound every wait instead of hanging)."""
     return _lib.call("tk_gemm_tc_status")
-
-
-def select_ids(ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
-               slot: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out[i] = last_token[slot[i]] if use_prev[i] else ids_host[i]`` (all int32)."""
-    _cuda(ids_host, use_prev, last_token, slot, out)
-    n = out.numel()
-    for name, t in (("ids_host", ids_host), ("use_prev", use_prev), ("slot", slot)):
-        if _i32(t, name).numel() < n:
-            raise KernelError(f"select_ids: {name} is shorter than the output")
-    _lib.call("tk_select_ids", _ptr(ids_host), _ptr(use_prev), _ptr(_i32(last_token, "last_token")),
-              _ptr(slot), _ptr(_i32(out, "out")), n, _stream())
-    return out
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,

@@ -26,6 +26,7 @@ _SIGNATURES = {
     "tk_built_for": [],
     "tk_set_pdl": [I],
     "tk_gather_rows": [P, P, P, I, I, I, I, P],
+    "tk_gather_rows_select": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_add_rmsnorm": [P, L, P, P, F, P, F, P, P, I, I, I, P],
     "tk_swiglu": [P, P, I, I, I, I, P],
     "tk_head_gate": [P, P, I, I, I, I, P],
@@ -42,9 +43,9 @@ _SIGNATURES = {
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny_tune": [I, I, I],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
-    "tk_select_ids": [P, P, P, P, P, I, P],
     "tk_gemm_tc_status": [],
     "tk_gemm_tc_split_mode": [I],
+    "tk_gemm_tc_tune": [I, I, I],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
 }
 
@@ -93,7 +94,7 @@ def calls() -> int:
 
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
-            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status", "tk_gemm_tc_split_mode"}
+            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_gemm_tc_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
 
 
 _fns: dict = {}

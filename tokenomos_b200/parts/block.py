@@ -74,6 +74,12 @@ class Stack:
     def embed(self, ids: torch.Tensor) -> torch.Tensor:
         return ops.gather_rows(self.embedding, ids)
 
+    def embed_fed(self, ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
+                  slot: torch.Tensor) -> torch.Tensor:
+        """Embedding rows of a decode step whose ids may still be on the device: row r takes
+        ``last_token[slot[r]]`` where ``use_prev[r]`` is set, else ``ids_host[r]``."""
+        return ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot)
+
     def forward(self, h: torch.Tensor, ctx: StepContext):
         """Runs the layer list; returns ``(h, residual, pending)`` of the last block: the final
         norm takes the last add with it, on the wanted rows only (``logits``)."""
@@ -82,11 +88,13 @@ class Stack:
             h, residual, pending = self.blocks[call.block].forward(h, residual, pending, ctx, i)
         return h, residual, pending
 
-    def logits(self, out, rows: torch.Tensor) -> torch.Tensor:
-        """Float32 logits [len(rows), vocab] at token rows ``rows`` (int32) of the step."""
+    def logits(self, out, rows: torch.Tensor | None) -> torch.Tensor:
+        """Float32 logits [len(rows), vocab] at token rows ``rows`` (int32) of the step; None:
+        at every row, in order."""
         h, residual, pending = out
-        h = ops.gather_rows(h, rows)
-        if residual is not None:
-            residual = ops.gather_rows(residual, rows)
+        if rows is not None:
+            h = ops.gather_rows(h, rows)
+            if residual is not None:
+                residual = ops.gather_rows(residual, rows)
         y, _ = self.final_norm.add_norm(h, residual, pending)
         return self.head(y, out_dtype=torch.float32)
