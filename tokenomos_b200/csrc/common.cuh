@@ -60,6 +60,16 @@ __device__ __forceinline__ float round_as(float v) {
     return to_f<T>(from_f<T>(v));
 }
 
+// silu(g) = g * sigmoid(g), rounded as a store in T would. 16-bit storage takes the fast
+// exponential and division (a few ulp of a float, far below the rounding that follows), so
+// every 16-bit kernel that applies the activation gets the same bits; 32-bit storage takes the
+// accurate ones.
+template <typename T>
+__device__ __forceinline__ float silu_as(float g) {
+    if constexpr (sizeof(T) == 2) return round_as<T>(__fdividef(g, 1.0f + __expf(-g)));
+    return g / (1.0f + expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -82,18 +82,138 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
     }
 }
 
+// The same with 16-byte accesses: a thread owns VEC = 16 / sizeof(T) neighbouring channels of one
+// tile, so every load and store moves whole 16-byte pieces of a token's row.
+template <typename T, int W>
+__global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
+                                      const float* __restrict__ w, const float* __restrict__ bias,
+                                      T* state, T* out, const int* cu, const int* seq_ctx,
+                                      const int* seq_slot, const int* tile_seq, const int* tile_off,
+                                      const int* tile_n) {
+    constexpr int VEC = 16 / sizeof(T);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    if (c >= d) return;
+    const int s = tile_seq[blockIdx.x];
+    const int off = tile_off[blockIdx.x];
+    const int n = tile_n[blockIdx.x];
+    const int start = cu[s];
+    const int len = cu[s + 1] - start;
+    const int ctx = seq_ctx[s];
+    T* st = state + (size_t)seq_slot[s] * (W - 1) * d + c;
+
+    float taps[W][VEC], b[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) taps[j][i] = w[(size_t)(c + i) * W + j];
+        b[i] = bias != nullptr ? bias[c + i] : 0.f;
+    }
+    auto load = [&](const T* p, float (&v)[VEC]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = to_f<T>(e[i]);
+    };
+    auto store = [&](T* p, const float (&v)[VEC]) {
+        uint4 raw;
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) e[i] = from_f<T>(v[i]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    };
+    // u at index `li` of the portion (negative: the state, or zero before position 0)
+    auto input = [&](int li, float (&u)[VEC]) {
+        if (li >= 0) {
+            const T* row = bcx + (size_t)(start + li) * stride;
+            float bv[VEC], xv[VEC];
+            load(row + c, bv);
+            load(row + 2 * d + c, xv);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) u[i] = round_as<T>(bv[i] * xv[i]);
+        } else if (ctx + li < 0) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) u[i] = 0.f;
+        } else {
+            load(st + (size_t)(W - 1 + li) * d, u);
+        }
+    };
+
+    float hist[W - 1][VEC];
+#pragma unroll
+    for (int k = 0; k < W - 1; ++k) input(off - (W - 1) + k, hist[k]);
+
+    float fresh[W - 1][VEC];
+    const bool writes_state = off == 0;
+    if (writes_state) {
+#pragma unroll
+        for (int k = 0; k < W - 1; ++k) input(len - (W - 1) + k, fresh[k]);
+    }
+
+    // four tokens' loads are issued before the first of them is used
+    for (int i0 = 0; i0 < n; i0 += 4) {
+        uint4 rb[4], rc[4], rx[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (i0 + k < n) {
+                const T* row = bcx + (size_t)(start + off + i0 + k) * stride;
+                rb[k] = *reinterpret_cast<const uint4*>(row + c);
+                rc[k] = *reinterpret_cast<const uint4*>(row + d + c);
+                rx[k] = *reinterpret_cast<const uint4*>(row + 2 * d + c);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (i0 + k >= n) break;
+            const T* bv = reinterpret_cast<const T*>(&rb[k]);
+            const T* cv = reinterpret_cast<const T*>(&rc[k]);
+            const T* xv = reinterpret_cast<const T*>(&rx[k]);
+            float y[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float u = round_as<T>(to_f<T>(bv[e]) * to_f<T>(xv[e]));
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < W - 1; ++j) acc += hist[j][e] * taps[j][e];
+                acc += u * taps[W - 1][e];
+                acc += b[e];
+                y[e] = to_f<T>(cv[e]) * round_as<T>(acc);
+#pragma unroll
+                for (int j = 0; j + 1 < W - 1; ++j) hist[j][e] = hist[j + 1][e];
+                hist[W - 2][e] = u;
+            }
+            store(out + (size_t)(start + off + i0 + k) * d + c, y);
+        }
+    }
+
+    if (writes_state) {
+#pragma unroll
+        for (int k = 0; k < W - 1; ++k) store(st + (size_t)k * d, fresh[k]);
+    }
+}
+
 template <typename T>
 static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, const float* bias,
                        void* state, void* out, const int* cu, const int* seq_ctx,
                        const int* seq_slot, const int* tile_seq, const int* tile_off,
                        const int* tile_n, int n_tiles, int W, cudaStream_t stream) {
-    const int threads = 128;
-    dim3 grid(n_tiles, (d + threads - 1) / threads);
+    constexpr int VEC = 16 / sizeof(T);
+    const bool vec_ok = d % VEC == 0 && stride % VEC == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                        (uintptr_t)state % 16 == 0;
+    const int threads = vec_ok ? 64 : 128;
+    const int per_block = vec_ok ? threads * VEC : threads;
+    dim3 grid(n_tiles, (d + per_block - 1) / per_block);
 #define TK_CONV_CASE(WW)                                                                         \
     case WW:                                                                                     \
-        tk_launch(conv_gated_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,                                   \
-            (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,        \
-            tile_seq, tile_off, tile_n);                                                         \
+        if (vec_ok)                                                                              \
+            tk_launch(conv_gated_vec_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,        \
+                (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
+                tile_seq, tile_off, tile_n);                                                     \
+        else                                                                                     \
+            tk_launch(conv_gated_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,            \
+                (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
+                tile_seq, tile_off, tile_n);                                                     \
         break;
     switch (W) {
         TK_CONV_CASE(2)

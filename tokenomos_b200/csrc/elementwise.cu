@@ -303,37 +303,53 @@ __global__ void swiglu_kernel(const T* gu, T* out, int64_t total,
         const int ui = block > 0 ? gi + block : inter + c;
         const float g = to_f<T>(gu[t * 2 * inter + gi]);
         const float u = to_f<T>(gu[t * 2 * inter + ui]);
-        const float s = round_as<T>(g / (1.0f + expf(-g)));
+        const float s = silu_as<T>(g);
         out[i] = from_f<T>(s * u);
     }
 }
 
-// 16 bytes of gate and of up per thread (block == 0 or block a multiple of 8 channels)
-__global__ void swiglu_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int64_t vecs, int inter,
-                                  int block) {
+// 16 bytes of gate and of up per thread and step (block == 0 or block a multiple of 8 channels),
+// two steps' loads in flight. One block row of the grid per token row, so no thread divides by
+// the row length. The sigmoid uses the fast exponential and reciprocal: their error (a few ulp
+// of a float) is far below the 16-bit rounding that follows. An earlier version with expf, a
+// full-precision division and a 64-bit index division per element was instruction-bound
+// (80 % issue slots busy at a third of the memory bandwidth).
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int inter, int block,
+                  int blocks_per_row) {
     pdl_launch_dependents();
     pdl_wait();
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    const int per_row = inter / 8;
-    for (; i < vecs; i += step) {
-        const int64_t t = i / per_row;
-        const int c = (int)(i - t * per_row) * 8;
-        const int gi = block > 0 ? (c / block) * 2 * block + c % block : c;
-        const int ui = block > 0 ? gi + block : inter + c;
-        const uint4 graw = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + gi);
-        const uint4 uraw = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + ui);
-        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&graw);
-        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uraw);
+    const int per_row = inter >> 3;
+    const int t = blockIdx.x / blocks_per_row;
+    const int v0 = (blockIdx.x - t * blocks_per_row) * (2 * 256) + threadIdx.x;
+    const __nv_bfloat16* row = gu + (size_t)t * 2 * inter;
+    uint4 graw[2], uraw[2];
+    int c[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int v = v0 + k * 256;
+        c[k] = v << 3;
+        if (v < per_row) {
+            const int gi = block > 0 ? (c[k] / block) * 2 * block + c[k] % block : c[k];
+            const int ui = block > 0 ? gi + block : inter + c[k];
+            graw[k] = *reinterpret_cast<const uint4*>(row + gi);
+            uraw[k] = *reinterpret_cast<const uint4*>(row + ui);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        if (v0 + k * 256 >= per_row) continue;
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&graw[k]);
+        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uraw[k]);
         uint4 packed;
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float gf = __bfloat162float(g[k]);
-            const float s = round_as<__nv_bfloat16>(gf / (1.0f + expf(-gf)));
-            o[k] = __float2bfloat16_rn(s * __bfloat162float(u[k]));
+        for (int e = 0; e < 8; ++e) {
+            const float gf = __bfloat162float(g[e]);
+            const float s = silu_as<__nv_bfloat16>(gf);
+            o[e] = __float2bfloat16_rn(s * __bfloat162float(u[e]));
         }
-        *reinterpret_cast<uint4*>(out + t * inter + c) = packed;
+        *reinterpret_cast<uint4*>(out + (size_t)t * inter + c[k]) = packed;
     }
 }
 
@@ -347,11 +363,14 @@ TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int block, 
     const int threads = 256;
     if (dtype == TK_BF16 && inter % 8 == 0 && (block == 0 || block % 8 == 0) && (uintptr_t)gu % 16 == 0 &&
         (uintptr_t)out % 16 == 0) {
-        const int64_t vecs = total / 8;
-        const int vblocks = (int)((vecs + threads - 1) / threads < 148 * 32 ? (vecs + threads - 1) / threads
-                                                                            : 148 * 32);
-        tk_launch(swiglu_vec_kernel, dim3(vblocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
-                  (__nv_bfloat16*)out, vecs, inter, block);
+        const int per_row = inter / 8;
+        const int blocks_per_row = (per_row + 2 * threads - 1) / (2 * threads);
+        if ((int64_t)rows * blocks_per_row > 0x7fffffffLL) {
+            tk_set_error("swiglu: %d rows of %d channels exceed the grid", rows, inter);
+            return -1;
+        }
+        tk_launch(swiglu_vec_kernel, dim3((unsigned)(rows * blocks_per_row)), dim3(threads), 0, stream,
+                  (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, inter, block, blocks_per_row);
         TK_CHECK_LAUNCH("swiglu_vec");
         return 0;
     }

@@ -148,7 +148,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
             // the unfused path stores gate and up in the output type, then rounds silu(gate)
             gate = round_as<TO>(gate);
             up = round_as<TO>(up);
-            const float act = round_as<TO>(gate / (1.0f + expf(-gate)));
+            const float act = silu_as<TO>(gate);
             out[(size_t)tok * ldo + n0 / 2 + j] = from_f<TO>(act * up);
         }
     } else {

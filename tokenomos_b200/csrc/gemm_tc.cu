@@ -178,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const float other = __shfl_xor_sync(0xffffffffu, mine, 8);       // gate <-> up
                     const int jj = b_row0 + c + e;
                     if (is_gate && row_ok && i_row + 8 < rows_a && jj < rows_b) {
-                        const float act = round_as<TO>(mine / (1.0f + expf(-mine)));
+                        const float act = silu_as<TO>(mine);
                         out[(size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7)] = from_f<TO>(act * other);
                     }
                 }
@@ -323,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             }
                             gv = round_as<TO>(gv);
                             uv = round_as<TO>(uv);
-                            res[e] = round_as<TO>(gv / (1.0f + expf(-gv))) * uv;
+                            res[e] = silu_as<TO>(gv) * uv;
                             ++n_ok;
                         }
                         store4(out + (size_t)jj * ldo + (i_row >> 4) * 8 + (i_row & 7), res, n_ok);

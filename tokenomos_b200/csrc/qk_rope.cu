@@ -87,6 +87,98 @@ __global__ void qk_norm_rope_write_kernel(
     }
 }
 
+// The same with 16-byte accesses: a head is spread over `lph` lanes (a power of two, 16 bytes
+// each), so a warp takes 32 / lph heads at a time; the head's sum of squares and the rotation's
+// partner elements move between lanes with shuffles instead of through shared memory. Needs
+// D = lph * (16 / sizeof(T)) and half the rotary width a multiple of the 16-byte chunk.
+template <typename T>
+__global__ void qk_norm_rope_write_vec_kernel(
+    const T* qkv, int64_t qkv_stride, T* q_out, T* kv_pool,
+    const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+    const float* __restrict__ inv_freq, const int* positions,
+    const int* tok_seq, const int* block_table, int bt_stride, int H,
+    int Hkv, int D, int R, int P, int lph) {
+    constexpr int VEC = 16 / sizeof(T);
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int pos = positions[t];
+    const int half = R >> 1;
+    float* cs = smem;
+    float* sn = smem + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s_, c_;
+        sincosf((float)pos * inv_freq[i], &s_, &c_);
+        cs[i] = round_as<T>(c_);
+        sn[i] = round_as<T>(s_);
+    }
+    __syncthreads();
+    size_t cache_row = 0;
+    if (Hkv > 0) {
+        const int s = tok_seq[t];
+        const int page = block_table[(size_t)s * bt_stride + pos / P];
+        cache_row = (size_t)page * 2 * Hkv * P + (pos % P);
+    }
+    const T* row = qkv + (size_t)t * qkv_stride;
+    const int heads = H + 2 * Hkv;
+    const int hpw = 32 / lph;                      // heads a warp takes per pass
+    const int sub = lane / lph, c = (lane % lph) * VEC;
+    const int half_lanes = half / VEC;
+    // the lane that holds this chunk's partner in the rotation (itself beyond the rotary width)
+    const int partner = c < half ? lane + half_lanes : (c < R ? lane - half_lanes : lane);
+    for (int h0 = (blockIdx.y * nwarp + warp) * hpw; h0 < heads; h0 += gridDim.y * nwarp * hpw) {
+        const int hh = h0 + sub;
+        const bool live = hh < heads;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * D + c);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        T* dst = nullptr;
+        const float* w = nullptr;
+        bool rotate = true;
+        if (hh < H) {
+            dst = q_out + ((size_t)t * H + hh) * D;
+            w = wq;
+        } else if (hh < H + Hkv) {
+            dst = kv_pool + (cache_row + (size_t)(hh - H) * P) * D;
+            w = wk;
+        } else if (live) {
+            dst = kv_pool + (cache_row + (size_t)(hh - H) * P) * D;      // V head hh - H - Hkv of [K | V]
+            rotate = false;
+        }
+        float v[VEC];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            v[i] = to_f<T>(e[i]);
+            ss += v[i] * v[i];
+        }
+        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (rotate && w != nullptr) {
+            const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[i] = round_as<T>(round_as<T>(v[i] * rstd) * w[c + i]);
+        }
+        float pv[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) pv[i] = __shfl_sync(0xffffffffu, v[i], partner);
+        if (!live) continue;
+        uint4 packed = raw;
+        if (rotate) {
+            T* o = reinterpret_cast<T*>(&packed);
+            const int i0 = c < half ? c : c - half;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                float r = v[i];
+                if (c < R) r = r * cs[i0 + i] + (c < half ? -pv[i] : pv[i]) * sn[i0 + i];
+                o[i] = from_f<T>(r);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + c) = packed;
+    }
+}
+
 // qkv: [T, (H + 2*Hkv) * D] with row stride `qkv_stride` (elements); Hkv = 0 for a layer that
 // only has queries (it reads another layer's cache). wq / wk may be null (no q/k norm).
 TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_out, void* kv_pool,
@@ -100,11 +192,36 @@ TK_API int tk_qk_norm_rope_write(const void* qkv, int64_t qkv_stride, void* q_ou
     TK_CHECK_ARG((wq == nullptr) == (wk == nullptr) || Hkv == 0,
                  "qk_norm_rope_write: q and k norms come together");
     if (T_ == 0) return 0;
-    // one warp per head at a time; with few tokens the heads spread over more blocks so the GPU
-    // fills, with many one block takes all heads of a token (the angles are computed once)
     const int heads = H + 2 * Hkv;
     const int threads = T_ >= 1024 ? 256 : 128;
     const int warps = threads / 32;
+    // 16-byte path: the head is a power-of-two number of 16-byte chunks, the rotation's halves
+    // are whole chunks, rows and bases are 16-byte aligned
+    const int vec = dtype == TK_F32 ? 4 : 8;
+    const int lph = D / vec;
+    const bool vec_ok = D % vec == 0 && lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0 && (R / 2) % vec == 0 &&
+                        qkv_stride % vec == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+                        (uintptr_t)kv_pool % 16 == 0;
+    if (vec_ok) {
+        const int per_pass = warps * (32 / lph);
+        const int per_token = T_ >= 1024 ? 1 : (heads + per_pass - 1) / per_pass;
+        const size_t smem = (size_t)R * sizeof(float);
+        const dim3 grid(T_, per_token);
+        if (dtype == TK_F32)
+            tk_launch(qk_norm_rope_write_vec_kernel<float>, dim3(grid), dim3(threads), smem, stream,
+                (const float*)qkv, qkv_stride, (float*)q_out, (float*)kv_pool, wq, wk, eps, inv_freq,
+                positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P, lph);
+        else if (dtype == TK_BF16)
+            tk_launch(qk_norm_rope_write_vec_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), smem, stream,
+                (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_pool, wq,
+                wk, eps, inv_freq, positions, tok_seq, block_table, bt_stride, H, Hkv, D, R, P, lph);
+        else
+            TK_CHECK_ARG(false, "qk_norm_rope_write: unknown dtype %d", dtype);
+        TK_CHECK_LAUNCH("qk_norm_rope_write");
+        return 0;
+    }
+    // one warp per head at a time; with few tokens the heads spread over more blocks so the GPU
+    // fills, with many one block takes all heads of a token (the angles are computed once)
     const int per_token = T_ >= 1024 ? 1 : (heads + warps - 1) / warps;
     const size_t smem = ((size_t)R + (size_t)warps * D) * sizeof(float);
     const dim3 grid(T_, per_token);

@@ -12,8 +12,9 @@ from tokenomos_b200.parts.contract import SlotState, StepContext
 from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import Runtime, register
 
-# tokens a conv tile walks in order; any value >= width - 1 is correct
-CONV_TILE = 32
+# tokens a conv tile walks in order; any value >= width - 1 is correct. Short tiles give the
+# kernel more threads (a 2,048-token portion of 2,048 channels: 18 us at 8, 33 us at 32)
+CONV_TILE = 8
 
 
 class ShortConv:
