@@ -272,7 +272,7 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfl
 // prefill: 64 rows per CTA, all keys
 // ---------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (D == 64 ? 4 : 2))
 attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                         __nv_bfloat16* out, const int* positions,
                         const int* tok_seq, const int* block_table,
@@ -285,8 +285,12 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     constexpr int TILE_BYTES = 64 * D * 2;
     const uint32_t smem = smem_u32(smem_raw);   // [stage][K|V][64][D]
     const int G = H / Hkv;
-    const int kvh = blockIdx.y;
-    const int tok0 = tile_tok0[blockIdx.x], ntok = tile_ntok[blockIdx.x];
+    // the grid is one-dimensional with the KV head fastest and the tiles in reverse: a causal
+    // tile late in its sequence reads the most keys, so the longest CTAs start first and the
+    // last wave is made of short ones
+    const int kvh = blockIdx.x % Hkv;
+    const int tile = gridDim.x / Hkv - 1 - blockIdx.x / Hkv;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     const int rows = ntok * G;
     const int seq = tok_seq[tok0];
     const int* bt_row = block_table + (size_t)seq * bt_stride;
@@ -541,7 +545,7 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_mma: bad page size or tile count");
     if (n_tiles == 0) return 0;
-    dim3 grid(n_tiles, Hkv);
+    dim3 grid(n_tiles * Hkv);
     const size_t smem = 2 * 2 * 64 * (size_t)D * 2;
     auto q_ = (const __nv_bfloat16*)q;
     auto p_ = (const __nv_bfloat16*)kv_pool;
