@@ -53,6 +53,33 @@ def test_greedy_generation_through_llm(name, lengths, steps, work, margin, model
             assert out.token_ids == plain_lfm3.generate_greedy(config, w, prompt, steps)
 
 
+@pytest.mark.parametrize("name, work, margin", [("A", "fp32", 1e-4), ("B", "fp32", 1e-4), ("D", "bf16", 0.25),
+                                                ("C", "bf16", 0.25)])
+def test_mixed_steps_through_captured_graphs(name, work, margin, model_folders):
+    """Prompt portions beside decoded tokens, replayed from captured steps (fixed-size layouts
+    padded with a dummy sequence, empty tiles and unused rows) and queued one step ahead of the
+    host: the same tokens as the eager steps, and the plain implementation's."""
+    from tokenomos_b200 import LLM, SamplingParams
+    folder = model_folders[name][torch.bfloat16]
+    config, w = plain_lfm3.read_folder(folder)
+    prompts = prompts_for(name, [37, 5, 64, 18, 51, 9, 70, 26], seed=4)
+    kw = dict(work=work, page=TINY[name]["page"], max_len=128, slots=5, pages=60, prefill_budget=24)
+    p = SamplingParams(max_tokens=20)
+    with LLM(str(folder), graphs=False, **kw) as llm:
+        eager = llm.generate(prompts, p)
+    with LLM(str(folder), graphs=True, **kw) as llm:
+        llm.engine.step_fn.capture_after = 0
+        graphed = llm.generate(prompts, p)
+        again = llm.generate(prompts, p)
+        assert llm.engine.stats.graph_steps > 10
+        llm.engine.cache.check()
+    for prompt, a, b, c in zip(prompts, eager, graphed, again):
+        assert b.token_ids == c.token_ids
+        teacher_forced_ok(config, w, prompt, b.token_ids, margin)
+        if work == "fp32":
+            assert a.token_ids == b.token_ids
+
+
 def test_seeded_sampling_repeats_alone_and_in_batches(model_folders):
     from tokenomos_b200 import LLM, SamplingParams
     folder = model_folders["B"][torch.bfloat16]

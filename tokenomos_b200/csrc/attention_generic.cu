@@ -45,6 +45,7 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
     const int gh = min(heads_per_chunk, G - g0);  // heads of this chunk
     const int tok0 = tile_tok0[blockIdx.x];
     const int ntok = tile_ntok[blockIdx.x];
+    if (ntok <= 0) return;       // an unused entry of a fixed-length tile list (captured steps)
     const int rows = ntok * gh;
     const int seq = tok_seq[tok0];
     const int tid = threadIdx.x;

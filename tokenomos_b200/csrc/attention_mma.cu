@@ -291,6 +291,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const int kvh = blockIdx.x % Hkv;
     const int tile = gridDim.x / Hkv - 1 - blockIdx.x / Hkv;
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    if (ntok <= 0) return;       // an unused entry of a fixed-length tile list (captured steps)
     const int rows = ntok * G;
     const int seq = tok_seq[tok0];
     const int* bt_row = block_table + (size_t)seq * bt_stride;
@@ -388,6 +389,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const int i = blockIdx.x;                        // which decode token
     const int kvh = blockIdx.y, split = blockIdx.z;
     const int tok = tok_index[i];
+    if (tok < 0) return;         // an unused entry of a fixed-length list (captured steps)
     const int seq = tok_seq[tok];
     const int pos = positions[tok];
     const int* bt_row = block_table + (size_t)seq * bt_stride;
@@ -499,6 +501,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
+    if (tok_index[i] < 0) return;        // an unused entry of a fixed-length list (captured steps)
     const size_t base = ((size_t)i * H + head) * nsplit;
     const float scale_log2 = scale * LOG2E;
     float M = -INFINITY;

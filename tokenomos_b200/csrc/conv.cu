@@ -29,6 +29,7 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
     const int s = tile_seq[blockIdx.x];
     const int off = tile_off[blockIdx.x];
     const int n = tile_n[blockIdx.x];
+    if (n <= 0) return;          // an unused entry of a fixed-length tile list (captured steps)
     const int start = cu[s];
     const int len = cu[s + 1] - start;
     const int ctx = seq_ctx[s];
@@ -98,6 +99,7 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
     const int s = tile_seq[blockIdx.x];
     const int off = tile_off[blockIdx.x];
     const int n = tile_n[blockIdx.x];
+    if (n <= 0) return;          // an unused entry of a fixed-length tile list (captured steps)
     const int start = cu[s];
     const int len = cu[s + 1] - start;
     const int ctx = seq_ctx[s];

@@ -35,6 +35,7 @@ class Result:
 class Stats:
     steps: int = 0
     decode_steps: int = 0          # steps in which every row brought one token
+    graph_steps: int = 0           # mixed steps that replayed a captured graph
     prefill_tokens: int = 0
     generated: int = 0
     preemptions: int = 0
@@ -126,23 +127,35 @@ class Engine:
             planned = self.scheduler.plan()
         if not planned:
             return self._finish(finished + self._drain())
+        def entries_of(planned):
+            entries, rows = [], []
+            for p in planned:
+                r = p.req
+                toks = [0] * p.count if p.fed_on_device else r.tokens[p.start:p.start + p.count]
+                entries.append(StepEntry(r.rid, toks, [p.count - 1] if p.sample else []))
+                if p.sample:
+                    rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed,
+                                 len(r.output) + r.inflight))
+            return entries, rows
+
         decode_only = all(p.count == 1 and p.sample for p in planned)
-        if not (self.graphs and decode_only) and (self._inflight or any(p.fed_on_device for p in planned)):
-            # the eager path needs every token on the host: undo nothing (pages stay held), read
-            # what is in flight, and plan again with the tokens known
+        entries, rows = entries_of(planned)
+        # a captured step (decode-only, or a mixed one whose bucket has been captured) is queued
+        # without waiting for the step before it; anything else runs eagerly and needs every
+        # token on the host first
+        graph = None
+        if self.graphs and not decode_only:
+            graph = self.step_fn.step_graph_for(entries)
+        if not (self.graphs and (decode_only or graph is not None)) and (
+                self._inflight or any(p.fed_on_device for p in planned)):
+            # undo nothing (pages stay held), read what is in flight, plan again with the tokens known
             finished += self._drain()
             planned = self.scheduler.plan() if not self.scheduler.idle() else []
             if not planned:
                 return self._finish(finished)
             decode_only = all(p.count == 1 and p.sample for p in planned)
-        entries, rows = [], []
-        for p in planned:
-            r = p.req
-            toks = [0] if p.fed_on_device else r.tokens[p.start:p.start + p.count]
-            entries.append(StepEntry(r.rid, toks, [p.count - 1] if p.sample else []))
-            if p.sample:
-                rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed,
-                             len(r.output) + r.inflight))
+            entries, rows = entries_of(planned)
+            graph = None
         tokens_in_step = sum(p.count for p in planned)
         self.stats.stamps.append((time.perf_counter(), len(planned), tokens_in_step))
         self.stats.steps += 1
@@ -150,8 +163,13 @@ class Engine:
             self.stats.decode_steps += 1
         else:
             self.stats.prefill_tokens += sum(p.count for p in planned if p.count > 1)
-        if self.graphs and decode_only:
-            handle = self.step_fn.launch_decode_graph(entries, rows, [p.fed_on_device for p in planned])
+        if self.graphs and (decode_only or graph is not None):
+            fed = [p.fed_on_device for p in planned]
+            if decode_only:
+                handle = self.step_fn.launch_decode_graph(entries, rows, fed)
+            else:
+                handle = self.step_fn.launch_step_graph(graph, entries, rows, fed)
+                self.stats.graph_steps += 1
             self.scheduler.launch(planned)
             self._inflight.append((planned, handle))
             self.stats.generated += len(rows)

@@ -33,23 +33,32 @@ class StepEntry:
 class _Tiles:
     """Cuts the step's sequences into runs of at most ``size`` tokens, on demand, once per size."""
 
-    def __init__(self, seq_lens: list[int], device, upload):
+    def __init__(self, seq_lens: list[int], device, upload, asked: set | None = None):
         self.seq_lens, self.device, self.upload = seq_lens, device, upload
         self.cache: dict[int, tuple] = {}
+        self.asked = asked          # every (size, which) any step's parts have asked for
+
+    @staticmethod
+    def cut(seq_lens: list[int], size: int, which: str):
+        """Host lists (sequence, first token, offset in the portion, tokens) of the tiles."""
+        seq, tok0, off, n = [], [], [], []
+        start = 0
+        for s, length in enumerate(seq_lens):
+            if which == "all" or length > 1:
+                for o in range(0, length, size):
+                    seq.append(s)
+                    tok0.append(start + o)
+                    off.append(o)
+                    n.append(min(size, length - o))
+            start += length
+        return seq, tok0, off, n
 
     def tiles(self, size: int, which: str = "all"):
         key = (size, which)
+        if self.asked is not None:
+            self.asked.add(key)
         if key not in self.cache:
-            seq, tok0, off, n = [], [], [], []
-            start = 0
-            for s, length in enumerate(self.seq_lens):
-                if which == "all" or length > 1:
-                    for o in range(0, length, size):
-                        seq.append(s)
-                        tok0.append(start + o)
-                        off.append(o)
-                        n.append(min(size, length - o))
-                start += length
+            seq, tok0, off, n = self.cut(self.seq_lens, size, which)
             k = len(seq)
             if k == 0:
                 empty = torch.empty(0, dtype=torch.int32, device=self.device)
@@ -60,6 +69,8 @@ class _Tiles:
         return self.cache[key]
 
     def singles(self):
+        if self.asked is not None:
+            self.asked.add("singles")
         if "singles" not in self.cache:
             idx, start = [], 0
             for length in self.seq_lens:
@@ -184,11 +195,194 @@ class DecodeHandle:
         return self._tokens
 
 
+STEP_TOKEN_BUCKETS = (32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384)
+STEP_SEQ_BUCKETS = (4, 16, 64, 128, 256, 512, 1024)
+
+
+class _FixedTiles:
+    """Tile lists of a captured step: device arrays of the greatest length the bucket allows,
+    refilled before every replay; entries past the step's own are empty tiles (0 tokens) and
+    negative token indices, which the kernels skip."""
+
+    def __init__(self, views: dict):
+        self.views = views
+
+    def tiles(self, size: int, which: str = "all"):
+        return self.views[(size, which)]
+
+    def singles(self):
+        return self.views["singles"]
+
+
+class _StepGraph:
+    """One captured step for any mix of prompt portions and single tokens that fits ``tokens``
+    packed tokens and ``seqs`` sequences: a static layout buffer in, sampled tokens out.
+
+    A step with fewer tokens is padded with a dummy sequence on the null slot and the null page
+    (its tokens are carried through the row-wise kernels and belong to no tile); unused sequences
+    are empty. Logits are taken at one row per sequence at most (the row whose token is sampled);
+    unused rows repeat row 0. As in the decode graph, the id of a single token may come from
+    ``last_token`` on the device."""
+
+    RING = 2
+
+    def __init__(self, step_fn: "StepFunction", tokens: int, seqs: int, tile_keys: set):
+        cache, dev = step_fn.cache, step_fn.device
+        self.tokens_cap, self.seqs_cap = tokens, seqs
+        self.width = cache.max_blocks
+        self.groups = list(cache.groups)
+        T, S = tokens, seqs
+        self.off = {}
+        o = 0
+
+        def field_(name, n):
+            nonlocal o
+            self.off[name] = (o, n)
+            o += n
+
+        for name, n in (("positions", T), ("tok_seq", T), ("ids_host", T), ("use_prev", T), ("tok_slot", T),
+                        ("cu", S + 1), ("seq_ctx", S), ("seq_slot", S), ("want", S), ("want_slot", S),
+                        ("sampling", 6 * S)):
+            field_(name, n)
+        for g in self.groups:
+            field_(("table", g), S * self.width)
+        self.tile_keys = sorted(k for k in tile_keys if k != "singles")
+        self.tile_cap = {}
+        for key in self.tile_keys:
+            self.tile_cap[key] = T // key[0] + S + 1
+            field_(("tiles", key), 4 * self.tile_cap[key])
+        field_("singles", S)
+        self.size = o
+        self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.table_len = [{g: [0] * S for g in self.groups} for _ in range(self.RING)]
+        self.tokens_host = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.turn = 0
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.sampled = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.last_token = step_fn.last_token
+
+        def view(name):
+            a, n = self.off[name]
+            return self.dev[a:a + n]
+
+        views = {"singles": view("singles")}
+        for key in self.tile_keys:
+            flat, k = view(("tiles", key)), self.tile_cap[key]
+            views[key] = (flat[:k], flat[k:2 * k], flat[2 * k:3 * k], flat[3 * k:])
+        self.ctx = StepContext(
+            n_tokens=T, n_seqs=S, positions=view("positions"), tok_seq=view("tok_seq"),
+            cu_seqlens=view("cu"), seq_ctx=view("seq_ctx"), seq_slot=view("seq_slot"),
+            block_tables={g: view(("table", g)).view(S, self.width) for g in self.groups},
+            states=cache.states, state_groups=cache.state_groups, page_size=cache.page_size,
+            host=HostLayout([], [], [], False, cache.max_len), tile_source=_FixedTiles(views))
+        self.view = view
+        self.graph = None
+        self.launches = 0
+
+    def body(self, model):
+        from tokenomos_b200.sampling import sampler
+
+        v = self.view
+        h = model.embed_fed(v("ids_host"), v("use_prev"), self.last_token, v("tok_slot"))
+        out = model.forward(h, self.ctx)
+        logits = model.logits(out, v("want"))
+        sampler.sample_packed(logits, v("sampling"), self.sampled,
+                              scatter=(v("want_slot"), self.last_token))
+
+    def capture(self, model, pool):
+        from tokenomos_b200.ops import _lib
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.body(model)              # warm-up outside the capture (library handles, sizes)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = _lib.calls()
+        with torch.cuda.graph(graph, pool=pool):
+            self.body(model)
+        self.launches = _lib.calls() - before
+        self.graph = graph
+
+    def fill(self, turn: int, entries: list[StepEntry], states: list, sampling_rows: list[tuple],
+             fed_on_device: list[bool]) -> int:
+        """Write the step's layout into staging buffer ``turn``; returns the wanted-row count."""
+        from tokenomos_b200.sampling import sampler
+
+        h, T, S = self.host_np[turn], self.tokens_cap, self.seqs_cap
+        n = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        total = sum(lens)
+        pad = T - total
+        lens_np = np.asarray(lens, dtype=np.int32)
+        ctx_np = np.asarray([st.length for st in states], dtype=np.int32)
+        slot_np = np.asarray([st.slot for st in states], dtype=np.int32)
+        cu = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum(lens_np, out=cu[1:])
+
+        def put(name, values, fill=0):
+            o, cap = self.off[name]
+            k = len(values)
+            h[o:o + k] = values
+            h[o + k:o + cap] = fill
+
+        put("positions", np.arange(total, dtype=np.int32) + np.repeat(ctx_np - cu[:-1], lens_np))
+        put("tok_seq", np.repeat(np.arange(n, dtype=np.int32), lens_np), n)       # padding: the dummy sequence
+        put("ids_host", np.fromiter((0 if f else t for e, f in zip(entries, fed_on_device) for t in e.tokens),
+                                    dtype=np.int32, count=total))
+        put("use_prev", np.repeat(np.asarray(fed_on_device, dtype=np.int32), lens_np))
+        put("tok_slot", np.repeat(slot_np, lens_np))
+        put("cu", cu, T)                         # the dummy sequence takes the rest; then empty ones
+        put("seq_ctx", ctx_np)
+        put("seq_slot", slot_np)
+        want, want_slot = [], []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                want.append(int(cu[i]) + w)
+                want_slot.append(int(slot_np[i]))
+        put("want", want)
+        put("want_slot", want_slot)
+        o, _ = self.off["sampling"]
+        sampler.pack_rows_into(h[o:o + 6 * S], sampling_rows, S)
+        for g in self.groups:
+            o, _ = self.off[("table", g)]
+            held = self.table_len[turn][g]
+            for i, st in enumerate(states):
+                row = st.tables[g]
+                base = o + i * self.width
+                h[base:base + len(row)] = row
+                if held[i] > len(row):
+                    h[base + len(row):base + held[i]] = 0
+                held[i] = len(row)
+            for i in range(n, S):
+                if held[i]:
+                    h[o + i * self.width:o + i * self.width + held[i]] = 0
+                    held[i] = 0
+        for key in self.tile_keys:
+            seq, tok0, off, cnt = _Tiles.cut(lens, key[0], key[1])
+            o, _ = self.off[("tiles", key)]
+            k, cap = len(seq), self.tile_cap[key]
+            for j, (values, fill) in enumerate(((seq, 0), (tok0, 0), (off, 1), (cnt, 0))):
+                h[o + j * cap:o + j * cap + k] = values
+                h[o + j * cap + k:o + (j + 1) * cap] = fill
+        singles = [int(cu[i]) for i, m in enumerate(lens) if m == 1]
+        put("singles", singles, -1)
+        return len(want)
+
+
 class StepFunction:
     def __init__(self, model, cache: CacheManager, staging_ints: int = 1 << 20):
         self.model, self.cache = model, cache
         self.device = cache.device
         self._graphs: dict[int, _DecodeGraph] = {}
+        self._step_graphs: dict[tuple, _StepGraph] = {}
+        self._step_graph_uses: dict[tuple, int] = {}
+        self._graph_pool = None
+        self._tile_keys: set = set()     # what the model's parts ask the tile source for
+        # a mixed step's bucket is captured once this many steps have fallen into it
+        self.capture_after = 2
         # the token each request's last step sampled, by state slot (slot 0: padded rows)
         self.last_token = torch.zeros(cache.max_requests + 1, dtype=torch.int32, device=self.device)
         self.h2d_bytes = 0
@@ -225,9 +419,8 @@ class StepFunction:
             self._ring_events[i] = ev
         return out
 
-    def layout(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor, torch.Tensor]:
-        """Hold pages for the entries' tokens and build the step's context; returns it with the
-        token ids [T] and the wanted rows [R] (both device int32). All or nothing: the pages the
+    def _reserve(self, entries: list[StepEntry]) -> None:
+        """Check the entries and hold pages for their tokens. All or nothing: the pages the
         whole step needs are counted first, and ``OutOfPages`` is raised before any is taken."""
         cache = self.cache
         if not entries:
@@ -255,6 +448,11 @@ class StepFunction:
         for e in entries:
             cache.extend(e.rid, len(e.tokens))
 
+    def layout(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor, torch.Tensor]:
+        """Hold pages for the entries' tokens (``_reserve``) and build the step's context; returns
+        it with the token ids [T] and the wanted rows [R] (both device int32)."""
+        cache = self.cache
+        self._reserve(entries)
         seq_lens = [len(e.tokens) for e in entries]
         seq_ctx = [cache.length(e.rid) for e in entries]
         seq_slot = [cache.slot(e.rid) for e in entries]
@@ -298,7 +496,7 @@ class StepFunction:
             n_tokens=T, n_seqs=S, positions=d_pos, tok_seq=d_tok_seq, cu_seqlens=d_cu,
             seq_ctx=d_ctx, seq_slot=d_slot, block_tables=block_tables, states=cache.states,
             state_groups=cache.state_groups, page_size=cache.page_size, host=host,
-            tile_source=_Tiles(seq_lens, self.device, self._upload))
+            tile_source=_Tiles(seq_lens, self.device, self._upload, self._tile_keys))
         return ctx, d_ids, d_want
 
     @torch.no_grad()
@@ -393,6 +591,64 @@ class StepFunction:
             for e in entries:
                 cache.commit(e.rid, 1)
         return DecodeHandle(event, g.tokens_host[turn], n)
+
+    # ---- any step through a CUDA graph ----
+
+    @staticmethod
+    def _bucket(value: int, buckets: tuple) -> int | None:
+        for b in buckets:
+            if value <= b:
+                return b
+        return None
+
+    def step_graph_for(self, entries: list[StepEntry]) -> "_StepGraph | None":
+        """The captured step that takes ``entries`` (prompt portions beside single tokens, one
+        wanted row per entry at most), capturing it when its bucket has been met
+        ``capture_after`` times; None while it is not worth a capture, or if no bucket fits."""
+        total = sum(len(e.tokens) for e in entries)
+        if any(len(e.want) > 1 for e in entries) or not self._tile_keys:
+            return None
+        tokens = self._bucket(total, STEP_TOKEN_BUCKETS)
+        # a step that does not fill its bucket needs one more sequence: the dummy one
+        seqs = self._bucket(len(entries) + (0 if tokens == total else 1), STEP_SEQ_BUCKETS)
+        if tokens is None or seqs is None or tokens > self.cache.max_len:
+            return None
+        key = (tokens, seqs)
+        g = self._step_graphs.get(key)
+        if g is None:
+            uses = self._step_graph_uses.get(key, 0) + 1
+            self._step_graph_uses[key] = uses
+            if uses <= self.capture_after:
+                return None
+            g = _StepGraph(self, tokens, seqs, self._tile_keys)
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            g.capture(self.model, self._graph_pool)
+            self._step_graphs[key] = g
+        elif not self._tile_keys <= set(g.tile_keys) | {"singles"}:
+            return None          # a part asked for tiles the capture did not know: run eagerly
+        return g
+
+    def launch_step_graph(self, g: "_StepGraph", entries: list[StepEntry], sampling_rows: list[tuple],
+                          fed_on_device: list[bool]) -> DecodeHandle:
+        """Queue one step through its captured graph and return at once (see
+        ``launch_decode_graph``): ``handle.tokens()`` waits for the sampled tokens, in the order
+        of the entries that want one."""
+        cache = self.cache
+        self._reserve(entries)
+        turn = g.turn
+        g.turn = (turn + 1) % g.RING
+        states = [cache.requests[e.rid] for e in entries]
+        wanted = g.fill(turn, entries, states, sampling_rows, fed_on_device)
+        g.dev.copy_(g.host[turn], non_blocking=True)
+        g.graph.replay()
+        g.tokens_host[turn].copy_(g.sampled, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.h2d_bytes += 4 * g.size
+        self.d2h_bytes += 4 * g.seqs_cap
+        self.steps += 1
+        return DecodeHandle(event, g.tokens_host[turn], wanted)
 
     def run_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
                          commit: bool = False) -> list[int]:

@@ -47,8 +47,9 @@ def _ptr(t: torch.Tensor | None):
 
 
 def _stream():
-    # the raw handle of torch's current stream (a capture's side stream included)
-    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    # the raw handle of torch's current stream (a capture's side stream included); the private
+    # getters skip torch.cuda's Python wrappers, which cost more than a kernel launch
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _i32(t: torch.Tensor, name: str) -> torch.Tensor:

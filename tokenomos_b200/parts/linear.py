@@ -68,6 +68,8 @@ class Linear:
         for matrices of a few thousand rows), the TMA + tcgen05 kernel for very tall matrices
         (the head) up to 64 rows, the library elsewhere."""
         m, n = x.shape[0], self.out_features
+        if m > 64:
+            return "library"             # no slicing, no checks: prompt portions come here
         if not ops.gemm_skinny_ok(x[:1], self.weight):
             return "library"
         if n >= 32768 and m <= 64:
