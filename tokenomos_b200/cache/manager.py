@@ -179,9 +179,21 @@ class CacheManager:
             need[k] = max(0, end_block - lo - have)
         return need
 
+    def _already_held(self, st: RequestState, n_new: int) -> bool:
+        """Every group's table already reaches the block of position ``length + n_new - 1`` (the
+        common case of a decoded token inside its last page): nothing to count or to take."""
+        end_block = -(-(st.length + n_new) // self.page_size)
+        for table in st.tables.values():
+            if len(table) < end_block:
+                return False
+        return True
+
     def can_extend(self, rid, n_new: int) -> bool:
-        if self._get(rid).length + n_new > self.max_len:
+        st = self._get(rid)
+        if st.length + n_new > self.max_len:
             return False
+        if self._already_held(st, n_new):
+            return True
         return all(n <= len(self.groups[k].pages) for k, n in self.pages_needed(rid, n_new).items())
 
     def extend(self, rid, n_new: int) -> None:
@@ -190,6 +202,9 @@ class CacheManager:
         if st.length + n_new > self.max_len:
             raise OutOfPages(f"request {rid!r}: {st.length} + {n_new} tokens exceed the longest "
                              f"sequence the block table holds ({self.max_len})")
+        if self._already_held(st, n_new):
+            st.reserved = max(st.reserved, st.length + n_new)
+            return
         need = self.pages_needed(rid, n_new)
         short = {k: (n, len(self.groups[k].pages)) for k, n in need.items()
                  if n > len(self.groups[k].pages)}

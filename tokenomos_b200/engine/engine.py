@@ -166,9 +166,9 @@ class Engine:
         if self.graphs and (decode_only or graph is not None):
             fed = [p.fed_on_device for p in planned]
             if decode_only:
-                handle = self.step_fn.launch_decode_graph(entries, rows, fed)
+                handle = self.step_fn.launch_decode_graph(entries, rows, fed, reserved=True)
             else:
-                handle = self.step_fn.launch_step_graph(graph, entries, rows, fed)
+                handle = self.step_fn.launch_step_graph(graph, entries, rows, fed, reserved=True)
                 self.stats.graph_steps += 1
             self.scheduler.launch(planned)
             self._inflight.append((planned, handle))

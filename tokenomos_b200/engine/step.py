@@ -528,21 +528,23 @@ class StepFunction:
     @torch.no_grad()
     def launch_decode_graph(self, entries: list[StepEntry], sampling_rows: list[tuple],
                             fed_on_device: list[bool] | None = None,
-                            commit: bool = False) -> DecodeHandle:
+                            commit: bool = False, reserved: bool = False) -> DecodeHandle:
         """Queue one decode step for entries of one token each and return at once: the layout
         goes up in one copy from pinned memory, the captured graph (token select, embedding ...
         sampled token) replays, the tokens come back in one copy; ``handle.tokens()`` waits for
         them. ``fed_on_device[i]``: entry i's token is the one its previous step sampled, which
         the host may not have read yet; the device takes it from ``last_token``. Rows of the
-        bucket beyond the entries point at the null slot and the null page."""
+        bucket beyond the entries point at the null slot and the null page. ``reserved``: the
+        caller (the scheduler's plan) already holds the pages and has checked the entries."""
         from tokenomos_b200.sampling import sampler
 
         cache = self.cache
         n = len(entries)
-        for e in entries:
-            if len(e.tokens) != 1:
-                raise ValueError("the decode graph takes one token per request")
-            cache.extend(e.rid, 1)
+        if not reserved:
+            for e in entries:
+                if len(e.tokens) != 1:
+                    raise ValueError("the decode graph takes one token per request")
+                cache.extend(e.rid, 1)
         g = self.decode_graph(n)
         turn = g.turn
         g.turn = (turn + 1) % g.RING
@@ -630,12 +632,13 @@ class StepFunction:
         return g
 
     def launch_step_graph(self, g: "_StepGraph", entries: list[StepEntry], sampling_rows: list[tuple],
-                          fed_on_device: list[bool]) -> DecodeHandle:
+                          fed_on_device: list[bool], reserved: bool = False) -> DecodeHandle:
         """Queue one step through its captured graph and return at once (see
         ``launch_decode_graph``): ``handle.tokens()`` waits for the sampled tokens, in the order
         of the entries that want one."""
         cache = self.cache
-        self._reserve(entries)
+        if not reserved:
+            self._reserve(entries)
         turn = g.turn
         g.turn = (turn + 1) % g.RING
         states = [cache.requests[e.rid] for e in entries]
