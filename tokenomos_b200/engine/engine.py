@@ -17,8 +17,10 @@ from dataclasses import dataclass, field
 
 import torch
 
-from tokenomos_b200.cache.manager import CacheManager
 from collections import deque
+
+from tokenomos_b200 import ops
+from tokenomos_b200.cache.manager import CacheManager
 
 from tokenomos_b200.engine.scheduler import NeedsDrain, Planned, Request, Scheduler
 from tokenomos_b200.engine.step import StepEntry, StepFunction
@@ -69,6 +71,7 @@ class Engine:
         # decode steps queued on the device whose tokens the host has not read: (plan, handle)
         self._inflight: deque = deque()
         self.depth = 1
+        self._checked_at = 0       # stats.steps when the kernels' error word was last read
         self.inbox: queue.Queue[Request] = queue.Queue()
         self.stats = Stats()
 
@@ -106,8 +109,17 @@ class Engine:
         return finished
 
     def drain(self) -> list[Request]:
-        """Read every step in flight: after this the host knows every sampled token."""
-        return self._finish(self._drain())
+        """Read every step in flight: after this the host knows every sampled token. Also the
+        place where a kernel that gave up waiting on a barrier (the tcgen05 GEMM bounds every
+        wait instead of hanging) turns into an exception."""
+        finished = self._finish(self._drain())
+        if self.stats.steps != self._checked_at and self.cache.device.type == "cuda":
+            self._checked_at = self.stats.steps
+            where = ops.gemm_tc_status()
+            if where:
+                raise RuntimeError(f"a tensor-core GEMM gave up waiting on a barrier (place {where}); "
+                                   "the tokens of the steps since the last check are not to be trusted")
+        return finished
 
     @torch.no_grad()
     def step(self) -> list[Request]:
