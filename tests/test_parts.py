@@ -263,3 +263,148 @@ def test_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
         r = r + plain_lfm3.swiglu(x, w, p, torch.float64)
     want = plain_lfm3.rmsnorm(r, w["toy.final.weight"], 1e-5) @ w["toy.embed.weight"].T
     assert (whole.double().cpu() - want).abs().max().item() < 1e-4 * want.abs().max().item()
+
+
+def test_toy_routed_ffn_and_toy_position_encoding_register_build_and_step(tmp_path):
+    """Two more parts defined here, with no change to the framework's files: a feed-forward that
+    routes every token to one of three small experts (router logits and probabilities in 32-bit)
+    and a position encoding (rotary angles of positions divided by a factor), both registered
+    with the parts registry and named by a new architecture's declaration beside the framework's
+    own attention mixer. The model is loaded from a folder and stepped whole, in portions and
+    beside another request; the logits agree with each other and with a plain restatement."""
+    from tokenomos_b200 import models, ops
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.engine.step import StepEntry, StepFunction
+    from tokenomos_b200.parts.linear import Linear
+    from tokenomos_b200.parts.registry import register
+    from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_NORM, BlockSpec, LayerCall, ModelSpec,
+                                           PartSpec, TensorDecl)
+    from tokenomos_b200.weights import write_model_folder
+
+    E, FACTOR = 3, 4.0
+
+    class RoutedFFN:
+        def __init__(self, router, experts):
+            self.router = router.float()                      # [E, width]
+            self.experts = experts                            # [(gate_up Linear, down Linear)]
+
+        def forward(self, x):
+            probs = torch.softmax(x.float() @ self.router.T, dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros_like(x)
+            for e, (gate_up, down) in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    y = down(ops.swiglu(gate_up(x[rows].contiguous())))
+                    out[rows] = (weight[rows, None] * y.float()).to(x.dtype)
+            return out
+
+    def build_routed(params, tensors, rt):
+        experts = [(Linear.fused([tensors[f"gate{e}"], tensors[f"up{e}"]]), Linear(tensors[f"down{e}"]))
+                   for e in range(params["experts"])]
+        return RoutedFFN(tensors["router"], experts)
+
+    class ScaledRope:
+        """Rotary tables of ``position / factor``: the kernels multiply positions by
+        ``inv_freq``, so dividing the frequencies does it."""
+
+        def __init__(self, head_dim, theta, factor, device):
+            idx = torch.arange(0, head_dim, 2, dtype=torch.float32)
+            self.inv_freq = (1.0 / (theta ** (idx / head_dim)) / factor).to(device).contiguous()
+            self.dim = head_dim
+
+        def tables(self, ctx):
+            return self.inv_freq
+
+    register("feed_forward", "toy_routed", build_routed)
+    register("position", "toy_scaled_rope",
+             lambda params, tensors, rt: ScaledRope(params["head_dim"], params["theta"], params["factor"], rt.device))
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.width, self.vocab, self.layers, self.eps = raw["width"], raw["vocab_size"], raw["layers"], raw["eps"]
+            self.heads, self.kv_heads, self.head_dim, self.inter = raw["heads"], raw["kv_heads"], raw["head_dim"], raw["inter"]
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw)
+
+    class ToyArch:
+        names = ("ToyRoutedForCausalLM",)
+        config_class = ToyConfig
+
+        def declare(self, c, tensor_names=()):
+            def norm(name, n):
+                return PartSpec("rmsnorm", {"eps": c.eps}, {"weight": TensorDecl(f"{name}.weight", (n,), ROLE_NORM)})
+            blocks = []
+            for i in range(c.layers):
+                p = f"toy.{i}."
+                H, Hkv, D, d = c.heads, c.kv_heads, c.head_dim, c.width
+                mixer = PartSpec("attention", {
+                    "heads": H, "kv_heads": Hkv, "head_dim": D, "eps": c.eps, "window": None,
+                    "position": {"kind": "toy_scaled_rope", "params": {"head_dim": D, "theta": 100.0, "factor": FACTOR}},
+                }, {"q": TensorDecl(f"{p}q.weight", (H * D, d)), "k": TensorDecl(f"{p}k.weight", (Hkv * D, d)),
+                    "v": TensorDecl(f"{p}v.weight", (Hkv * D, d)), "o": TensorDecl(f"{p}o.weight", (d, H * D)),
+                    "q_norm": TensorDecl(f"{p}qn.weight", (D,), ROLE_NORM),
+                    "k_norm": TensorDecl(f"{p}kn.weight", (D,), ROLE_NORM)})
+                ffn_tensors = {"router": TensorDecl(f"{p}router.weight", (E, d))}
+                for e in range(E):
+                    ffn_tensors[f"gate{e}"] = TensorDecl(f"{p}e{e}.w1.weight", (c.inter, d))
+                    ffn_tensors[f"up{e}"] = TensorDecl(f"{p}e{e}.w3.weight", (c.inter, d))
+                    ffn_tensors[f"down{e}"] = TensorDecl(f"{p}e{e}.w2.weight", (d, c.inter))
+                blocks.append(BlockSpec("prenorm", {
+                    "mixer": mixer, "ffn": PartSpec("toy_routed", {"experts": E}, ffn_tensors),
+                    "pre_mixer_norm": norm(f"{p}n1", d), "pre_ffn_norm": norm(f"{p}n2", d),
+                    "post_mixer_norm": None, "post_ffn_norm": None}))
+            return ModelSpec(c.width, c.vocab, TensorDecl("toy.embed.weight", (c.vocab, c.width), ROLE_EMBEDDING),
+                             tuple(blocks), tuple(LayerCall(i) for i in range(c.layers)),
+                             norm("toy.final", c.width), None)
+
+    models.register(ToyArch())
+    raw = {"architectures": ["ToyRoutedForCausalLM"], "width": 40, "vocab_size": 60, "layers": 2, "eps": 1e-5,
+           "heads": 4, "kv_heads": 2, "head_dim": 16, "inter": 24}
+    folder = write_model_folder(tmp_path / "toy_routed", raw, seed=7, std=0.3)
+    model = models.load(folder, "cuda", models.configure(folder, work="fp32"))
+    assert isinstance(model.blocks[0].ffn, RoutedFFN)
+    assert isinstance(model.blocks[1].mixer.rope, ScaledRope)
+    cache = CacheManager(model.state_specs(), 4, 24, 3, torch.float32, "cuda", max_len=64)
+    step = StepFunction(model, cache)
+    T = 21
+    ids = torch.randint(0, 60, (T,)).tolist()
+    cache.admit("w")
+    whole = step.run([StepEntry("w", ids, list(range(T)))])
+    cache.release("w")
+    cache.admit("other")
+    step.run([StepEntry("other", [1, 2, 3], [])])
+    cache.admit("p")
+    parts = [step.run([StepEntry("p", ids[a:b], list(range(b - a))), StepEntry("other", [7], [])][:1 + (a > 0)])
+             for a, b in ((0, 6), (6, 7), (7, 9), (9, T))]
+    assert torch.allclose(torch.cat(parts), whole, atol=1e-5)
+
+    # the plain restatement: same formulas, float64, whole sequence
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    H, Hkv, D = 4, 2, 16
+    r = w["toy.embed.weight"][ids]
+    cos, sin = plain_lfm3.rope_tables(torch.arange(T) / FACTOR, D, D // 2, 100.0, torch.float64)
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for i in range(2):
+        p = f"toy.{i}."
+        x = plain_lfm3.rmsnorm(r, w[f"{p}n1.weight"], 1e-5)
+        q = plain_lfm3.rmsnorm((x @ w[f"{p}q.weight"].T).view(T, H, D), w[f"{p}qn.weight"], 1e-5)
+        k = plain_lfm3.rmsnorm((x @ w[f"{p}k.weight"].T).view(T, Hkv, D), w[f"{p}kn.weight"], 1e-5)
+        q, k = plain_lfm3.rotate(q, cos, sin), plain_lfm3.rotate(k, cos, sin).repeat_interleave(H // Hkv, 1)
+        v = (x @ w[f"{p}v.weight"].T).view(T, Hkv, D).repeat_interleave(H // Hkv, 1)
+        sc = (torch.einsum("ihd,jhd->hij", q, k) * D ** -0.5).masked_fill(~causal[None], float("-inf"))
+        r = r + torch.einsum("hij,jhd->ihd", sc.softmax(-1), v).reshape(T, H * D) @ w[f"{p}o.weight"].T
+        x = plain_lfm3.rmsnorm(r, w[f"{p}n2.weight"], 1e-5)
+        probs = torch.softmax(x @ w[f"{p}router.weight"].T, dim=-1)
+        weight, choice = probs.max(dim=-1)
+        f = torch.zeros_like(x)
+        for t in range(T):
+            e = int(choice[t])
+            g, u = x[t] @ w[f"{p}e{e}.w1.weight"].T, x[t] @ w[f"{p}e{e}.w3.weight"].T
+            f[t] = weight[t] * ((torch.nn.functional.silu(g) * u) @ w[f"{p}e{e}.w2.weight"].T)
+        r = r + f
+    want = plain_lfm3.rmsnorm(r, w["toy.final.weight"], 1e-5) @ w["toy.embed.weight"].T
+    assert (whole.double().cpu() - want).abs().max().item() < 2e-4 * want.abs().max().item()
