@@ -151,14 +151,15 @@ def kv_bytes_per_token(cfg) -> int:
     return n_attn * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
 
 
-def make_engine(model, batch: int, page: int):
+def make_engine(model, batch: int, page: int, prompt: int = PROMPT, context: int = CONTEXT):
     from tokenomos_b200.engine.engine import Engine
-    pages = batch * (CONTEXT // page) + 2
-    return Engine(model, slots=batch, page=page, max_len=CONTEXT, pages=pages, prefill_budget=PROMPT,
+    pages = batch * (context // page) + 2
+    return Engine(model, slots=batch, page=page, max_len=context, pages=pages, prefill_budget=prompt,
                   graphs=True)
 
 
-def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, seed: int = 0) -> dict:
+def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, seed: int = 0,
+                  prompt: int = PROMPT, context: int = CONTEXT) -> dict:
     """K decode steps timed on the device: prefill ``batch`` prompts, then replay the captured
     decode step with the layout advanced on the host each step (the same work ``LLM.generate``
     does, minus the scheduler)."""
@@ -167,12 +168,12 @@ def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, se
     from tokenomos_b200.engine.step import StepEntry
     from tokenomos_b200.ops import _lib
 
-    eng = make_engine(model, batch, page)
+    eng = make_engine(model, batch, page, prompt, context)
     step_fn, cache = eng.step_fn, eng.cache
     g = torch.Generator().manual_seed(seed)
     last = []
     for r in range(batch):
-        ids = torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist()
+        ids = torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist()
         cache.admit(r)
         step_fn.run([StepEntry(r, ids, [])])
         last.append(int(ids[-1]))
@@ -212,21 +213,21 @@ def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, se
     return out
 
 
-def device_prefill(model, cfg, page: int, reps: int = 3) -> dict:
+def device_prefill(model, cfg, page: int, reps: int = 3, tokens: int = PROMPT) -> dict:
     import torch
 
     from tokenomos_b200.engine.step import StepEntry
 
-    eng = make_engine(model, 1, page)
+    eng = make_engine(model, 1, page, tokens, max(CONTEXT, 2 * tokens))
     g = torch.Generator().manual_seed(1)
-    ids = torch.randint(0, cfg.vocab_size, (PROMPT,), generator=g).tolist()
+    ids = torch.randint(0, cfg.vocab_size, (tokens,), generator=g).tolist()
     times = []
     for i in range(reps + 2):
         eng.cache.admit(i)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        eng.step_fn.run([StepEntry(i, ids, [PROMPT - 1])])
+        eng.step_fn.run([StepEntry(i, ids, [tokens - 1])])
         end.record()
         torch.cuda.synchronize()
         eng.cache.release(i)
@@ -244,12 +245,12 @@ def device_prefill(model, cfg, page: int, reps: int = 3) -> dict:
             per_tok += 3 * d * d + d * d
         else:
             per_tok += (H + 2 * Hkv) * D * d + H * D * d
-            flops += 2 * 2 * H * D * PROMPT * (PROMPT + 1) / 2
-        flops += 2 * PROMPT * per_tok
+            flops += 2 * 2 * H * D * tokens * (tokens + 1) / 2
+        flops += 2 * tokens * per_tok
     flops += 2 * cfg.vocab_size * d
     del eng
     torch.cuda.empty_cache()
-    return {"ms": ms, "tokens": PROMPT, "tok_s": PROMPT / ms * 1e3, "flops": flops}
+    return {"ms": ms, "tokens": tokens, "tok_s": tokens / ms * 1e3, "flops": flops}
 
 
 def e2e_decode(llm, cfg, batch: int, steps: int, warmup: int) -> dict:
@@ -320,6 +321,29 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
             cache.admit(0)
     torch.cuda.synchronize()
     print(f"profile case done: {mode} layers={layers} batch={batch} ctx={ctx} steps={steps}")
+
+
+def run_sweep(model, cfg, page: int, pk: dict) -> int:
+    """Decode at other batch sizes and context lengths, prefill at other lengths: one JSON line
+    of points, each with its fraction of the roofline (decode: bytes the step must read over the
+    measured copy bandwidth; prefill: flops over the measured bf16 GEMM rate)."""
+    conv_layers = sum(k == "conv" for k in cfg.layer_types)
+    out = {"sweep": "1.2B-size LFM3, bf16, random weights", "decode": [], "prefill": []}
+    for ctx in (512, 8192, 32768):
+        for batch in (1, 8, 64):
+            r = device_decode(model, cfg, batch, 32, 4, page, prompt=ctx, context=ctx + 64)
+            mid = (r["ctx_start"] + r["ctx_end"]) / 2
+            nbytes = (weight_bytes(model, cfg) + batch * mid * kv_bytes_per_token(cfg)
+                      + batch * conv_layers * 2 * (cfg.conv_L_cache - 1) * cfg.hidden_size * 2)
+            out["decode"].append({"batch": batch, "ctx": ctx, "ms": round(r["ms_per_step"], 4),
+                                  "tok_s": round(r["tok_s"], 1),
+                                  "frac_hbm": round(nbytes / (r["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3)})
+    for n in (512, 8192, 32768):
+        r = device_prefill(model, cfg, page, reps=2, tokens=n)
+        out["prefill"].append({"tokens": n, "ms": round(r["ms"], 3), "tok_s": round(r["tok_s"], 1),
+                               "frac_bf16": round(r["flops"] / (r["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
+    print(json.dumps(out))
+    return 0
 
 
 def run_workload(name: str, page: int) -> int:
@@ -399,6 +423,8 @@ def main() -> int:
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--sweep", action="store_true",
+                    help="decode and prefill at other batch sizes and context lengths instead")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -434,6 +460,11 @@ def main() -> int:
     llm = LLM(str(folder), work="bf16", slots=args.batch, page=args.page, max_len=CONTEXT,
               pages=pages, prefill_budget=PROMPT, graphs=True)
     model, cfg = llm.model, llm.model.config
+    if args.sweep:
+        rc = run_sweep(model, cfg, args.page, pk)
+        llm.close()
+        tmp.cleanup()
+        return rc
     clocks = Clocks()
     clocks.start()
     main_run = device_decode(model, cfg, args.batch, args.steps, warmup, args.page)
