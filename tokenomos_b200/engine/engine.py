@@ -143,7 +143,7 @@ class Engine:
             entries, rows = [], []
             for p in planned:
                 r = p.req
-                toks = [0] * p.count if p.fed_on_device else r.tokens[p.start:p.start + p.count]
+                toks = [0] * p.count if p.fed_on_device else r.span(p.start, p.count)
                 entries.append(StepEntry(r.rid, toks, [p.count - 1] if p.sample else []))
                 if p.sample:
                     rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed,

@@ -64,6 +64,15 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt + self.output
 
+    def span(self, start: int, count: int) -> list[int]:
+        """``tokens[start:start + count]`` without joining the two lists."""
+        n = len(self.prompt)
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        return self.prompt[start:] + self.output[:start + count - n]
+
     @property
     def total(self) -> int:
         """Tokens of the sequence so far, those still in flight included."""
@@ -171,8 +180,9 @@ class Scheduler:
         # 1 and 2: running requests, oldest first; a decoding one takes one token, one still
         # reading its prompt a portion of what is left of the budget. Victims are always the
         # newest, which this loop has not planned yet.
+        preempted = False                     # membership tests only once somebody has left
         for req in list(self.running):
-            if req not in self.running:       # preempted while serving an older one
+            if preempted and req not in self.running:       # preempted while serving an older one
                 continue
             if budget <= 0:
                 break
@@ -187,9 +197,10 @@ class Scheduler:
                     raise OutOfPages(f"request {req.rid} cannot get its pages although it is "
                                      "alone in the pool")
                 self._preempt(victim)
+                preempted = True
                 if victim is req:
                     break
-            if req not in self.running:
+            if preempted and req not in self.running:
                 continue
             fed = req.inflight > 0
             if fed and not (count == 1 and req.inflight == 1):
@@ -201,7 +212,7 @@ class Scheduler:
         # 3: admissions, in arrival order (a preempted request is at the front)
         while self.waiting and budget > 0 and len(self.running) < self.max_seqs:
             req = self.waiting[0]
-            need = self._pages_for(len(req.tokens) + 1)
+            need = self._pages_for(len(req.prompt) + len(req.output) + 1)
             if need + self._outstanding() > cache.free_pages() or cache.free_slots() < 1:
                 break
             self.waiting.popleft()

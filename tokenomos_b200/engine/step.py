@@ -255,7 +255,9 @@ class _StepGraph:
         self.size = o
         self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.host_np = [h.numpy() for h in self.host]
-        self.table_len = [{g: [0] * S for g in self.groups} for _ in range(self.RING)]
+        # what each staging buffer's block-table rows hold: (request, entries written) per row
+        self.table_rows = [{g: [(None, 0)] * S for g in self.groups} for _ in range(self.RING)]
+        self.windowless = {g: cache.groups[g].window is None for g in self.groups}
         self.tokens_host = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.turn = 0
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
@@ -346,20 +348,30 @@ class _StepGraph:
         put("want_slot", want_slot)
         o, _ = self.off["sampling"]
         sampler.pack_rows_into(h[o:o + 6 * S], sampling_rows, S)
+        # block tables: a row that held the same request the last time this staging buffer was
+        # used only gets its new entries (a window group's entries also turn to 0: rewritten)
         for g in self.groups:
             o, _ = self.off[("table", g)]
-            held = self.table_len[turn][g]
-            for i, st in enumerate(states):
+            held = self.table_rows[turn][g]
+            incremental = self.windowless[g]
+            for i, (e, st) in enumerate(zip(entries, states)):
                 row = st.tables[g]
                 base = o + i * self.width
-                h[base:base + len(row)] = row
-                if held[i] > len(row):
-                    h[base + len(row):base + held[i]] = 0
-                held[i] = len(row)
+                held_rid, held_len = held[i]
+                if incremental and held_rid == (e.rid, st.epoch) and held_len <= len(row):
+                    if held_len < len(row):
+                        h[base + held_len:base + len(row)] = row[held_len:]
+                else:
+                    h[base:base + len(row)] = row
+                    if held_len > len(row):
+                        h[base + len(row):base + held_len] = 0
+                held[i] = ((e.rid, st.epoch), len(row))
             for i in range(n, S):
-                if held[i]:
-                    h[o + i * self.width:o + i * self.width + held[i]] = 0
-                    held[i] = 0
+                if held[i][1]:
+                    h[o + i * self.width:o + i * self.width + held[i][1]] = 0
+                if held[i][0] is None:
+                    break                    # rows beyond were cleared before
+                held[i] = (None, 0)
         for key in self.tile_keys:
             seq, tok0, off, cnt = _Tiles.cut(lens, key[0], key[1])
             o, _ = self.off[("tiles", key)]
