@@ -460,9 +460,10 @@ def test_sample_is_batch_invariant_and_step_dependent():
 
 # ---- tensor-core attention (bfloat16, head sizes 64 and 128) -------------------------------------
 
-def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None):
+def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None, tc=False):
     """Like ``attention_case`` but through the tensor-core kernels: multi-token sequences go to
-    the prefill kernel, single-token ones to the decode kernel (split ``nsplit`` ways)."""
+    the prefill kernel (``tc``: the tcgen05 one), single-token ones to the decode kernel (split
+    ``nsplit`` ways)."""
     from tokenomos_b200 import ops
     dtype = torch.bfloat16
     assert ops.attention_mma_supported(H, Hkv, D, dtype)
@@ -490,7 +491,7 @@ def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None)
         ks.append(k), vs.append(v), qs.append(q)
     positions = [p for (c, n) in seqs for p in range(c, c + n)]
     tok_seq = [s for s, (c, n) in enumerate(seqs) for _ in range(n)]
-    per_tile = ops.attention_prefill_mma_tokens(H, Hkv)
+    per_tile = ops.attention_prefill_tc_tokens(H, Hkv) if tc else ops.attention_prefill_mma_tokens(H, Hkv)
     tok0, ntok, singles, start = [], [], [], 0
     for c, n in seqs:
         if n == 1:
@@ -503,8 +504,11 @@ def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None)
     q_dev, pool_dev = dev(torch.cat(qs), dtype), dev(pool, dtype)
     out = torch.full_like(q_dev, float("nan"))
     if tok0:
-        ops.attention_prefill_mma(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table),
-                                  i32(tok0), i32(ntok), window, D ** -0.5)
+        prefill = ops.attention_prefill_tc if tc else ops.attention_prefill_mma
+        prefill(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table), i32(tok0), i32(ntok),
+                window, D ** -0.5)
+        if tc:
+            assert ops.attention_prefill_tc_status() == 0
     if singles:
         ops.attention_decode_mma(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table),
                                  i32(singles), window, D ** -0.5, nsplit or 1)
@@ -530,6 +534,36 @@ def test_attention_mma_mixed_batches(H, Hkv, D, P, nsplit):
     seqs = [(0, 1), (17, 3), (0, 40), (40, 100), (333, 1), (5, 2), (64, 64), (1000, 1), (0, 130)]
     got, want = attention_mma_case(H, Hkv, D, P, seqs, nsplit=nsplit)
     close(got, want, torch.bfloat16, f"mma attention H{H} Hkv{Hkv} D{D} P{P} split {nsplit}")
+
+
+@pytest.mark.parametrize("H, Hkv, P", [(32, 8, 16), (8, 8, 64), (16, 1, 8), (6, 3, 7), (4, 4, 32)])
+def test_attention_tc_prefill(H, Hkv, P):
+    """The tcgen05 prefill kernel (head size 64): portions of every length beside cached
+    positions, tiles that are not full, groups of 1, 2, 4 and 16, a page size that is no power of
+    two."""
+    from tokenomos_b200 import ops
+    assert ops.attention_prefill_tc_supported(H, Hkv, 64, torch.bfloat16)
+    assert not ops.attention_prefill_tc_supported(H, Hkv, 128, torch.bfloat16)
+    seqs = [(17, 3), (0, 40), (40, 100), (5, 2), (64, 64), (0, 130), (300, 257), (1, 63), (0, 2)]
+    got, want = attention_mma_case(H, Hkv, 64, P, seqs, tc=True)
+    close(got, want, torch.bfloat16, f"tc attention H{H} Hkv{Hkv} P{P}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_tc_prefill_window_and_far_key(window):
+    seqs = [(0, 150), (20, 30), (3, 2), (200, 70)]
+    got, want = attention_mma_case(8, 2, 64, 16, seqs, window=window, tc=True)
+    close(got, want, torch.bfloat16, f"tc window {window}")
+
+    def far(s, q, k, v):
+        q[:] = 0.0
+        k[:] = 0.0
+        q[:, :, 0] = 8.0
+        k[13, :, 0] = 8.0
+
+    got, want = attention_mma_case(8, 2, 64, 16, [(670, 31), (0, 700)], boost=far, tc=True)
+    close(got, want, torch.bfloat16, "tc far key")
+    assert (got.double().cpu() - want).abs().max().item() < 0.05
 
 
 @pytest.mark.parametrize("window", [1, 5, 64, 100])

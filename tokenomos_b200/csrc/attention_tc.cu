@@ -1,0 +1,415 @@
+// Paged prefill attention on the fifth-generation tensor cores, for bfloat16 and head size 64:
+// S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
+// the online softmax runs on 128 threads, one query row each.
+//
+// A CTA takes up to 128 rows: 128 / G tokens of one sequence with the G query heads that share one
+// KV head (row = token * G + head), and walks the keys in tiles of 64, this step's own keys
+// included. Three groups of warps, coupled by mbarriers only:
+//
+//   warps 0-3  stage the tiles: Q once, then per tile K and V from the paged cache with cp.async
+//              into 128-byte-swizzled K-major tiles. K is used as it lands ([key][d] is the B
+//              operand of S = Q K^T). V must be contracted over its keys, so the same warps turn
+//              the [key][d] tile into [d][key] with ldmatrix.trans + stmatrix (8 x 8 blocks).
+//   warp 8     one lane issues the MMAs: S_j (128 x 64 x 64) into one of two S accumulators, so
+//              that S_{j+1} is computed while the softmax of tile j runs, and P_j V_j into a
+//              third accumulator.
+//   warps 4-7  thread r owns row r: reads S_j from tensor memory (twice: row maximum, then
+//              probabilities), masks (causal, window), keeps the running maximum and sum in
+//              32-bit, writes P_j as bfloat16 into the A operand tile of the second product, and
+//              folds the finished P_{j-1} V_{j-1} into its 64 output registers, one tile late:
+//              O = (O + PV_{j-1}) * 2^(m_{j-1} - m_j).
+//
+// Masking, scale, rounding of P to bfloat16 and the unrounded row sum are those of the other
+// attention kernels (Tokenomos kernels/attention/paged.py:67-76,150,267;
+// models/blocks/attention.py:31-40,173). Keys past the tile's last position are never read.
+//
+// Every mbarrier wait is bounded (about a second, or until another thread has recorded an
+// error); the kernel then leaves its loops, frees its tensor memory and returns, and
+// tk_attn_prefill_tc_status() reports where it gave up.
+#include <math.h>
+
+#include "paged_tiles.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int AT_D = 64;                  // head size
+constexpr int AT_ROWS = 128;              // query rows per CTA (UMMA M)
+constexpr int AT_KEYS = 64;               // keys per tile (UMMA N of S, K of P V)
+constexpr int AT_THREADS = 288;           // 4 staging warps, 4 softmax warps, 1 MMA warp
+constexpr int AT_STAGES = 3;              // key / value tiles in flight
+constexpr int AT_KV_BYTES = AT_KEYS * AT_D * 2;
+constexpr int AT_Q_BYTES = AT_ROWS * AT_D * 2;
+constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;
+constexpr long long AT_WAIT_CYCLES = 2000000000LL;
+
+__device__ int g_at_error = 0;
+
+__device__ __forceinline__ bool at_wait(uint32_t bar, uint32_t parity, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    int it = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++it & 255) == 0) {
+            if (*(volatile int*)&g_at_error != 0) return false;
+            if (clock64() - start > AT_WAIT_CYCLES) {
+                atomicCAS(&g_at_error, 0, where);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3])
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_bfloat16* out,
+                       const int* positions, const int* tok_seq, const int* block_table, int bt_stride,
+                       const int* tile_tok0, const int* tile_ntok, int H, int Hkv, int P, int window,
+                       float scale, int p_shift) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_tile = base;
+    const uint32_t k_tile0 = q_tile + AT_Q_BYTES;                         // AT_STAGES stages
+    const uint32_t vt_tile0 = k_tile0 + AT_STAGES * AT_KV_BYTES;          // [d][key]
+    const uint32_t v_stage0 = vt_tile0 + AT_STAGES * AT_KV_BYTES;         // [key][d] as it lands
+    const uint32_t p_tile = v_stage0 + AT_STAGES * AT_KV_BYTES;
+    const uint32_t bars = p_tile + AT_P_BYTES;
+    auto kv_full = [&](int s) { return bars + (uint32_t)s * 8; };
+    auto kv_empty = [&](int s) { return bars + (uint32_t)(AT_STAGES + s) * 8; };
+    auto s_full = [&](int b) { return bars + (uint32_t)(2 * AT_STAGES + b) * 8; };
+    auto s_free = [&](int b) { return bars + (uint32_t)(2 * AT_STAGES + 2 + b) * 8; };
+    const uint32_t p_full = bars + (2 * AT_STAGES + 4) * 8, pv_full = p_full + 8, pv_free = p_full + 16;
+    const uint32_t tmem_slot = p_full + 24;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int G = H / Hkv;
+    // the grid is one-dimensional with the KV head fastest and the tiles in reverse: a causal
+    // tile late in its sequence reads the most keys, so the longest CTAs start first
+    const int kvh = blockIdx.x % Hkv;
+    const int tile = gridDim.x / Hkv - 1 - blockIdx.x / Hkv;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    if (ntok <= 0) return;       // an unused entry of a fixed-length tile list (captured steps)
+    const int rows = ntok * G;
+    const int seq = tok_seq[tok0];
+    const int* bt_row = block_table + (size_t)seq * bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos_first = positions[tok0];
+    const int pos_last = pos_first + ntok - 1;       // consecutive positions within a tile
+    const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int j_begin = (lo / AT_KEYS) * AT_KEYS;
+    const int n_tiles = (pos_last - j_begin) / AT_KEYS + 1;
+
+    if (tid == 0) {
+        for (int i = 0; i < AT_STAGES; ++i) {
+            mbar_init(kv_full(i), 1);
+            mbar_init(kv_empty(i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full(i), 1);
+            mbar_init(s_free(i), 4);
+        }
+        mbar_init(p_full, 1);
+        mbar_init(pv_full, 1);
+        mbar_init(pv_free, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot_ptr;
+    const uint32_t tmem_pv = tmem + 2 * AT_KEYS;         // columns [128, 192); S_b at [64 b, 64 b + 64)
+
+    if (warp < 4) {
+        // ---- staging ----
+        PagedLoader<AT_D, AT_KEYS, 128> loader;
+        loader.init(tid, kvh, Hkv, P, p_shift);
+        // Q: row r = token * G + head; rows past the tile are zero
+        for (int i = tid; i < AT_ROWS * (AT_D / 8); i += 128) {
+            const int r = i >> 3, c = i & 7;
+            const bool valid = r < rows;
+            const __nv_bfloat16* src = q;
+            if (valid) src = q + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D + c * 8;
+            cp_async16(q_tile + tile_off<AT_D>(r, c), src, valid);
+        }
+        // two tiles' copies are in flight while a third is turned: the copy of tile it + 2 is
+        // issued once tile it is handed over
+        bool ok = true;
+        auto issue = [&](int it) {
+            const int s = it % AT_STAGES;
+            if (it >= AT_STAGES) ok = ok && at_wait(kv_empty(s), (uint32_t)((it / AT_STAGES - 1) & 1), 1);
+            const int j0 = j_begin + it * AT_KEYS;
+            const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage0 + (uint32_t)s * AT_KV_BYTES;
+            if (p_shift >= 0) {
+                loader.issue(kt, vs, pool, bt_row, j0, lo, pos_last);
+            } else {
+                load_tile<AT_D>(kt, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
+                load_tile<AT_D>(vs, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+            }
+            cp_async_commit();
+        };
+        issue(0);
+        if (n_tiles > 1) issue(1);
+        for (int it = 0; it < n_tiles && ok; ++it) {
+            const int s = it % AT_STAGES;
+            if (it + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            // V [key][d] -> [d][key]: 64 blocks of 8 x 8, four per instruction pair, sixteen pairs
+            const uint32_t vs = v_stage0 + (uint32_t)s * AT_KV_BYTES, vt = vt_tile0 + (uint32_t)s * AT_KV_BYTES;
+            const int m = lane >> 3, i8 = lane & 7;
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                const int b = (warp * 4 + o) * 4 + m;            // this lane's block: key block, d chunk
+                const int kb = b >> 3, c = b & 7;
+                uint32_t r4[4];
+                ldsm_x4_trans(r4, vs + tile_off<AT_D>(kb * 8 + i8, c));
+                stsm_x4(vt + tile_off<AT_D>(c * 8 + i8, kb), r4);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (tid == 0) mbar_arrive(kv_full(s));
+            if (it + 2 < n_tiles) issue(it + 2);
+        }
+    } else if (warp == 8) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(AT_KEYS);      // 128 x 64, both products
+            const uint64_t qdesc = umma_desc(q_tile), pdesc = umma_desc(p_tile);
+            bool ok = true;
+            auto issue_s = [&](int j) {
+                const int s = j % AT_STAGES, b = j & 1;
+                ok = ok && at_wait(kv_full(s), (uint32_t)((j / AT_STAGES) & 1), 2);
+                if (ok && j >= 2) ok = at_wait(s_free(b), (uint32_t)(((j >> 1) - 1) & 1), 3);
+                if (!ok) return;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t kdesc = umma_desc(k_tile0 + (uint32_t)s * AT_KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < AT_D / 16; ++k)
+                    umma_bf16(tmem + (uint32_t)b * AT_KEYS, qdesc + 2 * k, kdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                umma_commit(s_full(b));
+            };
+            issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) issue_s(j + 1);
+                if (!ok) break;
+                ok = at_wait(p_full, (uint32_t)(j & 1), 4);
+                if (ok && j >= 1) ok = at_wait(pv_free, (uint32_t)((j - 1) & 1), 5);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = j % AT_STAGES;
+                const uint64_t vdesc = umma_desc(vt_tile0 + (uint32_t)s * AT_KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < AT_KEYS / 16; ++k)
+                    umma_bf16(tmem_pv, pdesc + 2 * k, vdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                umma_commit(pv_full);
+                umma_commit(kv_empty(s));
+            }
+        }
+    } else {
+        // ---- softmax: thread r owns query row r ----
+        const int r = tid - 128;
+        const int quarter = warp & 3;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int pos_r = r < rows ? pos_first + r / G : -1;
+        const int lo_r = window > 0 ? pos_r - window + 1 : 0;
+        const float scale_log2 = scale * LOG2E;
+        float m_run = -INFINITY, l_run = 0.f;
+        float o[AT_D];
+#pragma unroll
+        for (int i = 0; i < AT_D; ++i) o[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1, j0 = j_begin + j * AT_KEYS;
+            ok = at_wait(s_full(b), (uint32_t)((j >> 1) & 1), 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t s_addr = tmem + lane_base + (uint32_t)b * AT_KEYS;
+            // a tile every row of the CTA sees whole needs no comparisons
+            const bool masked = j0 + AT_KEYS - 1 > pos_first || (window > 0 && j0 < pos_last - window + 1) ||
+                                rows < AT_ROWS;
+            // pass 1: the row's maximum over the tile's visible keys (the scale is positive)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < AT_KEYS; c += 16) {
+                float part[16];
+                tmem_ld16(s_addr + (uint32_t)c, part);
+                if (masked) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int key = j0 + c + e;
+                        if (key <= pos_r && key >= lo_r) mx = fmaxf(mx, part[e]);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) mx = fmaxf(mx, part[e]);
+                }
+            }
+            mx *= scale_log2;
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = m_new == -INFINITY ? 1.0f : fast_exp2(m_run - m_new);
+            // the product of the tile before has had a whole softmax pass to finish: fold it in
+            if (j >= 1) {
+                ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < AT_D; c += 16) {
+                    float part[16];
+                    tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) o[c + e] = (o[c + e] + part[e]) * alpha;
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pv_free);
+            }
+            l_run *= alpha;
+            // pass 2: probabilities, rounded to bfloat16 into the A operand of P V
+#pragma unroll
+            for (int c = 0; c < AT_KEYS; c += 16) {
+                float part[16];
+                tmem_ld16(s_addr + (uint32_t)c, part);
+                uint32_t packed[8];
+                if (masked) {
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2) {
+                        float p0 = 0.f, p1 = 0.f;
+                        const int key = j0 + c + e;
+                        if (key <= pos_r && key >= lo_r) p0 = fast_exp2(fmaf(part[e], scale_log2, -m_new));
+                        if (key + 1 <= pos_r && key + 1 >= lo_r) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, -m_new));
+                        l_run += p0 + p1;
+                        packed[e >> 1] = pack_bf16_pair(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2) {
+                        const float p0 = fast_exp2(fmaf(part[e], scale_log2, -m_new));
+                        const float p1 = fast_exp2(fmaf(part[e + 1], scale_log2, -m_new));
+                        l_run += p0 + p1;
+                        packed[e >> 1] = pack_bf16_pair(p0, p1);
+                    }
+                }
+                const uint32_t at0 = p_tile + tile_off<AT_D>(r, c >> 3), at1 = p_tile + tile_off<AT_D>(r, (c >> 3) + 1);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at0), "r"(packed[0]), "r"(packed[1]),
+                             "r"(packed[2]), "r"(packed[3])
+                             : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at1), "r"(packed[4]), "r"(packed[5]),
+                             "r"(packed[6]), "r"(packed[7])
+                             : "memory");
+            }
+            m_run = m_new;
+            // S_b is read: the MMA warp may overwrite it with the tile after next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free(b));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (r == 0) mbar_arrive(p_full);
+        }
+        if (ok) {
+            ok = at_wait(pv_full, (uint32_t)((n_tiles - 1) & 1), 8);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
+#pragma unroll
+            for (int c = 0; c < AT_D; c += 16) {
+                float part[16];
+                tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+                if (dst != nullptr) {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2)
+                        packed[e >> 1] = pack_bf16_pair((o[c + e] + part[e]) * inv, (o[c + e + 1] + part[e + 1]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        }
+    }
+    // ---- teardown: the tensor memory goes back whatever happened above ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+}  // namespace
+
+// Whether the tcgen05 prefill kernel takes this shape: head size 64, a group that divides 128.
+TK_API int tk_attn_prefill_tc_supported(int H, int Hkv, int D) {
+    if (Hkv <= 0 || H % Hkv || D != AT_D) return 0;
+    const int G = H / Hkv;
+    return G >= 1 && G <= AT_ROWS && AT_ROWS % G == 0;
+}
+
+// Tokens of one sequence that a tile of this kernel holds (what the caller cuts portions into).
+TK_API int tk_attn_prefill_tc_tokens(int H, int Hkv) { return AT_ROWS / (H / Hkv); }
+
+// 0, or where a CTA gave up waiting on a barrier since the last call (1 staging, 2-5 MMA issuer,
+// 6-8 softmax). Resets the word.
+TK_API int tk_attn_prefill_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_at_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_at_error, &zero, sizeof(int));
+    return v;
+}
+
+// q: [T, H, 64] bfloat16; kv_pool: [pages, 2, Hkv, P, 64]; out: [T, H, 64]; tiles of at most
+// tk_attn_prefill_tc_tokens tokens of one sequence with consecutive positions; window 0 = none.
+TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, const int* positions,
+                              const int* tok_seq, const int* block_table, int bt_stride,
+                              const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
+                              int P, int window, float scale, cudaStream_t stream) {
+    TK_CHECK_ARG(tk_attn_prefill_tc_supported(H, Hkv, D), "attn_prefill_tc: shape H=%d Hkv=%d D=%d is not taken "
+                 "(head size 64, a group that divides 128)", H, Hkv, D);
+    TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_tc: bad page size or tile count");
+    if (n_tiles == 0) return 0;
+    int shift = -1;
+    if ((P & (P - 1)) == 0) {
+        shift = 0;
+        while ((1 << shift) < P) ++shift;
+    }
+    const size_t smem = 1024 + AT_Q_BYTES + 3 * AT_STAGES * AT_KV_BYTES + AT_P_BYTES + (2 * AT_STAGES + 8) * 8 + 64;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+        e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv), dim3(AT_THREADS), smem, stream,
+                      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions, tok_seq,
+                      block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, shift);
+    if (e != cudaSuccess) {
+        tk_set_error("attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return -2;
+    }
+    return 0;
+}

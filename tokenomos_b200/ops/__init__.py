@@ -17,6 +17,8 @@ __all__ = [
     "KernelError", "available", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
+    "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
+    "attention_prefill_tc_status",
     "conv_gated", "conv_min_tile",
     "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "gather_rows_select",
 ]
@@ -239,6 +241,37 @@ def attention_prefill_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Ten
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
               _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
               float(scale), _stream())
+
+
+def attention_prefill_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tcgen05 prefill kernel takes this shape (bfloat16, head size 64, a group that
+    divides 128)."""
+    return dtype == torch.bfloat16 and bool(_lib.call("tk_attn_prefill_tc_supported", heads, kv_heads, head_dim))
+
+
+def attention_prefill_tc_tokens(heads: int, kv_heads: int) -> int:
+    """Tokens of one sequence per tile of ``attention_prefill_tc``."""
+    return _lib.call("tk_attn_prefill_tc_tokens", heads, kv_heads)
+
+
+def attention_prefill_tc(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
+                         positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+                         tile_tok0: torch.Tensor, tile_ntok: torch.Tensor, window: int | None,
+                         scale: float) -> None:
+    """``attention_prefill_mma`` on tcgen05.mma with the accumulators in tensor memory, for tiles
+    of ``attention_prefill_tc_tokens`` tokens of one sequence; writes the tiles' rows of ``out``."""
+    _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
+    T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_tc")
+    _lib.call("tk_attn_prefill_tc", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
+              block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
+              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
+              float(scale), _stream())
+
+
+def attention_prefill_tc_status() -> int:
+    """0, or where a CTA of the tcgen05 prefill kernel gave up waiting since the last call."""
+    return _lib.call("tk_attn_prefill_tc_status")
 
 
 def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,

@@ -10,6 +10,8 @@ reads the cache of another call of the layer list.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from tokenomos_b200 import ops
@@ -80,6 +82,8 @@ class Attention:
         out.copy_(res.view_as(out))
         return out
 
+    # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
+    prefill_tc = os.environ.get("TOKENOMOS_B200_ATTN_TC", "1") != "0"
     # CTAs the decode kernel should put on the GPU before it stops splitting keys further: three
     # fit on an SM (shared memory), and several waves of them even out the last, partial wave
     DECODE_CTAS = 4 * 444
@@ -91,11 +95,16 @@ class Attention:
         over their keys so that a small batch still fills the GPU."""
         if out is None:
             out = torch.empty_like(q)
-        per_tile = ops.attention_prefill_mma_tokens(self.heads, self.kv_heads)
+        # prompt portions: the tcgen05 kernel (tiles of 128 rows) where it takes the shape, else
+        # the mma.sync one (tiles of 64 rows)
+        tc = self.prefill_tc and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim,
+                                                                     q.dtype)
+        per_tile = (ops.attention_prefill_tc_tokens if tc else ops.attention_prefill_mma_tokens)(
+            self.heads, self.kv_heads)
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
         if tok0.numel():
-            ops.attention_prefill_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok,
-                                      self.window, self.scale)
+            (ops.attention_prefill_tc if tc else ops.attention_prefill_mma)(
+                q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window, self.scale)
         singles = ctx.singles()
         if singles.numel():
             longest = ctx.host.longest
