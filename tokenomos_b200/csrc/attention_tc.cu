@@ -66,6 +66,30 @@ __device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Packed 32-bit arithmetic (two lanes per instruction): the softmax threads are bound by the
+// number of instructions they issue, and most of them are elementwise on pairs.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -161,7 +185,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         bool ok = true;
         auto issue = [&](int it) {
             const int s = it % AT_STAGES;
-            if (it >= AT_STAGES) ok = ok && at_wait(kv_empty(s), (uint32_t)((it / AT_STAGES - 1) & 1), 1);
+            if (it >= AT_STAGES && ok) ok = at_wait(kv_empty(s), (uint32_t)((it / AT_STAGES - 1) & 1), 1);
             const int j0 = j_begin + it * AT_KEYS;
             const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage0 + (uint32_t)s * AT_KV_BYTES;
             if (p_shift >= 0) {
@@ -174,7 +198,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         };
         issue(0);
         if (n_tiles > 1) issue(1);
-        for (int it = 0; it < n_tiles && ok; ++it) {
+        // (after a failed wait the loop still runs to its end, without waiting: every thread must
+        // meet every named barrier)
+        for (int it = 0; it < n_tiles; ++it) {
             const int s = it % AT_STAGES;
             if (it + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
             asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -237,16 +263,18 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         const int pos_r = r < rows ? pos_first + r / G : -1;
         const int lo_r = window > 0 ? pos_r - window + 1 : 0;
         const float scale_log2 = scale * LOG2E;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o[AT_D];
+        float m_run = -INFINITY;
+        float2 l_run = make_float2(0.f, 0.f);            // the row sum in two lanes (even / odd keys)
+        float2 o[AT_D / 2];                              // output columns in pairs
 #pragma unroll
-        for (int i = 0; i < AT_D; ++i) o[i] = 0.f;
+        for (int i = 0; i < AT_D / 2; ++i) o[i] = make_float2(0.f, 0.f);
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1, j0 = j_begin + j * AT_KEYS;
-            ok = at_wait(s_full(b), (uint32_t)((j >> 1) & 1), 6);
+            // (after a failed wait the loop still runs to its end, without waiting: every thread
+            // must meet every named barrier)
+            if (ok) ok = at_wait(s_full(b), (uint32_t)((j >> 1) & 1), 6);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t s_addr = tmem + lane_base + (uint32_t)b * AT_KEYS;
             // a tile every row of the CTA sees whole needs no comparisons
@@ -255,18 +283,18 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             // pass 1: the row's maximum over the tile's visible keys (the scale is positive)
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < AT_KEYS; c += 16) {
-                float part[16];
-                tmem_ld16(s_addr + (uint32_t)c, part);
+            for (int c = 0; c < AT_KEYS; c += 32) {
+                float part[32];
+                tmem_ld32(s_addr + (uint32_t)c, part);
                 if (masked) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
+                    for (int e = 0; e < 32; ++e) {
                         const int key = j0 + c + e;
                         if (key <= pos_r && key >= lo_r) mx = fmaxf(mx, part[e]);
                     }
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) mx = fmaxf(mx, part[e]);
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, part[e]);
                 }
             }
             mx *= scale_log2;
@@ -274,54 +302,66 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             const float alpha = m_new == -INFINITY ? 1.0f : fast_exp2(m_run - m_new);
             // the product of the tile before has had a whole softmax pass to finish: fold it in
             if (j >= 1) {
-                ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
+                if (ok) ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // far from the diagonal the maximum rarely moves: then the fold is an add
+                const bool rescale = __any_sync(0xffffffffu, alpha != 1.0f);
 #pragma unroll
-                for (int c = 0; c < AT_D; c += 16) {
-                    float part[16];
-                    tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+                for (int c = 0; c < AT_D; c += 32) {
+                    float part[32];
+                    tmem_ld32(tmem_pv + lane_base + (uint32_t)c, part);
+                    if (rescale) {
+                        const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) o[c + e] = (o[c + e] + part[e]) * alpha;
+                        for (int e = 0; e < 32; e += 2)     // (o + pv) * alpha
+                            o[(c + e) >> 1] = fma2(o[(c + e) >> 1], a2, make_float2(part[e] * alpha, part[e + 1] * alpha));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2)
+                            o[(c + e) >> 1] = add2(o[(c + e) >> 1], make_float2(part[e], part[e + 1]));
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pv_free);
             }
-            l_run *= alpha;
+            l_run.x *= alpha;
+            l_run.y *= alpha;
             // pass 2: probabilities, rounded to bfloat16 into the A operand of P V
 #pragma unroll
-            for (int c = 0; c < AT_KEYS; c += 16) {
-                float part[16];
-                tmem_ld16(s_addr + (uint32_t)c, part);
-                uint32_t packed[8];
+            for (int c = 0; c < AT_KEYS; c += 32) {
+                float part[32];
+                tmem_ld32(s_addr + (uint32_t)c, part);
+                uint32_t packed[16];
                 if (masked) {
 #pragma unroll
-                    for (int e = 0; e < 16; e += 2) {
+                    for (int e = 0; e < 32; e += 2) {
                         float p0 = 0.f, p1 = 0.f;
                         const int key = j0 + c + e;
                         if (key <= pos_r && key >= lo_r) p0 = fast_exp2(fmaf(part[e], scale_log2, -m_new));
                         if (key + 1 <= pos_r && key + 1 >= lo_r) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, -m_new));
-                        l_run += p0 + p1;
+                        l_run = add2(l_run, make_float2(p0, p1));
                         packed[e >> 1] = pack_bf16_pair(p0, p1);
                     }
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 16; e += 2) {
-                        const float p0 = fast_exp2(fmaf(part[e], scale_log2, -m_new));
-                        const float p1 = fast_exp2(fmaf(part[e + 1], scale_log2, -m_new));
-                        l_run += p0 + p1;
-                        packed[e >> 1] = pack_bf16_pair(p0, p1);
+                    const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_new, -m_new);
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float2 x = fma2(make_float2(part[e], part[e + 1]), sc2, nm2);
+                        const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        l_run = add2(l_run, pp);
+                        packed[e >> 1] = pack_bf16_pair(pp.x, pp.y);
                     }
                 }
-                const uint32_t at0 = p_tile + tile_off<AT_D>(r, c >> 3), at1 = p_tile + tile_off<AT_D>(r, (c >> 3) + 1);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at0), "r"(packed[0]), "r"(packed[1]),
-                             "r"(packed[2]), "r"(packed[3])
-                             : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at1), "r"(packed[4]), "r"(packed[5]),
-                             "r"(packed[6]), "r"(packed[7])
-                             : "memory");
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t at = p_tile + tile_off<AT_D>(r, (c >> 3) + k);
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(at), "r"(packed[4 * k]),
+                                 "r"(packed[4 * k + 1]), "r"(packed[4 * k + 2]), "r"(packed[4 * k + 3])
+                                 : "memory");
+                }
             }
             m_run = m_new;
             // S_b is read: the MMA warp may overwrite it with the tile after next
@@ -338,7 +378,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            const float l_row = l_run.x + l_run.y;
+            const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
             __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
 #pragma unroll
             for (int c = 0; c < AT_D; c += 16) {
@@ -348,7 +389,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                     uint32_t packed[8];
 #pragma unroll
                     for (int e = 0; e < 16; e += 2)
-                        packed[e >> 1] = pack_bf16_pair((o[c + e] + part[e]) * inv, (o[c + e + 1] + part[e + 1]) * inv);
+                        packed[e >> 1] = pack_bf16_pair((o[(c + e) >> 1].x + part[e]) * inv,
+                                                        (o[(c + e) >> 1].y + part[e + 1]) * inv);
                     *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
