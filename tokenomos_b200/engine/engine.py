@@ -115,10 +115,10 @@ class Engine:
         finished = self._finish(self._drain())
         if self.stats.steps != self._checked_at and self.cache.device.type == "cuda":
             self._checked_at = self.stats.steps
-            where = ops.gemm_tc_status()
-            if where:
-                raise RuntimeError(f"a tensor-core GEMM gave up waiting on a barrier (place {where}); "
-                                   "the tokens of the steps since the last check are not to be trusted")
+            for what, where in (("GEMM", ops.gemm_tc_status()), ("attention", ops.attention_prefill_tc_status())):
+                if where:
+                    raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
+                                       "the tokens of the steps since the last check are not to be trusted")
         return finished
 
     @torch.no_grad()
