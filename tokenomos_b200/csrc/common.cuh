@@ -60,13 +60,26 @@ __device__ __forceinline__ float round_as(float v) {
     return to_f<T>(from_f<T>(v));
 }
 
-// silu(g) = g * sigmoid(g), rounded as a store in T would. 16-bit storage takes the fast
-// exponential and division (a few ulp of a float, far below the rounding that follows), so
-// every 16-bit kernel that applies the activation gets the same bits; 32-bit storage takes the
-// accurate ones.
+// silu(g) = g * sigmoid(g), rounded as a store in T would. 16-bit storage takes the special
+// function unit's exponential and reciprocal (a few ulp of a float, far below the rounding that
+// follows), spelled out instruction by instruction so that the scalar form here and the packed
+// form in the activation kernel give the same bits; 32-bit storage takes the accurate functions.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float TK_NEG_LOG2E = -1.4426950408889634f;
+
 template <typename T>
 __device__ __forceinline__ float silu_as(float g) {
-    if constexpr (sizeof(T) == 2) return round_as<T>(__fdividef(g, 1.0f + __expf(-g)));
+    if constexpr (sizeof(T) == 2)
+        return round_as<T>(__fmul_rn(g, rcp_approx(__fadd_rn(1.0f, ex2_approx(__fmul_rn(g, TK_NEG_LOG2E))))));
     return g / (1.0f + expf(-g));
 }
 

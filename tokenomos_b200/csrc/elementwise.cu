@@ -308,6 +308,24 @@ __global__ void swiglu_kernel(const T* gu, T* out, int64_t total,
     }
 }
 
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 // 16 bytes of gate and of up per thread and step (block == 0 or block a multiple of 8 channels),
 // two steps' loads in flight. One block row of the grid per token row, so no thread divides by
 // the row length. The sigmoid uses the fast exponential and reciprocal: their error (a few ulp
@@ -339,15 +357,23 @@ swiglu_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int rows, int int
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         if (v0 + k * 256 >= per_row) continue;
-        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&graw[k]);
-        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uraw[k]);
+        // two channels per step: packed 32-bit multiplies and adds around the exponential and the
+        // reciprocal (the same operations in the same order as silu_as), one conversion to a
+        // bfloat16 pair, one packed multiply with the up pair (a single rounding, as a 32-bit
+        // product rounded once)
+        const uint32_t* g2 = reinterpret_cast<const uint32_t*>(&graw[k]);
+        const uint32_t* u2 = reinterpret_cast<const uint32_t*>(&uraw[k]);
         uint4 packed;
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+        uint32_t* o2 = reinterpret_cast<uint32_t*>(&packed);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float gf = __bfloat162float(g[e]);
-            const float s = silu_as<__nv_bfloat16>(gf);
-            o[e] = __float2bfloat16_rn(s * __bfloat162float(u[e]));
+        for (int e = 0; e < 4; ++e) {
+            const float2 gf = make_float2(__uint_as_float(g2[e] << 16), __uint_as_float(g2[e] & 0xffff0000u));
+            float2 x = mul2(gf, make_float2(TK_NEG_LOG2E, TK_NEG_LOG2E));
+            x = add2(make_float2(1.0f, 1.0f), make_float2(ex2_approx(x.x), ex2_approx(x.y)));
+            const float2 sl = mul2(gf, make_float2(rcp_approx(x.x), rcp_approx(x.y)));
+            const __nv_bfloat162 sb = __floats2bfloat162_rn(sl.x, sl.y);
+            const __nv_bfloat162 prod = __hmul2(sb, *reinterpret_cast<const __nv_bfloat162*>(&u2[e]));
+            o2[e] = *reinterpret_cast<const uint32_t*>(&prod);
         }
         *reinterpret_cast<uint4*>(out + (size_t)t * inter + c[k]) = packed;
     }
