@@ -11,13 +11,13 @@
 //              operand of S = Q K^T). V must be contracted over its keys, so the same warps turn
 //              the [key][d] tile into [d][key] with ldmatrix.trans + stmatrix (8 x 8 blocks).
 //   warp 8     one lane issues the MMAs: S_j (128 x 64 x 64) into one of two S accumulators, so
-//              that S_{j+1} is computed while the softmax of tile j runs, and P_j V_j into a
-//              third accumulator.
-//   warps 4-7  thread r owns row r: reads S_j from tensor memory (twice: row maximum, then
-//              probabilities), masks (causal, window), keeps the running maximum and sum in
-//              32-bit, writes P_j as bfloat16 into the A operand tile of the second product, and
-//              folds the finished P_{j-1} V_{j-1} into its 64 output registers, one tile late:
-//              O = (O + PV_{j-1}) * 2^(m_{j-1} - m_j).
+//              that S_{j+1} is computed while the softmax of tile j runs, and O += P_j V_j into
+//              a third accumulator that lives in tensor memory for the whole walk.
+//   warps 4-7  thread r owns row r: reads S_j from tensor memory into registers, masks (causal,
+//              window), keeps a reference maximum and the row sum in 32-bit, and writes P_j as
+//              bfloat16 into the A operand tile of the second product. The reference maximum
+//              follows the true one lazily (see the softmax section); only when it is raised is
+//              the accumulated output read, scaled and written back (tcgen05.ld / tcgen05.st).
 //
 // Masking, scale, rounding of P to bfloat16 and the unrounded row sum are those of the other
 // attention kernels (Tokenomos kernels/attention/paged.py:67-76,150,267;
@@ -41,6 +41,7 @@ constexpr int AT_STAGES = 3;              // key / value tiles in flight
 constexpr int AT_KV_BYTES = AT_KEYS * AT_D * 2;
 constexpr int AT_Q_BYTES = AT_ROWS * AT_D * 2;
 constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;
+constexpr float AT_LAZY = 8.0f;           // log2 of how far a probability may exceed 1 before a rescale
 constexpr long long AT_WAIT_CYCLES = 2000000000LL;
 
 __device__ int g_at_error = 0;
@@ -121,7 +122,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
     auto kv_empty = [&](int s) { return bars + (uint32_t)(AT_STAGES + s) * 8; };
     auto s_full = [&](int b) { return bars + (uint32_t)(2 * AT_STAGES + b) * 8; };
     auto s_free = [&](int b) { return bars + (uint32_t)(2 * AT_STAGES + 2 + b) * 8; };
-    const uint32_t p_full = bars + (2 * AT_STAGES + 4) * 8, pv_full = p_full + 8, pv_free = p_full + 16;
+    const uint32_t p_full = bars + (2 * AT_STAGES + 4) * 8, pv_full = p_full + 8;
     const uint32_t tmem_slot = p_full + 24;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -153,7 +154,6 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         }
         mbar_init(p_full, 1);
         mbar_init(pv_full, 1);
-        mbar_init(pv_free, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -168,7 +168,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
     const uint32_t tmem = *tmem_slot_ptr;
     const uint32_t tmem_pv = tmem + 2 * AT_KEYS;         // columns [128, 192); S_b at [64 b, 64 b + 64)
 
+    // The register file is shared unevenly: the staging warps give registers up and the softmax
+    // warps (a whole row of scores each) take them.
     if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         // ---- staging ----
         PagedLoader<AT_D, AT_KEYS, 128> loader;
         loader.init(tid, kvh, Hkv, P, p_shift);
@@ -242,32 +245,35 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) issue_s(j + 1);
                 if (!ok) break;
-                ok = at_wait(p_full, (uint32_t)(j & 1), 4);
-                if (ok && j >= 1) ok = at_wait(pv_free, (uint32_t)((j - 1) & 1), 5);
+                ok = at_wait(p_full, (uint32_t)(j & 1), 4);    // P_j written, the output rescaled if need be
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int s = j % AT_STAGES;
                 const uint64_t vdesc = umma_desc(vt_tile0 + (uint32_t)s * AT_KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < AT_KEYS / 16; ++k)
-                    umma_bf16(tmem_pv, pdesc + 2 * k, vdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                    umma_bf16(tmem_pv, pdesc + 2 * k, vdesc + 2 * k, idesc, (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(pv_full);
                 umma_commit(kv_empty(s));
             }
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 128;");
         // ---- softmax: thread r owns query row r ----
+        // The output accumulates in tensor memory over all key tiles (P V with the accumulate
+        // flag) under a reference maximum m_ref that follows the true maximum lazily: it is
+        // raised, and the accumulated row and sum rescaled, only when some row of the warp sees a
+        // score more than AT_LAZY (in log2 units) above it. Until then probabilities may exceed 1,
+        // by at most 2^AT_LAZY; in 32-bit accumulation, with the division by the row sum at the
+        // end, that changes nothing but the scale the intermediate values live at.
         const int r = tid - 128;
         const int quarter = warp & 3;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos_r = r < rows ? pos_first + r / G : -1;
         const int lo_r = window > 0 ? pos_r - window + 1 : 0;
         const float scale_log2 = scale * LOG2E;
-        float m_run = -INFINITY;
-        float2 l_run = make_float2(0.f, 0.f);            // the row sum in two lanes (even / odd keys)
-        float2 o[AT_D / 2];                              // output columns in pairs
-#pragma unroll
-        for (int i = 0; i < AT_D / 2; ++i) o[i] = make_float2(0.f, 0.f);
+        float m_ref = -INFINITY;
+        float2 l_run = make_float2(0.f, 0.f), l_alt = make_float2(0.f, 0.f);   // the row sum in four lanes
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1, j0 = j_begin + j * AT_KEYS;
@@ -277,81 +283,81 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             ok = __all_sync(0xffffffffu, ok);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t s_addr = tmem + lane_base + (uint32_t)b * AT_KEYS;
+            float s_lo[32], s_hi[32];                    // the row's 64 scores stay in registers
+            tmem_ld32(s_addr, s_lo);
+            tmem_ld32(s_addr + 32u, s_hi);
+            // S_b is read: the MMA warp may overwrite it with the tile after next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free(b));
             // a tile every row of the CTA sees whole needs no comparisons
             const bool masked = j0 + AT_KEYS - 1 > pos_first || (window > 0 && j0 < pos_last - window + 1) ||
                                 rows < AT_ROWS;
-            // pass 1: the row's maximum over the tile's visible keys (the scale is positive)
-            float mx = -INFINITY;
+            // the row's maximum over the tile's visible keys (the scale is positive)
+            // (four chains: a thread has few other warps to hide a 64-deep dependency behind)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (masked) {
 #pragma unroll
-            for (int c = 0; c < AT_KEYS; c += 32) {
-                float part[32];
-                tmem_ld32(s_addr + (uint32_t)c, part);
-                if (masked) {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int key = j0 + c + e;
-                        if (key <= pos_r && key >= lo_r) mx = fmaxf(mx, part[e]);
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, part[e]);
+                for (int e = 0; e < 32; ++e) {
+                    const int key = j0 + e;
+                    if (key <= pos_r && key >= lo_r) mx4[e & 1] = fmaxf(mx4[e & 1], s_lo[e]);
+                    if (key + 32 <= pos_r && key + 32 >= lo_r) mx4[2 + (e & 1)] = fmaxf(mx4[2 + (e & 1)], s_hi[e]);
                 }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], fmaxf(s_lo[e], s_hi[e]));
             }
-            mx *= scale_log2;
-            const float m_new = fmaxf(m_run, mx);
-            const float alpha = m_new == -INFINITY ? 1.0f : fast_exp2(m_run - m_new);
-            // the product of the tile before has had a whole softmax pass to finish: fold it in
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            const bool raise = __any_sync(0xffffffffu, mx > m_ref + AT_LAZY);
+            // the product of the tile before is complete: the P tile may be rewritten and the
+            // accumulated output rescaled
             if (j >= 1) {
                 if (ok) ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
                 ok = __all_sync(0xffffffffu, ok);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // far from the diagonal the maximum rarely moves: then the fold is an add
-                const bool rescale = __any_sync(0xffffffffu, alpha != 1.0f);
-#pragma unroll
-                for (int c = 0; c < AT_D; c += 32) {
-                    float part[32];
-                    tmem_ld32(tmem_pv + lane_base + (uint32_t)c, part);
-                    if (rescale) {
-                        const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2)     // (o + pv) * alpha
-                            o[(c + e) >> 1] = fma2(o[(c + e) >> 1], a2, make_float2(part[e] * alpha, part[e + 1] * alpha));
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2)
-                            o[(c + e) >> 1] = add2(o[(c + e) >> 1], make_float2(part[e], part[e + 1]));
-                    }
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pv_free);
             }
-            l_run.x *= alpha;
-            l_run.y *= alpha;
-            // pass 2: probabilities, rounded to bfloat16 into the A operand of P V
+            if (raise) {
+                const float m_new = fmaxf(m_ref, mx);
+                if (j >= 1) {
+                    const float alpha = m_new == -INFINITY ? 1.0f : fast_exp2(m_ref - m_new);
 #pragma unroll
-            for (int c = 0; c < AT_KEYS; c += 32) {
-                float part[32];
-                tmem_ld32(s_addr + (uint32_t)c, part);
+                    for (int c = 0; c < AT_D; c += 16) {          // (narrow: the scores stay in registers)
+                        float part[16];
+                        tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) part[e] *= alpha;
+                        tmem_st16(tmem_pv + lane_base + (uint32_t)c, part);
+                    }
+                    l_run.x *= alpha;
+                    l_run.y *= alpha;
+                    l_alt.x *= alpha;
+                    l_alt.y *= alpha;
+                }
+                m_ref = m_new;
+            }
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+            // probabilities, rounded to bfloat16 into the A operand of P V
+            auto emit = [&](const float (&part)[32], int c) {
                 uint32_t packed[16];
                 if (masked) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         float p0 = 0.f, p1 = 0.f;
                         const int key = j0 + c + e;
-                        if (key <= pos_r && key >= lo_r) p0 = fast_exp2(fmaf(part[e], scale_log2, -m_new));
-                        if (key + 1 <= pos_r && key + 1 >= lo_r) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, -m_new));
-                        l_run = add2(l_run, make_float2(p0, p1));
+                        if (key <= pos_r && key >= lo_r) p0 = fast_exp2(fmaf(part[e], scale_log2, neg_m));
+                        if (key + 1 <= pos_r && key + 1 >= lo_r) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, neg_m));
+                        if (e & 2) l_alt = add2(l_alt, make_float2(p0, p1));
+                        else l_run = add2(l_run, make_float2(p0, p1));
                         packed[e >> 1] = pack_bf16_pair(p0, p1);
                     }
                 } else {
-#pragma unroll
-                    const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_new, -m_new);
+                    const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         const float2 x = fma2(make_float2(part[e], part[e + 1]), sc2, nm2);
                         const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                        l_run = add2(l_run, pp);
+                        if (e & 2) l_alt = add2(l_alt, pp);
+                        else l_run = add2(l_run, pp);
                         packed[e >> 1] = pack_bf16_pair(pp.x, pp.y);
                     }
                 }
@@ -362,12 +368,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                                  "r"(packed[4 * k + 1]), "r"(packed[4 * k + 2]), "r"(packed[4 * k + 3])
                                  : "memory");
                 }
-            }
-            m_run = m_new;
-            // S_b is read: the MMA warp may overwrite it with the tile after next
+            };
+            emit(s_lo, 0);
+            emit(s_hi, 32);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free(b));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 3, 128;" ::: "memory");
             if (r == 0) mbar_arrive(p_full);
@@ -378,7 +382,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float l_row = l_run.x + l_run.y;
+            const float l_row = (l_run.x + l_run.y) + (l_alt.x + l_alt.y);
             const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
             __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
 #pragma unroll
@@ -389,8 +393,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                     uint32_t packed[8];
 #pragma unroll
                     for (int e = 0; e < 16; e += 2)
-                        packed[e >> 1] = pack_bf16_pair((o[(c + e) >> 1].x + part[e]) * inv,
-                                                        (o[(c + e) >> 1].y + part[e + 1]) * inv);
+                        packed[e >> 1] = pack_bf16_pair(part[e] * inv, part[e + 1] * inv);
                     *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
@@ -418,7 +421,7 @@ TK_API int tk_attn_prefill_tc_supported(int H, int Hkv, int D) {
 // Tokens of one sequence that a tile of this kernel holds (what the caller cuts portions into).
 TK_API int tk_attn_prefill_tc_tokens(int H, int Hkv) { return AT_ROWS / (H / Hkv); }
 
-// 0, or where a CTA gave up waiting on a barrier since the last call (1 staging, 2-5 MMA issuer,
+// 0, or where a CTA gave up waiting on a barrier since the last call (1 staging, 2-4 MMA issuer,
 // 6-8 softmax). Resets the word.
 TK_API int tk_attn_prefill_tc_status() {
     int v = 0, zero = 0;
