@@ -566,6 +566,30 @@ def test_attention_tc_prefill_window_and_far_key(window):
     assert (got.double().cpu() - want).abs().max().item() < 0.05
 
 
+@pytest.mark.parametrize("shape", ["rising", "falling", "leap"])
+def test_attention_tc_prefill_moving_maxima(shape):
+    """The tcgen05 kernel rescales its accumulated output only when a score exceeds its reference
+    maximum by 2^8. Scores that climb a few units per key tile (probabilities above 1 for a while,
+    then a rescale every other tile), scores that fall from the first key on, and one late score
+    far above all before it go through both branches."""
+    def boost(s, q, k, v):
+        n = k.shape[0]
+        ramp = torch.arange(n, dtype=torch.float64)
+        q[:, :, 0] = 8.0
+        if shape == "rising":
+            k[:, :, 0] = (ramp * 0.05)[:, None]
+        elif shape == "falling":
+            k[:, :, 0] = ((n - ramp) * 0.05)[:, None]
+        else:
+            k[:, :, 0] = 0.0
+            k[n // 2 + 37, :, 0] = 60.0
+        k[:] = k.to(torch.bfloat16).double()
+
+    seqs = [(0, 700), (300, 257), (650, 31)]
+    got, want = attention_mma_case(8, 2, 64, 16, seqs, boost=boost, tc=True)
+    close(got, want, torch.bfloat16, f"tc moving maxima {shape}")
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 100])
 def test_attention_mma_window(window):
     seqs = [(0, 150), (70, 1), (20, 30), (3, 2), (500, 1), (63, 1)]
