@@ -7,15 +7,17 @@
 // included. Three groups of warps, coupled by mbarriers only:
 //
 //   warps 0-3  stage the tiles: Q once, then per tile K and V from the paged cache with cp.async
-//              into 128-byte-swizzled K-major tiles. K is used as it lands ([key][d] is the B
-//              operand of S = Q K^T). V must be contracted over its keys, so the same warps turn
-//              the [key][d] tile into [d][key] with ldmatrix.trans + stmatrix (8 x 8 blocks).
+//              into 128-byte-swizzled K-major tiles (three stages of K and turned V). K is used as
+//              it lands ([key][d] is the B operand of S = Q K^T). V must be contracted over its
+//              keys, so the same warps turn the [key][d] tile into [d][key] with ldmatrix.trans +
+//              stmatrix (8 x 8 blocks).
 //   warp 8     one lane issues the MMAs: S_j (128 x 64 x 64) into one of two S accumulators, so
 //              that S_{j+1} is computed while the softmax of tile j runs, and O += P_j V_j into
 //              a third accumulator that lives in tensor memory for the whole walk.
 //   warps 4-7  thread r owns row r: reads S_j from tensor memory into registers, masks (causal,
 //              window), keeps a reference maximum and the row sum in 32-bit, and writes P_j as
-//              bfloat16 into the A operand tile of the second product. The reference maximum
+//              bfloat16 into one of two A operand tiles of the second product, so that writing
+//              P_j never waits for P_{j-1} V_{j-1}. The reference maximum
 //              follows the true one lazily (see the softmax section); only when it is raised is
 //              the accumulated output read, scaled and written back (tcgen05.ld / tcgen05.st).
 //
@@ -69,25 +71,12 @@ __device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
 
 // Packed 32-bit arithmetic (two lanes per instruction): the softmax threads are bound by the
 // number of instructions they issue, and most of them are elementwise on pairs.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-    return d;
-}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "add.rn.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
 
@@ -115,9 +104,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
     const uint32_t q_tile = base;
     const uint32_t k_tile0 = q_tile + AT_Q_BYTES;                         // AT_STAGES stages
     const uint32_t vt_tile0 = k_tile0 + AT_STAGES * AT_KV_BYTES;          // [d][key]
-    const uint32_t v_stage0 = vt_tile0 + AT_STAGES * AT_KV_BYTES;         // [key][d] as it lands
-    const uint32_t p_tile = v_stage0 + AT_STAGES * AT_KV_BYTES;
-    const uint32_t bars = p_tile + AT_P_BYTES;
+    const uint32_t v_stage = vt_tile0 + AT_STAGES * AT_KV_BYTES;          // [key][d] as it lands (one tile)
+    const uint32_t p_tile0 = v_stage + AT_KV_BYTES;                       // two P tiles, used in turn
+    const uint32_t bars = p_tile0 + 2 * AT_P_BYTES;
     auto kv_full = [&](int s) { return bars + (uint32_t)s * 8; };
     auto kv_empty = [&](int s) { return bars + (uint32_t)(AT_STAGES + s) * 8; };
     auto s_full = [&](int b) { return bars + (uint32_t)(2 * AT_STAGES + b) * 8; };
@@ -183,32 +172,37 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             if (valid) src = q + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D + c * 8;
             cp_async16(q_tile + tile_off<AT_D>(r, c), src, valid);
         }
-        // two tiles' copies are in flight while a third is turned: the copy of tile it + 2 is
-        // issued once tile it is handed over
+        // One copy is in flight while the tile before it is turned and handed over. The copy of
+        // tile it + 1 needs the stage that tile it - 2 held, which P V of that tile gives back a
+        // whole softmax pass before S of tile it + 1 is wanted; looking two tiles ahead instead
+        // made this warp group wait for the stage of tile it - 1 with tile it + 1 lying unturned,
+        // and the softmax threads waited for S every tile. The block-table entries of a tile are
+        // fetched one tile ahead of its copies.
         bool ok = true;
         auto issue = [&](int it) {
             const int s = it % AT_STAGES;
             if (it >= AT_STAGES && ok) ok = at_wait(kv_empty(s), (uint32_t)((it / AT_STAGES - 1) & 1), 1);
             const int j0 = j_begin + it * AT_KEYS;
-            const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage0 + (uint32_t)s * AT_KV_BYTES;
+            const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage;
             if (p_shift >= 0) {
-                loader.issue(kt, vs, pool, bt_row, j0, lo, pos_last);
+                loader.issue_looked_up(kt, vs, pool, j0, lo, pos_last);
+                if (it + 1 < n_tiles) loader.lookup(bt_row, j0 + AT_KEYS, lo, pos_last);
             } else {
                 load_tile<AT_D>(kt, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
                 load_tile<AT_D>(vs, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
             }
             cp_async_commit();
         };
+        if (p_shift >= 0) loader.lookup(bt_row, j_begin, lo, pos_last);
         issue(0);
-        if (n_tiles > 1) issue(1);
         // (after a failed wait the loop still runs to its end, without waiting: every thread must
         // meet every named barrier)
         for (int it = 0; it < n_tiles; ++it) {
             const int s = it % AT_STAGES;
-            if (it + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+            cp_async_wait<0>();
             asm volatile("bar.sync 2, 128;" ::: "memory");
             // V [key][d] -> [d][key]: 64 blocks of 8 x 8, four per instruction pair, sixteen pairs
-            const uint32_t vs = v_stage0 + (uint32_t)s * AT_KV_BYTES, vt = vt_tile0 + (uint32_t)s * AT_KV_BYTES;
+            const uint32_t vs = v_stage, vt = vt_tile0 + (uint32_t)s * AT_KV_BYTES;
             const int m = lane >> 3, i8 = lane & 7;
 #pragma unroll
             for (int o = 0; o < 4; ++o) {
@@ -221,13 +215,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (tid == 0) mbar_arrive(kv_full(s));
-            if (it + 2 < n_tiles) issue(it + 2);
+            if (it + 1 < n_tiles) issue(it + 1);
         }
     } else if (warp == 8) {
         // ---- MMA issuer ----
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(AT_KEYS);      // 128 x 64, both products
-            const uint64_t qdesc = umma_desc(q_tile), pdesc = umma_desc(p_tile);
+            const uint64_t qdesc = umma_desc(q_tile);
             bool ok = true;
             auto issue_s = [&](int j) {
                 const int s = j % AT_STAGES, b = j & 1;
@@ -250,6 +244,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int s = j % AT_STAGES;
                 const uint64_t vdesc = umma_desc(vt_tile0 + (uint32_t)s * AT_KV_BYTES);
+                const uint64_t pdesc = umma_desc(p_tile0 + (uint32_t)(j & 1) * AT_P_BYTES);
 #pragma unroll
                 for (int k = 0; k < AT_KEYS / 16; ++k)
                     umma_bf16(tmem_pv, pdesc + 2 * k, vdesc + 2 * k, idesc, (j > 0 || k > 0) ? 1u : 0u);
@@ -305,20 +300,17 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], fmaxf(s_lo[e], s_hi[e]));
+                for (int e = 0; e < 32; ++e) mx4[e & 3] = fmax3(mx4[e & 3], s_lo[e], s_hi[e]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             const bool raise = __any_sync(0xffffffffu, mx > m_ref + AT_LAZY);
-            // the product of the tile before is complete: the P tile may be rewritten and the
-            // accumulated output rescaled
-            if (j >= 1) {
-                if (ok) ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
-                ok = __all_sync(0xffffffffu, ok);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
             if (raise) {
                 const float m_new = fmaxf(m_ref, mx);
                 if (j >= 1) {
+                    // the product of the tile before must have landed before the output is touched
+                    if (ok) ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
+                    ok = __all_sync(0xffffffffu, ok);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const float alpha = m_new == -INFINITY ? 1.0f : fast_exp2(m_ref - m_new);
 #pragma unroll
                     for (int c = 0; c < AT_D; c += 16) {          // (narrow: the scores stay in registers)
@@ -337,6 +329,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             }
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             // probabilities, rounded to bfloat16 into the A operand of P V
+            // (P_j goes to the tile that P_{j-2} used: S_j is complete, and the tensor pipe runs
+            // in order, so the product that read P_{j-2} is complete too)
+            const uint32_t p_tile = p_tile0 + (uint32_t)(j & 1) * AT_P_BYTES;
             auto emit = [&](const float (&part)[32], int c) {
                 uint32_t packed[16];
                 if (masked) {
@@ -445,7 +440,7 @@ TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, con
         shift = 0;
         while ((1 << shift) < P) ++shift;
     }
-    const size_t smem = 1024 + AT_Q_BYTES + 3 * AT_STAGES * AT_KV_BYTES + AT_P_BYTES + (2 * AT_STAGES + 8) * 8 + 64;
+    const size_t smem = 1024 + AT_Q_BYTES + (2 * AT_STAGES + 1) * AT_KV_BYTES + 2 * AT_P_BYTES + (2 * AT_STAGES + 8) * 8 + 64;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
         e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv), dim3(AT_THREADS), smem, stream,

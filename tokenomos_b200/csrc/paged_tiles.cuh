@@ -89,6 +89,32 @@ struct PagedLoader {
             cp_async16(vtile + dst[k], valid ? src + v_delta : src, valid);
         }
     }
+
+    // The same in two halves, so that the block-table loads of a tile are in flight long before
+    // its copies are issued (four dependent lookups in a row otherwise sit on the loader's path):
+    // lookup() fetches the page numbers of the tile at j0, issue_looked_up() uses them.
+    int page[PER];
+
+    __device__ __forceinline__ void lookup(const int* bt_row, int j0, int j_first, int j_last) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int j = min(max(j0 + r0 + k * STEP, j_first), j_last);     // always a held position
+            page[k] = bt_row[j >> p_shift];
+        }
+    }
+
+    __device__ __forceinline__ void issue_looked_up(uint32_t ktile, uint32_t vtile, const __nv_bfloat16* pool,
+                                                    int j0, int j_first, int j_last) const {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int j = j0 + r0 + k * STEP;
+            const bool valid = j >= j_first && j <= j_last;
+            const __nv_bfloat16* src = pool;
+            if (valid) src = pool + (size_t)page[k] * page_stride + head_off + (size_t)(j & p_mask) * D;
+            cp_async16(ktile + dst[k], src, valid);
+            cp_async16(vtile + dst[k], valid ? src + v_delta : src, valid);
+        }
+    }
 };
 
 constexpr float LOG2E = 1.4426950408889634f;
