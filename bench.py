@@ -381,10 +381,18 @@ def run_workload(name: str, page: int) -> int:
         steps_before = llm.engine.stats.steps
         decode_before, graph_before = llm.engine.stats.decode_steps, llm.engine.stats.graph_steps
         clocks.start()
-        t0 = time.perf_counter()
-        outs = llm.generate(prompts, SamplingParams(max_tokens=w["new_tokens"]))
-        torch.cuda.synchronize()
-        seconds = time.perf_counter() - t0
+        # three steady-state passes, the median reported: the loop is host-bound in places, and
+        # the host is a shared machine
+        passes = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            outs = llm.generate(prompts, SamplingParams(max_tokens=w["new_tokens"]))
+            torch.cuda.synchronize()
+            passes.append(time.perf_counter() - t0)
+        seconds = sorted(passes)[1]
+        steps_per_pass = (llm.engine.stats.steps - steps_before) // 3
+        decode_per_pass = (llm.engine.stats.decode_steps - decode_before) // 3
+        graph_per_pass = (llm.engine.stats.graph_steps - graph_before) // 3
     finally:
         clock_report = clocks.stop()
         stats = llm.engine.stats
@@ -396,10 +404,10 @@ def run_workload(name: str, page: int) -> int:
         "workload": name, "metric": "tokens/s over the whole call (prompt + generated)",
         "value": round((sum(lengths) + generated) / seconds, 1), "unit": "tokens/s",
         "generated_per_s": round(generated / seconds, 1), "seconds": round(seconds, 3),
-        "first_pass_seconds": round(first_seconds, 3),
-        "captured_step_shapes": len(llm_graphs), "graph_steps": stats.graph_steps - graph_before,
+        "passes_seconds": [round(t, 3) for t in passes], "first_pass_seconds": round(first_seconds, 3),
+        "captured_step_shapes": len(llm_graphs), "graph_steps": graph_per_pass,
         "requests": w["requests"], "prompt_tokens": sum(lengths), "generated": generated,
-        "steps": stats.steps - steps_before, "decode_steps": stats.decode_steps - decode_before, "preemptions": stats.preemptions,
+        "steps": steps_per_pass, "decode_steps": decode_per_pass, "preemptions": stats.preemptions,
         "dtype": "bf16", "data": "synthetic token ids, random-init weights N(0, 0.02)",
         "config": {"layers": len(w["config"]["layer_types"]), "hidden_size": w["config"]["hidden_size"],
                    "intermediate_size": w["config"]["intermediate_size"], "max_len": w["max_len"],

@@ -86,6 +86,9 @@ class RequestState:
     # per group: blocks below this index have been given back (a window has passed them); every
     # block from here to the end of the table holds a page
     first_live: dict[tuple, int] = field(default_factory=dict)
+    # tokens the tables of every group already reach (the shortest table times the page size):
+    # an extension below this needs no page
+    held_tokens: int = 0
 
 
 class CacheManager:
@@ -129,6 +132,9 @@ class CacheManager:
                 if src in self.state_groups:
                     self.state_groups[key] = self.state_groups[src]
 
+        # the groups whose pages a window gives back as a request advances
+        self._windowed = [(k, g) for k, g in self.groups.items() if g.window is not None]
+
     # ---- sizes ----
 
     def bytes_per_page(self) -> int:
@@ -158,6 +164,8 @@ class CacheManager:
             raise OutOfPages("no free slot")
         self._epoch = getattr(self, "_epoch", 0) + 1
         st = RequestState(self.slots.take(), tables={k: [] for k in self.groups}, epoch=self._epoch)
+        if not self.groups:
+            st.held_tokens = self.max_len          # nothing is paged: no extension needs a page
         self.requests[rid] = st
         return st
 
@@ -196,6 +204,23 @@ class CacheManager:
             return True
         return all(n <= len(self.groups[k].pages) for k, n in self.pages_needed(rid, n_new).items())
 
+    def try_extend(self, rid, n_new: int) -> bool:
+        """``can_extend`` and, if it can, ``extend``, in one call: what the scheduler asks for
+        every running request every step. The common case, a decoded token inside its last page,
+        is two comparisons."""
+        st = self.requests.get(rid)
+        if st is None:
+            raise CacheError(f"request {rid!r} is not live")
+        end = st.length + n_new
+        if end <= st.held_tokens and end <= self.max_len:
+            if end > st.reserved:
+                st.reserved = end
+            return True
+        if not self.can_extend(rid, n_new):
+            return False
+        self.extend(rid, n_new)
+        return True
+
     def extend(self, rid, n_new: int) -> None:
         """Hold pages for positions ``[length, length + n_new)`` in every group; all or nothing."""
         st = self._get(rid)
@@ -217,6 +242,7 @@ class CacheManager:
             for _ in range(len(table), end_block):
                 table.append(g.pages.take())
         st.reserved = max(st.reserved, st.length + n_new)
+        st.held_tokens = min(len(t) for t in st.tables.values()) * self.page_size
 
     def commit(self, rid, n_new: int) -> None:
         """The step wrote ``n_new`` tokens: advance, and give back what a window has passed."""
@@ -224,9 +250,7 @@ class CacheManager:
         if st.length + n_new > st.reserved:
             raise CacheError(f"request {rid!r}: commit of {n_new} tokens beyond what was extended")
         st.length += n_new
-        for k, g in self.groups.items():
-            if g.window is None:
-                continue
+        for k, g in self._windowed:
             table = st.tables[k]
             passed = min(self._first_needed_block(g, st.length), len(table))
             for b in range(st.first_live.get(k, 0), passed):

@@ -186,10 +186,14 @@ class Scheduler:
                 continue
             if budget <= 0:
                 break
-            count = min(req.pending, budget)
+            total = len(req.prompt) + len(req.output) + req.inflight
+            count = min(total - req.computed, budget)
             if count <= 0:
                 continue                      # everything is sampled; waiting for its tokens
-            while not cache.can_extend(req.rid, count):
+            fed = req.inflight > 0
+            if fed and not (count == 1 and req.inflight == 1):
+                raise NeedsDrain("only a single decoded token can be fed on the device")
+            while not cache.try_extend(req.rid, count):
                 if self.inflight():
                     raise NeedsDrain("a preemption needs every token value on the host")
                 victim = self.running[-1]
@@ -202,11 +206,7 @@ class Scheduler:
                     break
             if preempted and req not in self.running:
                 continue
-            fed = req.inflight > 0
-            if fed and not (count == 1 and req.inflight == 1):
-                raise NeedsDrain("only a single decoded token can be fed on the device")
-            cache.extend(req.rid, count)
-            sample = req.computed + count == req.total and not req.sampled_all
+            sample = req.computed + count == total and len(req.output) + req.inflight < req.max_new
             planned.append(Planned(req, req.computed, count, sample, fed))
             budget -= count
         # 3: admissions, in arrival order (a preempted request is at the front)

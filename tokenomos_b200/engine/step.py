@@ -11,6 +11,7 @@ with decoded tokens in one forward; here that is the normal case.
 
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -40,18 +41,19 @@ class _Tiles:
 
     @staticmethod
     def cut(seq_lens: list[int], size: int, which: str):
-        """Host lists (sequence, first token, offset in the portion, tokens) of the tiles."""
-        seq, tok0, off, n = [], [], [], []
-        start = 0
-        for s, length in enumerate(seq_lens):
-            if which == "all" or length > 1:
-                for o in range(0, length, size):
-                    seq.append(s)
-                    tok0.append(start + o)
-                    off.append(o)
-                    n.append(min(size, length - o))
-            start += length
-        return seq, tok0, off, n
+        """Host arrays (sequence, first token, offset in the portion, tokens) of the tiles, in
+        the order of the sequences; ``which`` other than "all" leaves single-token sequences out."""
+        lens = np.asarray(seq_lens, dtype=np.int64)
+        starts = np.cumsum(lens) - lens
+        counts = -(-lens // size)
+        if which != "all":
+            counts = np.where(lens > 1, counts, 0)
+        seq = np.repeat(np.arange(len(lens)), counts)
+        first = np.cumsum(counts) - counts                     # each sequence's first tile
+        off = (np.arange(len(seq)) - first[seq]) * size
+        tok0 = starts[seq] + off
+        n = np.minimum(size, lens[seq] - off)
+        return tuple(a.astype(np.int32) for a in (seq, tok0, off, n))
 
     def tiles(self, size: int, which: str = "all"):
         key = (size, which)
@@ -64,7 +66,7 @@ class _Tiles:
                 empty = torch.empty(0, dtype=torch.int32, device=self.device)
                 self.cache[key] = (empty, empty, empty, empty)
             else:
-                flat = self.upload(seq + tok0 + off + n)
+                flat = self.upload(np.concatenate((seq, tok0, off, n)))
                 self.cache[key] = (flat[:k], flat[k:2 * k], flat[2 * k:3 * k], flat[3 * k:])
         return self.cache[key]
 
@@ -332,9 +334,11 @@ class _StepGraph:
 
         put("positions", np.arange(total, dtype=np.int32) + np.repeat(ctx_np - cu[:-1], lens_np))
         put("tok_seq", np.repeat(np.arange(n, dtype=np.int32), lens_np), n)       # padding: the dummy sequence
-        put("ids_host", np.fromiter((0 if f else t for e, f in zip(entries, fed_on_device) for t in e.tokens),
-                                    dtype=np.int32, count=total))
-        put("use_prev", np.repeat(np.asarray(fed_on_device, dtype=np.int32), lens_np))
+        use_prev = np.repeat(np.asarray(fed_on_device, dtype=np.int32), lens_np)
+        ids = np.fromiter(itertools.chain.from_iterable(e.tokens for e in entries), dtype=np.int32, count=total)
+        ids[use_prev != 0] = 0               # a token fed on the device has no value on the host
+        put("ids_host", ids)
+        put("use_prev", use_prev)
         put("tok_slot", np.repeat(slot_np, lens_np))
         put("cu", cu, T)                         # the dummy sequence takes the rest; then empty ones
         put("seq_ctx", ctx_np)
