@@ -131,8 +131,15 @@ def test_random_orders_keep_the_books(seed):
         elif op < 0.85 and live:
             rid = rng.choice(list(live))
             n = rng.choice([1, 1, 1, 2, 5, 17])
-            if c.can_extend(rid, n):
+            can = c.can_extend(rid, n)
+            if rng.random() < 0.5:           # the scheduler's one call for both
+                free_before = c.free_pages()
+                assert c.try_extend(rid, n) == can
+                if not can:
+                    assert c.free_pages() == free_before      # all or nothing
+            elif can:
                 c.extend(rid, n)
+            if can:
                 if rng.random() < 0.9:       # sometimes a step is planned and re-planned
                     c.commit(rid, n)
                     live[rid] += n
