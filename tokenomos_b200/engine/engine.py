@@ -121,6 +121,34 @@ class Engine:
                                        "the tokens of the steps since the last check are not to be trusted")
         return finished
 
+    def _decode_step(self, planned, finished: list[Request]) -> list[Request]:
+        """Every request decodes one token: the captured decode graph, queued without waiting
+        for the step before it. One pass over the plan builds what the graph's layout needs."""
+        rids, tokens, rows, fed = [], [], [], []
+        for p in planned:
+            r = p.req
+            rids.append(r.rid)
+            fed.append(p.fed_on_device)
+            if p.fed_on_device:
+                tokens.append(0)
+            else:
+                at = p.start - len(r.prompt)
+                tokens.append(r.output[at] if at >= 0 else r.prompt[p.start])
+            rows.append((r.temperature, r.top_p, r.top_k, r.min_p, r.seed, len(r.output) + r.inflight))
+        n = len(planned)
+        self.stats.stamps.append((time.perf_counter(), n, n))
+        self.stats.steps += 1
+        self.stats.decode_steps += 1
+        handle = self.step_fn.launch_decode_ids(rids, tokens, rows, fed)
+        self.scheduler.launch(planned)
+        self._inflight.append((planned, handle))
+        self.stats.generated += n
+        while len(self._inflight) > self.depth:
+            old_planned, old_handle = self._inflight.popleft()
+            finished += self.scheduler.deliver(old_planned, old_handle.tokens())
+        self.stats.preemptions = self.scheduler.stats["preemptions"]
+        return self._finish(finished)
+
     @torch.no_grad()
     def step(self) -> list[Request]:
         """Plan and queue one step; returns the requests that finished meanwhile. A step in
@@ -151,6 +179,8 @@ class Engine:
             return entries, rows
 
         decode_only = all(p.count == 1 and p.sample for p in planned)
+        if self.graphs and decode_only:
+            return self._decode_step(planned, finished)
         entries, rows = entries_of(planned)
         # a captured step (decode-only, or a mixed one whose bucket has been captured) is queued
         # without waiting for the step before it; anything else runs eagerly and needs every

@@ -89,7 +89,7 @@ class Request:
         return len(self.output) + self.inflight >= self.max_new
 
 
-@dataclass
+@dataclass(slots=True)
 class Planned:
     """One request's share of the next step: tokens ``[start, start + count)`` of prompt +
     output; ``sample``: the share reaches the end of what is known, so its last position's
@@ -181,7 +181,8 @@ class Scheduler:
         # reading its prompt a portion of what is left of the budget. Victims are always the
         # newest, which this loop has not planned yet.
         preempted = False                     # membership tests only once somebody has left
-        for req in list(self.running):
+        try_extend = cache.try_extend
+        for req in tuple(self.running):
             if preempted and req not in self.running:       # preempted while serving an older one
                 continue
             if budget <= 0:
@@ -193,7 +194,7 @@ class Scheduler:
             fed = req.inflight > 0
             if fed and not (count == 1 and req.inflight == 1):
                 raise NeedsDrain("only a single decoded token can be fed on the device")
-            while not cache.try_extend(req.rid, count):
+            while not try_extend(req.rid, count):
                 if self.inflight():
                     raise NeedsDrain("a preemption needs every token value on the host")
                 victim = self.running[-1]
@@ -234,11 +235,13 @@ class Scheduler:
     def launch(self, planned: list[Planned]) -> None:
         """The step has been handed to the device: advance every planned request's length; the
         tokens it samples are in flight until ``deliver``."""
+        commit = self.cache.commit
         for p in planned:
-            self.cache.commit(p.req.rid, p.count)
-            p.req.computed += p.count
+            req, count = p.req, p.count
+            commit(req.rid, count)
+            req.computed += count
             if p.sample:
-                p.req.inflight += 1
+                req.inflight += 1
 
     def deliver(self, planned: list[Planned], sampled: list[int]) -> list[Request]:
         """The sampled tokens of a launched step (one per share with ``sample``, in order):

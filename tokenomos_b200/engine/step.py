@@ -130,7 +130,7 @@ class _DecodeGraph:
         self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.host_np = [h.numpy() for h in self.host]
         # what each staging buffer's block-table rows hold: (request, entries written) per row
-        self.host_rows = [{g: [(None, 0)] * b for g in self.groups} for _ in range(self.RING)]
+        self.host_rows = [{g: [(None, 0, 0)] * b for g in self.groups} for _ in range(self.RING)]
         self.tokens_host = [torch.zeros(b, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.turn = 0
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
@@ -552,24 +552,34 @@ class StepFunction:
         the host may not have read yet; the device takes it from ``last_token``. Rows of the
         bucket beyond the entries point at the null slot and the null page. ``reserved``: the
         caller (the scheduler's plan) already holds the pages and has checked the entries."""
-        from tokenomos_b200.sampling import sampler
-
-        cache = self.cache
-        n = len(entries)
         if not reserved:
             for e in entries:
                 if len(e.tokens) != 1:
                     raise ValueError("the decode graph takes one token per request")
-                cache.extend(e.rid, 1)
+                self.cache.extend(e.rid, 1)
+        return self.launch_decode_ids([e.rid for e in entries], [e.tokens[0] for e in entries],
+                                      sampling_rows, fed_on_device, commit)
+
+    @torch.no_grad()
+    def launch_decode_ids(self, rids: list, tokens: list[int], sampling_rows: list[tuple],
+                          fed_on_device: list[bool] | None = None, commit: bool = False) -> DecodeHandle:
+        """``launch_decode_graph`` for requests whose pages are held already, given as parallel
+        lists (request ids, the one token each feeds): what the engine's loop calls every decode
+        step, without building an entry per request."""
+        from tokenomos_b200.sampling import sampler
+
+        cache = self.cache
+        n = len(rids)
         g = self.decode_graph(n)
         turn = g.turn
         g.turn = (turn + 1) % g.RING
         h, rows_held, b, width = g.host_np[turn], g.host_rows[turn], g.rows, g.width
-        states = [cache.requests[e.rid] for e in entries]
+        requests = cache.requests
+        states = [requests[rid] for rid in rids]
         lengths = [st.length for st in states]
         for name, values in (("positions", lengths), ("seq_ctx", lengths),
                              ("seq_slot", [st.slot for st in states]),
-                             ("ids_host", [e.tokens[0] for e in entries]),
+                             ("ids_host", tokens),
                              ("use_prev", [int(f) for f in fed_on_device] if fed_on_device else [0] * n)):
             o, _ = g.off[name]
             h[o:o + n] = values
@@ -582,21 +592,24 @@ class StepFunction:
             o, _ = g.off[("table", grp)]
             held = rows_held[grp]
             incremental = cache.groups[grp].window is None
-            for i, (e, st) in enumerate(zip(entries, states)):
+            for i, (rid, st) in enumerate(zip(rids, states)):
                 row = st.tables[grp]
-                base = o + i * width
-                held_rid, held_len = held[i]
-                if incremental and held_rid == (e.rid, st.epoch) and held_len <= len(row):
-                    if held_len < len(row):
-                        h[base + held_len:base + len(row)] = row[held_len:]
+                have = len(row)
+                held_rid, held_epoch, held_len = held[i]
+                if incremental and held_len <= have and held_rid == rid and held_epoch == st.epoch:
+                    if held_len == have:
+                        continue                 # the common case: the same pages as last time
+                    base = o + i * width
+                    h[base + held_len:base + have] = row[held_len:]
                 else:
-                    h[base:base + len(row)] = row
-                    h[base + len(row):base + width] = 0
-                held[i] = ((e.rid, st.epoch), len(row))
+                    base = o + i * width
+                    h[base:base + have] = row
+                    h[base + have:base + width] = 0
+                held[i] = (rid, st.epoch, have)
             for i in range(n, b):
                 if held[i][0] is not None:
                     h[o + i * width:o + (i + 1) * width] = 0
-                    held[i] = (None, 0)
+                    held[i] = (None, 0, 0)
         g.dev.copy_(g.host[turn], non_blocking=True)
         g.graph.replay()
         g.tokens_host[turn].copy_(g.tokens, non_blocking=True)
@@ -606,8 +619,8 @@ class StepFunction:
         self.d2h_bytes += 4 * b
         self.steps += 1
         if commit:
-            for e in entries:
-                cache.commit(e.rid, 1)
+            for rid in rids:
+                cache.commit(rid, 1)
         return DecodeHandle(event, g.tokens_host[turn], n)
 
     # ---- any step through a CUDA graph ----
