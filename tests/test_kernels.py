@@ -392,6 +392,79 @@ def test_conv_gated_cut_anywhere_equals_whole(dtype):
         assert torch.equal(run(cuts), whole), cuts
 
 
+def test_conv_gated_blocked_columns_equal_plain_columns():
+    """Rows of bcx in runs of 8 channels of B, of C and of X in turn (what the in-projection with
+    interleaved rows produces) give what the plain [B | C | X] rows give, bit for bit, state too."""
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.shortconv import interleave_bcx
+    for dtype in DTYPES:
+        W, d, slots = 3, 40, 4
+        taps, bias = torch.randn(d, W), torch.randn(d)
+        seqs = [(2, 0, 19), (1, 7, 1), (3, 3, 33)]
+        T = sum(n for _, _, n in seqs)
+        bcx = torch.randn(T, 3 * d).to(dtype)
+        blocked = interleave_bcx(bcx.t().contiguous(), 8).t().contiguous()
+        cu = [0]
+        for _, _, n in seqs:
+            cu.append(cu[-1] + n)
+        tiles = [(s, o, min(8, n - o)) for s, (_, _, n) in enumerate(seqs) for o in range(0, n, 8)]
+        state0 = torch.randn(slots, W - 1, d).to(dtype)
+        outs, states = [], []
+        for rows, block in ((bcx, 0), (blocked, 8)):
+            state = dev(state0).clone()
+            outs.append(ops.conv_gated(dev(rows), dev(taps), dev(bias), state, i32(cu),
+                                       i32([c for _, c, _ in seqs]), i32([s for s, _, _ in seqs]),
+                                       i32([t[0] for t in tiles]), i32([t[1] for t in tiles]),
+                                       i32([t[2] for t in tiles]), block))
+            states.append(state)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
+
+
+@pytest.mark.parametrize("W, d, K, M, with_bias", [(3, 64, 128, 8, False), (2, 40, 72, 5, True),
+                                                  (4, 96, 520, 13, True), (8, 24, 64, 1, False),
+                                                  (3, 2048, 2048, 8, False)])
+def test_gemm_skinny_conv_equals_projection_then_conv(W, d, K, M, with_bias):
+    """The decode kernel that runs the gated short conv in the epilogue of its in-projection
+    (rows of the weight in blocks of 24) against the two kernels it replaces: the projection with
+    plain rows, then the conv with one token per sequence. Requests at positions 0, 1 and beyond
+    (the state row reads as zeros before position 0); state rows of other slots stay."""
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.shortconv import interleave_bcx
+    dtype = torch.bfloat16
+    slots = M + 3
+    w = (torch.randn(3 * d, K) * K ** -0.5).to(dtype)
+    b_in = torch.randn(3 * d) if with_bias else None
+    taps = torch.randn(d, W)
+    conv_bias = torch.randn(d) if with_bias else None
+    x = torch.randn(M, K).to(dtype)
+    ctx = [(0, 1, 2, 5, 40, 3, 0, 9, 1, 2, 100, 7, 6)[i % 13] for i in range(M)]
+    slot = torch.randperm(slots)[:M].tolist()
+    state0 = torch.randn(slots, W - 1, d).to(dtype)
+    # the unfused path
+    s1 = dev(state0).clone()
+    bcx = ops.gemm_skinny(dev(x), dev(w), dev(b_in) if with_bias else None)
+    want = ops.conv_gated(bcx, dev(taps), dev(conv_bias) if with_bias else None, s1, i32(list(range(M + 1))),
+                          i32(ctx), i32(slot), i32(list(range(M))), i32([0] * M), i32([1] * M))
+    # the fused kernel
+    s2 = dev(state0).clone()
+    got = ops.gemm_skinny_conv(dev(x), dev(interleave_bcx(w, 8)),
+                               dev(interleave_bcx(b_in, 8)) if with_bias else None, dev(taps),
+                               dev(conv_bias) if with_bias else None, s2, i32(ctx), i32(slot))
+    assert torch.equal(got, want), (got.float() - want.float()).abs().max().item()
+    assert torch.equal(s1, s2)
+    untouched = [i for i in range(slots) if i not in slot]
+    assert torch.equal(s2[untouched].cpu(), state0[untouched])
+    # and against 64-bit arithmetic
+    bcx64 = x.double() @ w.double().t() + (b_in.double() if with_bias else 0.0)
+    for i in range(M):
+        prev = state0[slot[i]].double().clone()
+        for k in range(W - 1):
+            if ctx[i] - (W - 1) + k < 0:
+                prev[k] = 0.0
+        ref, _ = conv_ref(bcx64[i:i + 1], taps.double(), conv_bias.double() if with_bias else None, prev)
+        close(got[i:i + 1], ref, dtype, f"fused conv token {i}", scale=max(ref.abs().max().item(), 1.0))
+
+
 # ---- sampling ----------------------------------------------------------------------------------
 
 def sample_rows(logits, rows):

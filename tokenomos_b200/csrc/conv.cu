@@ -21,11 +21,14 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
                                   const int* seq_slot,
                                   const int* tile_seq,
                                   const int* tile_off,
-                                  const int* tile_n) {
+                                  const int* tile_n, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= d) return;
+    // columns of this channel's B, C and X in a row of bcx
+    const int cb = block ? (c / block) * 3 * block + c % block : c;
+    const int cc = block ? cb + block : d + c, cx = block ? cb + 2 * block : 2 * d + c;
     const int s = tile_seq[blockIdx.x];
     const int off = tile_off[blockIdx.x];
     const int n = tile_n[blockIdx.x];
@@ -44,7 +47,7 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
     auto input = [&](int li) -> float {
         if (li >= 0) {
             const T* row = bcx + (size_t)(start + li) * stride;
-            return round_as<T>(to_f<T>(row[c]) * to_f<T>(row[2 * d + c]));
+            return round_as<T>(to_f<T>(row[cb]) * to_f<T>(row[cx]));
         }
         if (ctx + li < 0) return 0.f;
         return to_f<T>(st[(size_t)(W - 1 + li) * d]);
@@ -64,14 +67,14 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
 
     for (int i = 0; i < n; ++i) {
         const T* row = bcx + (size_t)(start + off + i) * stride;
-        const float u = round_as<T>(to_f<T>(row[c]) * to_f<T>(row[2 * d + c]));
+        const float u = round_as<T>(to_f<T>(row[cb]) * to_f<T>(row[cx]));
         float acc = 0.f;
 #pragma unroll
         for (int j = 0; j < W - 1; ++j) acc += hist[j] * taps[j];
         acc += u * taps[W - 1];
         acc += b;
         const float y = round_as<T>(acc);
-        out[(size_t)(start + off + i) * d + c] = from_f<T>(to_f<T>(row[d + c]) * y);
+        out[(size_t)(start + off + i) * d + c] = from_f<T>(to_f<T>(row[cc]) * y);
 #pragma unroll
         for (int j = 0; j + 1 < W - 1; ++j) hist[j] = hist[j + 1];
         hist[W - 2] = u;
@@ -90,12 +93,15 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
                                       const float* __restrict__ w, const float* __restrict__ bias,
                                       T* state, T* out, const int* cu, const int* seq_ctx,
                                       const int* seq_slot, const int* tile_seq, const int* tile_off,
-                                      const int* tile_n) {
+                                      const int* tile_n, int block) {
     constexpr int VEC = 16 / sizeof(T);
     pdl_launch_dependents();
     pdl_wait();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
     if (c >= d) return;
+    // columns of these channels' B, C and X in a row of bcx (a block is a multiple of VEC)
+    const int cb = block ? (c / block) * 3 * block + c % block : c;
+    const int cc = block ? cb + block : d + c, cx = block ? cb + 2 * block : 2 * d + c;
     const int s = tile_seq[blockIdx.x];
     const int off = tile_off[blockIdx.x];
     const int n = tile_n[blockIdx.x];
@@ -130,8 +136,8 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
         if (li >= 0) {
             const T* row = bcx + (size_t)(start + li) * stride;
             float bv[VEC], xv[VEC];
-            load(row + c, bv);
-            load(row + 2 * d + c, xv);
+            load(row + cb, bv);
+            load(row + cx, xv);
 #pragma unroll
             for (int i = 0; i < VEC; ++i) u[i] = round_as<T>(bv[i] * xv[i]);
         } else if (ctx + li < 0) {
@@ -160,9 +166,9 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
         for (int k = 0; k < 4; ++k) {
             if (i0 + k < n) {
                 const T* row = bcx + (size_t)(start + off + i0 + k) * stride;
-                rb[k] = *reinterpret_cast<const uint4*>(row + c);
-                rc[k] = *reinterpret_cast<const uint4*>(row + d + c);
-                rx[k] = *reinterpret_cast<const uint4*>(row + 2 * d + c);
+                rb[k] = *reinterpret_cast<const uint4*>(row + cb);
+                rc[k] = *reinterpret_cast<const uint4*>(row + cc);
+                rx[k] = *reinterpret_cast<const uint4*>(row + cx);
             }
         }
 #pragma unroll
@@ -199,9 +205,9 @@ template <typename T>
 static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, const float* bias,
                        void* state, void* out, const int* cu, const int* seq_ctx,
                        const int* seq_slot, const int* tile_seq, const int* tile_off,
-                       const int* tile_n, int n_tiles, int W, cudaStream_t stream) {
+                       const int* tile_n, int n_tiles, int W, int block, cudaStream_t stream) {
     constexpr int VEC = 16 / sizeof(T);
-    const bool vec_ok = d % VEC == 0 && stride % VEC == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+    const bool vec_ok = d % VEC == 0 && block % VEC == 0 && stride % VEC == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                         (uintptr_t)state % 16 == 0;
     const int threads = vec_ok ? 64 : 128;
     const int per_block = vec_ok ? threads * VEC : threads;
@@ -211,11 +217,11 @@ static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, c
         if (vec_ok)                                                                              \
             tk_launch(conv_gated_vec_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,        \
                 (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
-                tile_seq, tile_off, tile_n);                                                     \
+                tile_seq, tile_off, tile_n, block);                                              \
         else                                                                                     \
             tk_launch(conv_gated_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,            \
                 (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
-                tile_seq, tile_off, tile_n);                                                     \
+                tile_seq, tile_off, tile_n, block);                                              \
         break;
     switch (W) {
         TK_CONV_CASE(2)
@@ -239,19 +245,21 @@ TK_API int tk_conv_min_tile(int W) { return W - 1; }
 
 // bcx: [T, 3d] (B | C | X) with row stride `stride`; w: [d, W]; bias: [d] or null;
 // state: [slots, W-1, d]; out: [T, d]; cu: [S+1]; seq_ctx, seq_slot: [S];
-// tiles: sequence, offset in the sequence's portion, token count.
+// tiles: sequence, offset in the sequence's portion, token count. block 0: a row of bcx is all of
+// B, then C, then X; block b > 0 (d a multiple of b): runs of b channels of B, of C and of X in turn.
 TK_API int tk_conv_gated(const void* bcx, int64_t stride, int d, const float* w, const float* bias,
                          void* state, void* out, const int* cu, const int* seq_ctx,
                          const int* seq_slot, const int* tile_seq, const int* tile_off,
-                         const int* tile_n, int n_tiles, int W, int dtype, cudaStream_t stream) {
+                         const int* tile_n, int n_tiles, int W, int block, int dtype, cudaStream_t stream) {
     TK_CHECK_ARG(d > 0 && n_tiles >= 0 && stride >= 3 * (int64_t)d, "conv_gated: bad sizes");
+    TK_CHECK_ARG(block >= 0 && (block == 0 || d % block == 0), "conv_gated: %d channels in blocks of %d", d, block);
     if (n_tiles == 0) return 0;
     if (dtype == TK_F32)
         return launch_conv<float>(bcx, stride, d, w, bias, state, out, cu, seq_ctx, seq_slot,
-                                  tile_seq, tile_off, tile_n, n_tiles, W, stream);
+                                  tile_seq, tile_off, tile_n, n_tiles, W, block, stream);
     if (dtype == TK_BF16)
         return launch_conv<__nv_bfloat16>(bcx, stride, d, w, bias, state, out, cu, seq_ctx,
-                                          seq_slot, tile_seq, tile_off, tile_n, n_tiles, W, stream);
+                                          seq_slot, tile_seq, tile_off, tile_n, n_tiles, W, block, stream);
     TK_CHECK_ARG(false, "conv_gated: unknown dtype %d", dtype);
     return -1;
 }

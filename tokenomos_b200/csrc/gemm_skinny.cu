@@ -46,27 +46,47 @@ __device__ __forceinline__ uint4 ld_activation(const void* p) {
 constexpr int ROWS = 16;     // weight rows per CTA
 constexpr int KSLICE = 64;   // K elements a warp takes per iteration (128 bytes of each row)
 
+// What the short-conv epilogue needs beside the product (EPI_CONV): the depthwise taps, the
+// per-request state rows and where each token's request keeps them.
+struct ConvTail {
+    const float* taps;        // [d, W]
+    const float* bias;        // [d] or null
+    __nv_bfloat16* state;     // [slots, W - 1, d]
+    const int* seq_ctx;       // [M] tokens already cached (0: the state row reads as zeros)
+    const int* seq_slot;      // [M]
+    int W, d;
+};
+
+enum : int { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
+
 // MT: 8 or 16 tokens (one or two n8 tiles). R8: the CTA owns 8 weight rows instead of 16 (the
 // upper half of the mma tile stays zero): twice as many CTAs for matrices with few rows.
-// SWIGLU: the weight rows come in blocks of 16, 8 gate rows then the 8 up rows of the same
+// EPI_SWIGLU: the weight rows come in blocks of 16, 8 gate rows then the 8 up rows of the same
 // channels, and the CTA writes silu(gate) * up for its 8 channels: out is [M, N / 2].
+// EPI_CONV: the weight rows come in blocks of 24 (8 rows of B, of C and of X of the same 8
+// channels of a gated short conv), every token is a sequence of its own with one new token, and
+// the CTA writes C * conv(B * X) for its 8 channels and moves their state on: out is [M, N / 3].
+// A second mma per step takes the X rows (its upper half stays zero).
 // UNROLL: slices whose loads a warp has in flight together (registers: 8 per slice and row half)
-template <int MT, typename TO, bool R8, bool SWIGLU, int UNROLL>
+template <int MT, typename TO, bool R8, int EPI, int UNROLL>
 __global__ void __launch_bounds__(512)
 gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                    const __nv_bfloat16* __restrict__ w, int64_t ldw, const float* __restrict__ bias,
-                   TO* out, int64_t ldo, int M, int N, int K) {
-    extern __shared__ float red[];                 // [warps][ROWS][MT]
+                   TO* out, int64_t ldo, int M, int N, int K, ConvTail tail) {
+    extern __shared__ float red[];                 // [warps][RED_ROWS][MT]
     pdl_launch_dependents();
+    constexpr bool SWIGLU = EPI == EPI_SWIGLU, CONV = EPI == EPI_CONV;
+    constexpr int RED_ROWS = CONV ? 24 : ROWS;
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    constexpr int CTA_ROWS = R8 ? 8 : ROWS;
+    constexpr int CTA_ROWS = CONV ? 24 : (R8 ? 8 : ROWS);
     const int n0 = blockIdx.x * CTA_ROWS;
-    const int r0 = n0 + g, r1 = n0 + g + 8;
-    const bool r0_ok = r0 < N, r1_ok = !R8 && r1 < N;
+    const int r0 = n0 + g, r1 = n0 + g + 8, r2 = n0 + g + 16;
+    const bool r0_ok = r0 < N, r1_ok = !R8 && r1 < N, r2_ok = CONV && r2 < N;
     const __nv_bfloat16* w0 = w + (size_t)(r0_ok ? r0 : 0) * ldw;
     const __nv_bfloat16* w1 = w + (size_t)(r1_ok ? r1 : 0) * ldw;
+    const __nv_bfloat16* w2 = w + (size_t)(r2_ok ? r2 : 0) * ldw;
     constexpr int TG = MT / 8;
     const __nv_bfloat16* xr[TG];
     bool x_ok[TG];
@@ -76,17 +96,21 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
         x_ok[i] = tok < M;
         xr[i] = x + (size_t)(x_ok[i] ? tok : 0) * ldx;
     }
-    float acc[TG][4];
+    float acc[TG][4], accx[CONV ? TG : 1][4];
 #pragma unroll
     for (int i = 0; i < TG; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (CONV ? TG : 1); ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accx[i][e] = 0.f;
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int slices = (K + KSLICE - 1) / KSLICE;
     bool waited = false;
     for (int s0 = warp; s0 < slices; s0 += warps * UNROLL) {
-        uint4 wa[UNROLL][2], wb[UNROLL][2];
+        uint4 wa[UNROLL][2], wb[UNROLL][2], wc[CONV ? UNROLL : 1][2];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int s = s0 + u * warps;
@@ -96,6 +120,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                 const bool ok = s < slices && k < K;
                 wa[u][h] = (ok && r0_ok) ? ldg_stream(w0 + k) : zero;
                 wb[u][h] = (ok && r1_ok) ? ldg_stream(w1 + k) : zero;
+                if constexpr (CONV) wc[u][h] = (ok && r2_ok) ? ldg_stream(w2 + k) : zero;
             }
         }
         // the weights do not depend on the kernel before this one: their loads are in flight
@@ -117,6 +142,10 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                     // elements 0..3 of the 16 bytes are one mma step, 4..7 the next
                     mma16816(acc[i], wa[u][h].x, wb[u][h].x, wa[u][h].y, wb[u][h].y, xv.x, xv.y);
                     mma16816(acc[i], wa[u][h].z, wb[u][h].z, wa[u][h].w, wb[u][h].w, xv.z, xv.w);
+                    if constexpr (CONV) {
+                        mma16816(accx[i], wc[u][h].x, 0u, wc[u][h].y, 0u, xv.x, xv.y);
+                        mma16816(accx[i], wc[u][h].z, 0u, wc[u][h].w, 0u, xv.z, xv.w);
+                    }
                 }
             }
         }
@@ -125,14 +154,59 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
     // acc[i]: rows g / g + 8, tokens 8 i + 2 t, + 1
 #pragma unroll
     for (int i = 0; i < TG; ++i) {
-        float* dst = red + (size_t)warp * ROWS * MT;
+        float* dst = red + (size_t)warp * RED_ROWS * MT;
         dst[g * MT + 8 * i + 2 * t] = acc[i][0];
         dst[g * MT + 8 * i + 2 * t + 1] = acc[i][1];
         dst[(g + 8) * MT + 8 * i + 2 * t] = acc[i][2];
         dst[(g + 8) * MT + 8 * i + 2 * t + 1] = acc[i][3];
+        if constexpr (CONV) {
+            dst[(g + 16) * MT + 8 * i + 2 * t] = accx[i][0];
+            dst[(g + 16) * MT + 8 * i + 2 * t + 1] = accx[i][1];
+        }
     }
     __syncthreads();
-    if constexpr (SWIGLU) {
+    if constexpr (CONV) {
+        // one thread per (token, channel): B, C, X of the channel as the unfused path stores them,
+        // u = B X, the taps over the state row and u, the state moved on by one
+        const int W = tail.W, d = tail.d;
+        for (int idx = threadIdx.x; idx < 8 * MT; idx += blockDim.x) {
+            const int tok = idx / 8, j = idx % 8;
+            const int c = blockIdx.x * 8 + j;
+            if (tok >= M || c >= d) continue;
+            float bv = 0.f, cv = 0.f, xv = 0.f;
+            for (int wv = 0; wv < warps; ++wv) {
+                const float* src = red + (size_t)wv * RED_ROWS * MT + tok;
+                bv += src[j * MT];
+                cv += src[(j + 8) * MT];
+                xv += src[(j + 16) * MT];
+            }
+            if (bias != nullptr) {
+                bv += bias[n0 + j];
+                cv += bias[n0 + 8 + j];
+                xv += bias[n0 + 16 + j];
+            }
+            bv = round_as<TO>(bv);
+            cv = round_as<TO>(cv);
+            xv = round_as<TO>(xv);
+            const float u = round_as<TO>(bv * xv);
+            const int ctx = tail.seq_ctx[tok];
+            __nv_bfloat16* st = tail.state + (size_t)tail.seq_slot[tok] * (W - 1) * d + c;
+            const float* taps = tail.taps + (size_t)c * W;
+            // state row k holds u of position ctx - (W - 1) + k; before position 0 it reads as 0
+            float acc_c = 0.f;
+            for (int k = 0; k < W - 1; ++k) {
+                const float hv = ctx - (W - 1) + k < 0 ? 0.f : __bfloat162float(st[(size_t)k * d]);
+                acc_c += hv * taps[k];
+                // row k - 1 takes what row k held (it was read in the pass before this one)
+                if (k > 0) st[(size_t)(k - 1) * d] = __float2bfloat16_rn(hv);
+            }
+            st[(size_t)(W - 2) * d] = __float2bfloat16_rn(u);
+            acc_c += u * taps[W - 1];
+            if (tail.bias != nullptr) acc_c += tail.bias[c];
+            const float y = round_as<TO>(acc_c);
+            out[(size_t)tok * ldo + c] = from_f<TO>(cv * y);
+        }
+    } else if constexpr (SWIGLU) {
         for (int idx = threadIdx.x; idx < 8 * MT; idx += blockDim.x) {
             const int tok = idx / 8, j = idx % 8;
             if (tok >= M || n0 + 8 + j >= N) continue;
@@ -216,16 +290,16 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
     do {                                                                                           \
         if (unroll == 2)                                                                           \
             tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 2>, dim3(blocks), dim3(threads), smem, stream, \
-                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K);                            \
+                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{});                \
         else                                                                                       \
             tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 4>, dim3(blocks), dim3(threads), smem, stream, \
-                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K);                            \
+                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{});                \
     } while (0)
 #define TK_SKINNY_T(TO_)                                                                           \
     do {                                                                                           \
-        if (swiglu) { if (MT == 8) TK_SKINNY(8, TO_, false, true); else TK_SKINNY(16, TO_, false, true); } \
-        else if (r8) { if (MT == 8) TK_SKINNY(8, TO_, true, false); else TK_SKINNY(16, TO_, true, false); } \
-        else { if (MT == 8) TK_SKINNY(8, TO_, false, false); else TK_SKINNY(16, TO_, false, false); }  \
+        if (swiglu) { if (MT == 8) TK_SKINNY(8, TO_, false, EPI_SWIGLU); else TK_SKINNY(16, TO_, false, EPI_SWIGLU); } \
+        else if (r8) { if (MT == 8) TK_SKINNY(8, TO_, true, EPI_NONE); else TK_SKINNY(16, TO_, true, EPI_NONE); } \
+        else { if (MT == 8) TK_SKINNY(8, TO_, false, EPI_NONE); else TK_SKINNY(16, TO_, false, EPI_NONE); }  \
     } while (0)
     if (out_dtype == TK_BF16) TK_SKINNY_T(__nv_bfloat16);
     else if (out_dtype == TK_F32) TK_SKINNY_T(float);
@@ -233,5 +307,47 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
 #undef TK_SKINNY_T
 #undef TK_SKINNY
     TK_CHECK_LAUNCH("gemm_skinny");
+    return 0;
+}
+
+// The in-projection of a gated short conv with the conv in its epilogue, for a step in which every
+// token is a sequence of its own with one new token (decoding). x: [M, K] bfloat16, M <= 16;
+// w: [3 d, K] bfloat16 whose rows come in blocks of 24: 8 rows of B, of C and of X of the same 8
+// channels (d a multiple of 8); bias: [3 d] in the same order, or null. taps: [d, W] float32,
+// conv_bias: [d] or null; state: [slots, W - 1, d] bfloat16, moved on by one token per request;
+// seq_ctx, seq_slot: [M]. out: [M, d] bfloat16 = C * conv(B * X).
+TK_API int tk_gemm_skinny_conv(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                               void* out, int64_t ldo, int M, int d, int K, const float* taps,
+                               const float* conv_bias, void* state, const int* seq_ctx,
+                               const int* seq_slot, int W, cudaStream_t stream) {
+    TK_CHECK_ARG(M >= 0 && M <= 16 && d > 0 && K > 0, "gemm_skinny_conv: M=%d (at most 16) d=%d K=%d", M, d, K);
+    TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_skinny_conv: K and the leading "
+                 "dimensions must be multiples of 8 (K=%d)", K);
+    TK_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_skinny_conv: operands must be 16-byte aligned");
+    TK_CHECK_ARG(d % 8 == 0, "gemm_skinny_conv: the channel count (%d) must come in blocks of 8", d);
+    TK_CHECK_ARG(W >= 2 && W <= 8, "gemm_skinny_conv: width %d outside 2..8", W);
+    if (M == 0) return 0;
+    const int N = 3 * d;
+    const int slices = (K + KSLICE - 1) / KSLICE;
+    const int blocks = d / 8;
+    const int unroll = 2;
+    // (90 registers: two CTAs of 8 warps per SM. Bounding it to 80 for three made the decode step
+    // slower, 0.842 ms against 0.816 ms.)
+    const int max_warps = g_max_warps ? g_max_warps : (blocks >= 200 ? 8 : 16);
+    int warps = (slices + unroll - 1) / unroll;
+    warps = warps < 1 ? 1 : (warps > max_warps ? max_warps : warps);
+    const int MT = M <= 8 ? 8 : 16;
+    const size_t smem = (size_t)warps * 24 * MT * sizeof(float);
+    const ConvTail tail{taps, conv_bias, (__nv_bfloat16*)state, seq_ctx, seq_slot, W, d};
+    auto x_ = (const __nv_bfloat16*)x;
+    auto w_ = (const __nv_bfloat16*)w;
+    auto o_ = (__nv_bfloat16*)out;
+#define TK_SKINNY_CONV(MT_, U_)                                                                    \
+    tk_launch(gemm_skinny_kernel<MT_, __nv_bfloat16, false, EPI_CONV, U_>, dim3(blocks), dim3(warps * 32), \
+              smem, stream, x_, ldx, w_, ldw, bias, o_, ldo, M, N, K, tail)
+    if (MT == 8) TK_SKINNY_CONV(8, 2);
+    else TK_SKINNY_CONV(16, 2);
+#undef TK_SKINNY_CONV
+    TK_CHECK_LAUNCH("gemm_skinny_conv");
     return 0;
 }

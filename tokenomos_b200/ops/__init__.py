@@ -20,7 +20,7 @@ __all__ = [
     "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
     "attention_prefill_tc_status",
     "conv_gated", "conv_min_tile",
-    "gemm", "gemm_skinny", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "gather_rows_select",
+    "gemm", "gemm_skinny", "gemm_skinny_conv", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "gather_rows_select",
 ]
 
 
@@ -300,9 +300,10 @@ def conv_min_tile(width: int) -> int:
 def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
                state: torch.Tensor, cu: torch.Tensor, seq_ctx: torch.Tensor,
                seq_slot: torch.Tensor, tile_seq: torch.Tensor, tile_off: torch.Tensor,
-               tile_n: torch.Tensor) -> torch.Tensor:
+               tile_n: torch.Tensor, block: int = 0) -> torch.Tensor:
     """Gated short conv of ``bcx`` [T, 3d] = (B | C | X): returns ``C * conv(B * X)`` [T, d] and
-    replaces each sequence's row of ``state`` [slots, W-1, d]. ``weight`` [d, W] float32."""
+    replaces each sequence's row of ``state`` [slots, W-1, d]. ``weight`` [d, W] float32.
+    ``block`` b > 0: a row of ``bcx`` holds runs of b channels of B, of C and of X in turn."""
     _cuda(bcx, weight, bias, state, cu, seq_ctx, seq_slot, tile_seq, tile_off, tile_n)
     T, three_d = bcx.shape
     d = three_d // 3
@@ -318,7 +319,34 @@ def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
               _ptr(state), _ptr(out), _ptr(_i32(cu, "cu")), _ptr(_i32(seq_ctx, "seq_ctx")),
               _ptr(_i32(seq_slot, "seq_slot")), _ptr(_i32(tile_seq, "tile_seq")),
               _ptr(_i32(tile_off, "tile_off")), _ptr(_i32(tile_n, "tile_n")), tile_seq.numel(), W,
-              _dtype_code(bcx), _stream())
+              int(block), _dtype_code(bcx), _stream())
+    return out
+
+
+def gemm_skinny_conv(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, taps: torch.Tensor,
+                     conv_bias: torch.Tensor | None, state: torch.Tensor, seq_ctx: torch.Tensor,
+                     seq_slot: torch.Tensor) -> torch.Tensor:
+    """A gated short conv's in-projection with the conv in its epilogue, for a step whose tokens
+    are one new token of a sequence each (decoding): ``x`` [M <= 16, K] bfloat16, ``w`` [3d, K]
+    with rows in blocks of 24 (8 rows of B, of C and of X of the same 8 channels), ``bias`` in the
+    same order; returns ``C * conv(B * X)`` [M, d] and moves each request's row of ``state``
+    [slots, W-1, d] on by its token. ``seq_ctx``, ``seq_slot``: [M]."""
+    _cuda(x, w, bias, taps, conv_bias, state, seq_ctx, seq_slot)
+    M, K = x.shape
+    d, W = taps.shape
+    if tuple(w.shape) != (3 * d, K) or not gemm_skinny_ok(x, w):
+        raise KernelError(f"gemm_skinny_conv: x {tuple(x.shape)} against w {tuple(w.shape)} for {d} channels")
+    if taps.dtype != torch.float32 or not taps.is_contiguous():
+        raise KernelError("gemm_skinny_conv: taps must be contiguous float32 [d, W]")
+    if state.dtype != torch.bfloat16 or not state.is_contiguous() or tuple(state.shape[1:]) != (W - 1, d):
+        raise KernelError(f"gemm_skinny_conv: state {tuple(state.shape)} for width {W}, {d} channels")
+    if seq_ctx.numel() < M or seq_slot.numel() < M:
+        raise KernelError("gemm_skinny_conv: one sequence per token")
+    out = torch.empty(M, d, dtype=x.dtype, device=x.device)
+    _lib.call("tk_gemm_skinny_conv", _ptr(x), x.stride(0), _ptr(w), w.stride(0),
+              _ptr(_f32vec(bias, "bias", 3 * d)), _ptr(out), d, M, d, K, _ptr(taps),
+              _ptr(_f32vec(conv_bias, "conv bias", d)), _ptr(state), _ptr(_i32(seq_ctx, "seq_ctx")),
+              _ptr(_i32(seq_slot, "seq_slot")), W, _stream())
     return out
 
 

@@ -17,11 +17,19 @@ from tokenomos_b200.parts.registry import Runtime, register
 CONV_TILE = 8
 
 
+# channels per run when the in-projection's rows hold B, C and X of the same channels in turn
+# (what the decode kernel's epilogue needs side by side)
+RUN = 8
+
+
 class ShortConv:
     def __init__(self, in_proj: Linear, out_proj: Linear, conv: torch.Tensor,
-                 conv_bias: torch.Tensor | None = None):
-        """``conv`` [dim, width]: tap ``width - 1`` multiplies the current token."""
-        self.in_proj, self.out_proj = in_proj, out_proj
+                 conv_bias: torch.Tensor | None = None, run: int = 0):
+        """``conv`` [dim, width]: tap ``width - 1`` multiplies the current token. ``run`` 0:
+        ``in_proj``'s rows are all of B, then C, then X; ``run`` 8: runs of 8 channels of B, of C
+        and of X in turn, so that a decode CTA that owns 24 rows holds all three of the same 8
+        channels and can run the conv in its epilogue."""
+        self.in_proj, self.out_proj, self.run = in_proj, out_proj, run
         self.conv = conv.float().contiguous()
         self.conv_bias = conv_bias.float().contiguous() if conv_bias is not None else None
         self.dim, self.width = conv.shape
@@ -33,11 +41,25 @@ class ShortConv:
         return {"conv": SlotState((self.width - 1, self.dim))}
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
+        state = ctx.states[(call, "conv")]
+        if (self.run == RUN and ctx.n_tokens == ctx.n_seqs and 2 <= self.width <= 8
+                and ops.gemm_skinny_ok(x, self.in_proj.weight)):
+            # every sequence brings one token: projection and conv in one kernel
+            y = ops.gemm_skinny_conv(x, self.in_proj.weight, self.in_proj.bias, self.conv, self.conv_bias,
+                                     state, ctx.seq_ctx, ctx.seq_slot)
+            return self.out_proj(y)
         bcx = self.in_proj(x)
         seq, _, off, n = ctx.tiles(self.tile)
-        y = ops.conv_gated(bcx, self.conv, self.conv_bias, ctx.states[(call, "conv")],
-                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n)
+        y = ops.conv_gated(bcx, self.conv, self.conv_bias, state,
+                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run)
         return self.out_proj(y)
+
+
+def interleave_bcx(w: torch.Tensor, run: int) -> torch.Tensor:
+    """Rows (or entries) [B | C | X] of 3 d -> runs of ``run`` channels of B, of C and of X in turn."""
+    d = w.shape[0] // 3
+    parts = w.view(3, d // run, run, *w.shape[1:])
+    return parts.transpose(0, 1).reshape(w.shape).contiguous()
 
 
 @register("mixer", "short_conv")
@@ -47,7 +69,13 @@ def build_short_conv(params: dict, tensors: dict, rt: Runtime) -> ShortConv:
     if conv.shape[1] != params["width"]:
         raise ValueError(f"short conv: the weight has {conv.shape[1]} taps, the configuration "
                          f"says {params['width']}")
+    w_in, b_in = tensors["in_proj"], tensors.get("in_proj_bias")
+    run = 0
+    if w_in.dtype == torch.bfloat16 and conv.shape[0] % RUN == 0:
+        run = RUN
+        w_in = interleave_bcx(w_in, RUN)
+        b_in = interleave_bcx(b_in, RUN) if b_in is not None else None
     return ShortConv(
-        Linear(tensors["in_proj"], tensors.get("in_proj_bias")),
+        Linear(w_in, b_in),
         Linear(tensors["out_proj"], tensors.get("out_proj_bias")),
-        conv, tensors.get("conv_bias"))
+        conv, tensors.get("conv_bias"), run)
