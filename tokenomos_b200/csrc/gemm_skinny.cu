@@ -242,8 +242,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
 // Tuning knobs (tk_gemm_skinny_tune; 0 = choose by shape): slices in flight per warp (2 or 4), the
 // most warps a CTA may have, and the number of 16-row CTAs below which a matrix is cut into
 // 8-row CTAs instead. Measured on a B200 in CUDA graphs at 1 and 8 tokens (2048- and 8192-wide K):
-// two slices in flight beat four (54 instead of 104 registers: four CTAs per SM, whose load,
-// compute and reduce phases overlap); a tall matrix (300 or more CTAs) wants 8 warps per CTA, a
+// two slices in flight beat four (75 instead of 126 registers: three CTAs of 8 warps per SM
+// instead of two, whose load, compute and reduce phases overlap); a tall matrix (300 or more CTAs) wants 8 warps per CTA, a
 // short one 16 (more of K in flight per CTA); 8-row CTAs only pay below half a wave.
 static int g_unroll = 0, g_max_warps = 0, g_r8_below = -1;
 
