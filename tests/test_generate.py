@@ -80,6 +80,27 @@ def test_mixed_steps_through_captured_graphs(name, work, margin, model_folders):
             assert a.token_ids == b.token_ids
 
 
+def test_mixed_step_whose_bucket_has_as_many_tokens_as_sequences(model_folders):
+    """Forty requests, most of them decoding beside one prompt portion: such a step falls into the
+    captured bucket of 64 tokens and 64 sequences, whose layout has as many tokens as sequences
+    without being one token per sequence. The parts must not take it for a decode step."""
+    from tokenomos_b200 import LLM, SamplingParams
+    name = "D"                   # head size 64: the tensor-core attention kernels, the fused conv
+    folder = model_folders[name][torch.bfloat16]
+    config, w = plain_lfm3.read_folder(folder)
+    prompts = prompts_for(name, [3 + (i * 7) % 11 for i in range(39)] + [50], seed=9)
+    kw = dict(work="bf16", page=TINY[name]["page"], max_len=96, slots=40, pages=200, prefill_budget=58)
+    p = SamplingParams(max_tokens=12)
+    with LLM(str(folder), graphs=True, **kw) as llm:
+        llm.engine.step_fn.capture_after = 0
+        outs = llm.generate(prompts, p)
+        shapes = set(llm.engine.step_fn._step_graphs)
+        llm.engine.cache.check()
+    assert (64, 64) in shapes, shapes
+    for prompt, o in zip(prompts, outs):
+        teacher_forced_ok(config, w, prompt, o.token_ids, 0.25)
+
+
 def test_seeded_sampling_repeats_alone_and_in_batches(model_folders):
     from tokenomos_b200 import LLM, SamplingParams
     folder = model_folders["B"][torch.bfloat16]

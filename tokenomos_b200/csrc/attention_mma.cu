@@ -297,7 +297,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const int G = H / Hkv;
     const int i = blockIdx.x;                        // which decode token
     const int kvh = blockIdx.y, split = blockIdx.z;
-    const int tok = tok_index[i];
+    const int tok = tok_index != nullptr ? tok_index[i] : i;     // null: token i is sequence i's one token
     if (tok < 0) return;         // an unused entry of a fixed-length list (captured steps)
     const int seq = tok_seq[tok];
     const int pos = positions[tok];
@@ -444,7 +444,8 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
-    if (tok_index[i] < 0) return;        // an unused entry of a fixed-length list (captured steps)
+    const int tok = tok_index != nullptr ? tok_index[i] : i;
+    if (tok < 0) return;                 // an unused entry of a fixed-length list (captured steps)
     const size_t base = ((size_t)i * H + head) * nsplit;
     const float scale_log2 = scale * LOG2E;
     float M = -INFINITY;
@@ -456,7 +457,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
         L += part_ml[(base + s) * 2 + 1] * f;
         acc += part_o[(base + s) * D + c] * f;
     }
-    out[((size_t)tok_index[i] * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
 // log2 of a power-of-two page size, else -1 (the kernels then divide per 16-byte request)

@@ -109,6 +109,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int slices = (K + KSLICE - 1) / KSLICE;
     bool waited = false;
+    float pf_state[3] = {0.f, 0.f, 0.f};
+    int pf_ctx = 0;
+    bool pf = false;
     for (int s0 = warp; s0 < slices; s0 += warps * UNROLL) {
         uint4 wa[UNROLL][2], wb[UNROLL][2], wc[CONV ? UNROLL : 1][2];
 #pragma unroll
@@ -128,6 +131,20 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
         if (!waited) {
             pdl_wait();
             waited = true;
+            if constexpr (CONV) {
+                // what this thread's (token, channel) needs of the conv state in the epilogue is
+                // asked for now (widths up to 4): two trips to memory, one behind the other, that
+                // would otherwise follow the reduction at the kernel's tail
+                const int tok = threadIdx.x / 8, c = blockIdx.x * 8 + threadIdx.x % 8;
+                if (threadIdx.x < 8 * MT && tok < M && c < tail.d && tail.W <= 4) {
+                    pf_ctx = tail.seq_ctx[tok];
+                    const __nv_bfloat16* st = tail.state + (size_t)tail.seq_slot[tok] * (tail.W - 1) * tail.d + c;
+#pragma unroll
+                    for (int k = 0; k < 3; ++k)
+                        if (k < tail.W - 1) pf_state[k] = __bfloat162float(st[(size_t)k * tail.d]);
+                    pf = true;
+                }
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -189,16 +206,28 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
             cv = round_as<TO>(cv);
             xv = round_as<TO>(xv);
             const float u = round_as<TO>(bv * xv);
-            const int ctx = tail.seq_ctx[tok];
+            const bool have = pf && idx == (int)threadIdx.x;          // fetched at the start
+            const int ctx = have ? pf_ctx : tail.seq_ctx[tok];
             __nv_bfloat16* st = tail.state + (size_t)tail.seq_slot[tok] * (W - 1) * d + c;
             const float* taps = tail.taps + (size_t)c * W;
             // state row k holds u of position ctx - (W - 1) + k; before position 0 it reads as 0
             float acc_c = 0.f;
-            for (int k = 0; k < W - 1; ++k) {
-                const float hv = ctx - (W - 1) + k < 0 ? 0.f : __bfloat162float(st[(size_t)k * d]);
-                acc_c += hv * taps[k];
-                // row k - 1 takes what row k held (it was read in the pass before this one)
-                if (k > 0) st[(size_t)(k - 1) * d] = __float2bfloat16_rn(hv);
+            if (have) {
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    if (k < W - 1) {
+                        const float hv = ctx - (W - 1) + k < 0 ? 0.f : pf_state[k];
+                        acc_c += hv * taps[k];
+                        if (k > 0) st[(size_t)(k - 1) * d] = __float2bfloat16_rn(hv);
+                    }
+                }
+            } else {
+                for (int k = 0; k < W - 1; ++k) {
+                    const float hv = ctx - (W - 1) + k < 0 ? 0.f : __bfloat162float(st[(size_t)k * d]);
+                    acc_c += hv * taps[k];
+                    // row k - 1 takes what row k held (it was read in the pass before this one)
+                    if (k > 0) st[(size_t)(k - 1) * d] = __float2bfloat16_rn(hv);
+                }
             }
             st[(size_t)(W - 2) * d] = __float2bfloat16_rn(u);
             acc_c += u * taps[W - 1];

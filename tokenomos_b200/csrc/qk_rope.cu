@@ -104,7 +104,17 @@ __global__ void qk_norm_rope_write_vec_kernel(
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int heads = H + 2 * Hkv;
+    const int hpw = 32 / lph;                      // heads a warp takes per pass
+    const int sub = lane / lph, c = (lane % lph) * VEC;
+    const T* row = qkv + (size_t)t * qkv_stride;
+    // this thread's share of the first pass is asked for before anything else: its trip to
+    // memory runs beside those for the position, the sequence and the page
+    const int h_first = (blockIdx.y * nwarp + warp) * hpw;
+    uint4 raw_first = make_uint4(0u, 0u, 0u, 0u);
+    if (h_first + sub < heads) raw_first = *reinterpret_cast<const uint4*>(row + (size_t)(h_first + sub) * D + c);
     const int pos = positions[t];
+    const int seq_of_t = Hkv > 0 ? tok_seq[t] : 0;
     const int half = R >> 1;
     float* cs = smem;
     float* sn = smem + half;
@@ -117,22 +127,20 @@ __global__ void qk_norm_rope_write_vec_kernel(
     __syncthreads();
     size_t cache_row = 0;
     if (Hkv > 0) {
-        const int s = tok_seq[t];
-        const int page = block_table[(size_t)s * bt_stride + pos / P];
+        const int page = block_table[(size_t)seq_of_t * bt_stride + pos / P];
         cache_row = (size_t)page * 2 * Hkv * P + (pos % P);
     }
-    const T* row = qkv + (size_t)t * qkv_stride;
-    const int heads = H + 2 * Hkv;
-    const int hpw = 32 / lph;                      // heads a warp takes per pass
-    const int sub = lane / lph, c = (lane % lph) * VEC;
     const int half_lanes = half / VEC;
     // the lane that holds this chunk's partner in the rotation (itself beyond the rotary width)
     const int partner = c < half ? lane + half_lanes : (c < R ? lane - half_lanes : lane);
-    for (int h0 = (blockIdx.y * nwarp + warp) * hpw; h0 < heads; h0 += gridDim.y * nwarp * hpw) {
+    for (int h0 = h_first; h0 < heads; h0 += gridDim.y * nwarp * hpw) {
         const int hh = h0 + sub;
         const bool live = hh < heads;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (live) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * D + c);
+        uint4 raw = raw_first;
+        if (h0 != h_first) {
+            raw = make_uint4(0u, 0u, 0u, 0u);
+            if (live) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * D + c);
+        }
         const T* e = reinterpret_cast<const T*>(&raw);
         T* dst = nullptr;
         const float* w = nullptr;

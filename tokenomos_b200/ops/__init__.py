@@ -276,22 +276,23 @@ def attention_prefill_tc_status() -> int:
 
 def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                          positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
-                         tok_index: torch.Tensor, window: int | None, scale: float,
+                         tok_index: torch.Tensor | None, window: int | None, scale: float,
                          nsplit: int) -> None:
     """Tensor-core attention for sequences that bring one token (``tok_index``: their rows in
-    the packed batch), each split ``nsplit`` ways over its keys; up to 8 splits meet inside a
+    the packed batch; None: every row of ``q`` is one, in order, which spares the kernel a
+    lookup), each split ``nsplit`` ways over its keys; up to 8 splits meet inside a
     thread-block cluster, more go through scratch memory that this function allocates and a
     second kernel. Writes those rows of ``out`` [T, H, D]."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tok_index)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_decode_mma")
-    n = tok_index.numel()
+    n = tok_index.numel() if tok_index is not None else T
     scratch = None
     if nsplit > 1 and not _lib.call("tk_attn_decode_in_cluster", int(nsplit)):
         scratch = torch.empty(n * H * nsplit * (D + 2), dtype=torch.float32, device=q.device)
     _lib.call("tk_attn_decode_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
-              block_table.stride(0), _ptr(_i32(tok_index, "tok_index")), n, H, Hkv, D, P,
-              int(window or 0), float(scale), int(nsplit), _ptr(scratch), _stream())
+              block_table.stride(0), _ptr(_i32(tok_index, "tok_index") if tok_index is not None else None),
+              n, H, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), _stream())
 
 
 def conv_min_tile(width: int) -> int:

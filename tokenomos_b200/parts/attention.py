@@ -105,12 +105,15 @@ class Attention:
         if tok0.numel():
             (ops.attention_prefill_tc if tc else ops.attention_prefill_mma)(
                 q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window, self.scale)
-        singles = ctx.singles()
-        if singles.numel():
+        # every sequence brings one token: row i is sequence i's, no list of rows needed
+        decode_only = ctx.host.decode_only
+        singles = None if decode_only else ctx.singles()
+        if decode_only or singles.numel():
             longest = ctx.host.longest
             if self.window is not None:
                 longest = min(longest, self.window)
-            want = -(-self.DECODE_CTAS // (singles.numel() * self.kv_heads))
+            rows = ctx.n_tokens if decode_only else singles.numel()
+            want = -(-self.DECODE_CTAS // (rows * self.kv_heads))
             nsplit = max(1, min(want, -(-longest // self.DECODE_MIN_KEYS)))
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
                                      self.window, self.scale, nsplit)

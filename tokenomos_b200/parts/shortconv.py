@@ -42,7 +42,7 @@ class ShortConv:
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         state = ctx.states[(call, "conv")]
-        if (self.run == RUN and ctx.n_tokens == ctx.n_seqs and 2 <= self.width <= 8
+        if (self.run == RUN and ctx.host.decode_only and 2 <= self.width <= 8
                 and ops.gemm_skinny_ok(x, self.in_proj.weight)):
             # every sequence brings one token: projection and conv in one kernel
             y = ops.gemm_skinny_conv(x, self.in_proj.weight, self.in_proj.bias, self.conv, self.conv_bias,
