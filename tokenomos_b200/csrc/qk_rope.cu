@@ -115,6 +115,8 @@ __global__ void qk_norm_rope_write_vec_kernel(
     if (h_first + sub < heads) raw_first = *reinterpret_cast<const uint4*>(row + (size_t)(h_first + sub) * D + c);
     const int pos = positions[t];
     const int seq_of_t = Hkv > 0 ? tok_seq[t] : 0;
+    // (the page is looked up before the angles are computed, not after: its trip runs beside them)
+    const int page = Hkv > 0 ? block_table[(size_t)seq_of_t * bt_stride + pos / P] : 0;
     const int half = R >> 1;
     float* cs = smem;
     float* sn = smem + half;
@@ -125,11 +127,7 @@ __global__ void qk_norm_rope_write_vec_kernel(
         sn[i] = round_as<T>(s_);
     }
     __syncthreads();
-    size_t cache_row = 0;
-    if (Hkv > 0) {
-        const int page = block_table[(size_t)seq_of_t * bt_stride + pos / P];
-        cache_row = (size_t)page * 2 * Hkv * P + (pos % P);
-    }
+    const size_t cache_row = Hkv > 0 ? (size_t)page * 2 * Hkv * P + (pos % P) : 0;
     const int half_lanes = half / VEC;
     // the lane that holds this chunk's partner in the rotation (itself beyond the rotary width)
     const int partner = c < half ? lane + half_lanes : (c < R ? lane - half_lanes : lane);
