@@ -11,6 +11,8 @@ with decoded tokens in one forward; here that is the normal case.
 
 from __future__ import annotations
 
+import contextlib
+import gc
 import itertools
 from dataclasses import dataclass, field
 
@@ -29,6 +31,22 @@ class StepEntry:
     rid: object
     tokens: list[int]
     want: list[int] = field(default_factory=list)
+
+
+@contextlib.contextmanager
+def _no_collection():
+    """No garbage collection while a CUDA graph is captured: a collector that ran in the middle
+    and freed an older engine's graph would destroy a graph during the capture, which CUDA
+    refuses, and the capture would be lost (seen when an engine was built after others had
+    gone). The collector runs once before instead."""
+    gc.collect()
+    was = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
 
 
 class _Tiles:
@@ -177,7 +195,7 @@ class _DecodeGraph:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = _lib.calls()
-        with torch.cuda.graph(graph):
+        with _no_collection(), torch.cuda.graph(graph):
             self.body(model)
         self.launches = _lib.calls() - before
         self.graph = graph
@@ -305,7 +323,7 @@ class _StepGraph:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = _lib.calls()
-        with torch.cuda.graph(graph, pool=pool):
+        with _no_collection(), torch.cuda.graph(graph, pool=pool):
             self.body(model)
         self.launches = _lib.calls() - before
         self.graph = graph
