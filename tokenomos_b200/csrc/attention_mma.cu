@@ -236,13 +236,16 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
         const int j0 = j_begin + it * 64;
         if (p_shift >= 0) {
-            loader.issue(base, base + TILE_BYTES, pool, bt_row, j0, lo, pos_last);
+            // (pages looked up one tile ahead, as in the decode kernel)
+            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, lo, pos_last);
+            if (it + 1 < n_tiles) loader.lookup(bt_row, j0 + 64, lo, pos_last);
         } else {
             load_tile<D>(base, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
             load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
         }
         cp_async_commit();
     };
+    if (p_shift >= 0) loader.lookup(bt_row, j_begin, lo, pos_last);
     issue(0);
     for (int it = 0; it < n_tiles; ++it) {
         cp_async_wait<0>();
@@ -329,7 +332,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
         const int j0 = j_begin + tile * 32;
         if (p_shift >= 0) {
-            loader.issue(base, base + TILE_BYTES, pool, bt_row, j0, lo, pos);
+            // the pages of this tile were looked up when the tile before it was issued; now the
+            // next tile's are, so that no copy waits for a block-table entry
+            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, lo, pos);
+            if (tile + 4 < t_end) loader.lookup(bt_row, j0 + 4 * 32, lo, pos);
         } else {
             load_tile<D>(base, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 0, lane, 32);
             load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 1, lane, 32);
@@ -337,7 +343,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         cp_async_commit();
     };
     int stage = 0;
-    if (t_begin + warp < t_end) issue(t_begin + warp, 0);
+    if (t_begin + warp < t_end) {
+        if (p_shift >= 0) loader.lookup(bt_row, j_begin + (t_begin + warp) * 32, lo, pos);
+        issue(t_begin + warp, 0);
+    }
     for (int tile = t_begin + warp; tile < t_end; tile += 4) {
         const bool more = tile + 4 < t_end;
         if (more) issue(tile + 4, stage ^ 1);
