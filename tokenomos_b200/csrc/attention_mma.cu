@@ -15,8 +15,6 @@
 // Keys past a query's position are never read: their shared-memory rows are zero-filled.
 #include <math.h>
 
-#include <cooperative_groups.h>
-
 #include "paged_tiles.cuh"
 
 namespace {
@@ -292,7 +290,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                        const int* tok_seq, const int* block_table,
                        int bt_stride, const int* tok_index, int H, int Hkv, int P,
                        int window, float scale, int nsplit, float* part_o,
-                       float* part_ml, int p_shift, int cluster_merge) {
+                       float* part_ml, int p_shift) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -383,10 +381,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         }
     }
     __syncthreads();
-    // with the splits of a (token, KV head) in one thread-block cluster, their partial results
-    // meet in distributed shared memory instead of in scratch memory and a second kernel
-    float* cl_o = sm_ml + 4 * 16 * 2;                              // [16][D]
-    float* cl_ml = cl_o + 16 * D;                                  // [16][2]
     for (int idx = tid; idx < G * D; idx += 128) {
         const int r = idx / D, c = idx % D;
         float M = -INFINITY;
@@ -403,12 +397,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         const int head = kvh * G + r;
         if (nsplit == 1) {
             out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-        } else if (cluster_merge) {
-            cl_o[r * D + c] = acc;
-            if (c == 0) {
-                cl_ml[r * 2] = M;
-                cl_ml[r * 2 + 1] = L;
-            }
         } else {
             const size_t slot = ((size_t)i * H + head) * nsplit + split;
             part_o[slot * D + c] = acc;
@@ -417,30 +405,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                 part_ml[slot * 2 + 1] = L;
             }
         }
-    }
-    if (nsplit > 1 && cluster_merge) {
-        // (every CTA of the cluster got here: they share the token, so none left at the top)
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        const int rank = (int)cluster.block_rank();
-        // the G * D outputs are dealt out over the cluster's CTAs, one per thread
-        for (int j = tid; j * nsplit + rank < G * D; j += 128) {
-            const int idx = j * nsplit + rank;
-            const int r = idx / D, c = idx % D;
-            float M = -INFINITY;
-            for (int k = 0; k < nsplit; ++k) M = fmaxf(M, cluster.map_shared_rank(cl_ml, k)[r * 2]);
-            float L = 0.f, acc = 0.f;
-            for (int k = 0; k < nsplit; ++k) {
-                const float* ml = cluster.map_shared_rank(cl_ml, k);
-                const float mk = ml[r * 2];
-                const float f = mk == -INFINITY ? 0.f : fast_exp2((mk - M) * scale_log2);
-                L += ml[r * 2 + 1] * f;
-                acc += cluster.map_shared_rank(cl_o, k)[r * D + c] * f;
-            }
-            out[((size_t)tok * H + kvh * G + r) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-        }
-        cluster.sync();      // nobody's shared memory goes away while a peer still reads it
     }
 }
 
@@ -475,38 +439,6 @@ int page_shift(int P) {
     int s = 0;
     while ((1 << s) < P) ++s;
     return s;
-}
-
-// Up to 8 splits (the portable cluster size) are merged inside a thread-block cluster.
-int g_decode_cluster = 1;
-bool decode_cluster_ok(int nsplit) { return g_decode_cluster && nsplit > 1 && nsplit <= 8; }
-
-template <typename Kernel, typename... Args>
-cudaError_t launch_decode(Kernel kernel, dim3 grid, size_t smem, cudaStream_t stream, int cluster_z, Args... args) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    int n = 0;
-    if (tk_pdl_enabled()) {
-        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
-    }
-    if (cluster_z > 1) {
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = cluster_z;
-        ++n;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 bool mma_shape_ok(int H, int Hkv, int D) {
@@ -554,18 +486,8 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
 // Floats of scratch the decode kernel needs for `n` tokens split `nsplit` ways:
 // part_o [n, H, nsplit, D] then part_ml [n, H, nsplit, 2] (nothing when nsplit is 1).
 TK_API int64_t tk_attn_decode_mma_scratch(int n, int H, int D, int nsplit) {
-    return nsplit <= 1 || decode_cluster_ok(nsplit) ? 0 : (int64_t)n * H * nsplit * (D + 2);
+    return nsplit <= 1 ? 0 : (int64_t)n * H * nsplit * (D + 2);
 }
-
-// 1 (default): up to 8 splits of a token meet in a thread-block cluster; 0: always through scratch
-// memory and the merge kernel (for measurements).
-TK_API int tk_attn_decode_cluster(int on) {
-    g_decode_cluster = on != 0;
-    return 0;
-}
-
-// Whether a call with this many splits merges them in a cluster (and needs no scratch memory).
-TK_API int tk_attn_decode_in_cluster(int nsplit) { return decode_cluster_ok(nsplit) ? 1 : 0; }
 
 TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, const int* positions,
                               const int* tok_seq, const int* block_table, int bt_stride,
@@ -575,37 +497,31 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n >= 0 && nsplit >= 1 && nsplit <= 65535, "attn_decode_mma: bad sizes");
     if (n == 0) return 0;
-    const bool cluster = decode_cluster_ok(nsplit);
-    TK_CHECK_ARG(nsplit == 1 || cluster || scratch != nullptr, "attn_decode_mma: %d splits need scratch memory", nsplit);
+    TK_CHECK_ARG(nsplit == 1 || scratch != nullptr, "attn_decode_mma: %d splits need scratch memory", nsplit);
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n * H * nsplit * D : nullptr;
     dim3 grid(n, Hkv, nsplit);
-    // K/V staging: 4 warps x 2 stages x (K, V) x 32 keys; the merges reuse it as [4][16][D+2] floats
-    // and, for the cluster's merge, [16][D+2] more
+    // K/V staging: 4 warps x 2 stages x (K, V) x 32 keys; the merge reuses it as [4][16][D+2] floats
     const size_t staging = 4 * 2 * 2 * 32 * (size_t)D * 2;
-    const size_t merge = 5 * 16 * ((size_t)D + 2) * sizeof(float);
+    const size_t merge = 4 * 16 * ((size_t)D + 2) * sizeof(float);
     const size_t smem = staging > merge ? staging : merge;
     auto q_ = (const __nv_bfloat16*)q;
     auto p_ = (const __nv_bfloat16*)kv_pool;
     auto o_ = (__nv_bfloat16*)out;
-    cudaError_t e;
     if (D == 64) {
-        e = launch_decode(attn_decode_mma_kernel<64>, grid, smem, stream, cluster ? nsplit : 0, q_, p_, o_, positions, tok_seq,
-                          block_table, bt_stride, tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml,
-                          page_shift(P), cluster ? 1 : 0);
-        if (e == cudaSuccess && nsplit > 1 && !cluster)
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
             tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
     } else {
-        e = launch_decode(attn_decode_mma_kernel<128>, grid, smem, stream, cluster ? nsplit : 0, q_, p_, o_, positions, tok_seq,
-                          block_table, bt_stride, tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml,
-                          page_shift(P), cluster ? 1 : 0);
-        if (e == cudaSuccess && nsplit > 1 && !cluster)
+        cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
             tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
-    }
-    if (e != cudaSuccess) {
-        tk_set_error("attn_decode_mma: launch failed: %s", cudaGetErrorString(e));
-        cudaGetLastError();
-        return -2;
     }
     TK_CHECK_LAUNCH("attn_decode_merge");
     return 0;

@@ -280,14 +280,13 @@ def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tens
                          nsplit: int) -> None:
     """Tensor-core attention for sequences that bring one token (``tok_index``: their rows in
     the packed batch; None: every row of ``q`` is one, in order, which spares the kernel a
-    lookup), each split ``nsplit`` ways over its keys; up to 8 splits meet inside a
-    thread-block cluster, more go through scratch memory that this function allocates and a
-    second kernel. Writes those rows of ``out`` [T, H, D]."""
+    lookup), each split ``nsplit`` ways over its keys; partial results go through scratch memory
+    that this function allocates and a merge kernel. Writes those rows of ``out`` [T, H, D]."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tok_index)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_decode_mma")
     n = tok_index.numel() if tok_index is not None else T
     scratch = None
-    if nsplit > 1 and not _lib.call("tk_attn_decode_in_cluster", int(nsplit)):
+    if nsplit > 1:
         scratch = torch.empty(n * H * nsplit * (D + 2), dtype=torch.float32, device=q.device)
     _lib.call("tk_attn_decode_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),

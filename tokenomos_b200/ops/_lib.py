@@ -41,8 +41,6 @@ _SIGNATURES = {
     "tk_attn_prefill_tc_status": [],
     "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
-    "tk_attn_decode_cluster": [I],
-    "tk_attn_decode_in_cluster": [I],
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
     "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, P],
@@ -102,8 +100,7 @@ def calls() -> int:
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
-            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune",
-            "tk_attn_decode_cluster", "tk_attn_decode_in_cluster"}
+            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
 
 
 _fns: dict = {}

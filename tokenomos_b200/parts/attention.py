@@ -84,11 +84,15 @@ class Attention:
 
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
     prefill_tc = os.environ.get("TOKENOMOS_B200_ATTN_TC", "1") != "0"
-    # CTAs the decode kernel should put on the GPU before it stops splitting keys further: three
-    # fit on an SM (shared memory), and several waves of them even out the last, partial wave
+    # How the decode kernel splits a token's keys over CTAs, measured on a B200 at batch 1 to 64
+    # and 512 to 32,768 cached positions: about DECODE_KEYS keys a CTA; more CTAs than that gives
+    # while fewer than DECODE_FILL of them would be on the GPU (never below DECODE_MIN_KEYS keys a
+    # CTA); never more than DECODE_CTAS CTAs (three fit on an SM by shared memory, and a few waves
+    # of them even out the last, partial one)
+    DECODE_KEYS = 512
+    DECODE_FILL = 256
+    DECODE_MIN_KEYS = 128
     DECODE_CTAS = 4 * 444
-    # fewest keys worth a CTA of their own
-    DECODE_MIN_KEYS = 256
 
     def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
@@ -113,8 +117,10 @@ class Attention:
             if self.window is not None:
                 longest = min(longest, self.window)
             rows = ctx.n_tokens if decode_only else singles.numel()
-            want = -(-self.DECODE_CTAS // (rows * self.kv_heads))
-            nsplit = max(1, min(want, -(-longest // self.DECODE_MIN_KEYS)))
+            per_split = rows * self.kv_heads                   # CTAs one split puts on the GPU
+            by_keys = -(-longest // self.DECODE_KEYS)
+            to_fill = min(-(-self.DECODE_FILL // per_split), -(-longest // self.DECODE_MIN_KEYS))
+            nsplit = max(1, min(-(-self.DECODE_CTAS // per_split), max(by_keys, to_fill)))
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
                                      self.window, self.scale, nsplit)
         return out
