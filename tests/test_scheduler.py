@@ -170,3 +170,22 @@ def test_random_loads_give_the_same_replies_as_a_roomy_pool(seed):
     for r in reqs:
         assert r.output == expected(r.prompt, r.max_new)
     assert tight.cache.free_slots() == tight.cache.max_requests
+
+
+def test_decode_attention_split_rule():
+    """How many CTAs share a decoded token's keys: about 512 keys each; more splits while the GPU
+    would stay empty (never below 128 keys a split); never more CTAs than fit in a few waves."""
+    from tokenomos_b200.parts.attention import Attention
+    f = Attention.decode_splits
+    assert f(8, 8, 4096) == 8 and f(64, 8, 4096) == 4 and f(32, 8, 4096) == 7     # 512 keys; the CTA cap
+    assert f(1, 8, 4096) == 32 and f(1, 8, 100) == 1 and f(8, 8, 1024) == 4       # filling the GPU
+    assert f(1, 8, 32768) == 64 and f(64, 8, 32768) == 4
+    for rows in (1, 2, 3, 8, 17, 64, 256, 1000):
+        for kv in (1, 2, 8):
+            prev = 0
+            for longest in (1, 64, 128, 129, 500, 2048, 4096, 10 ** 5):
+                n = f(rows, kv, longest)
+                assert 1 <= n <= max(1, -(-longest // Attention.DECODE_MIN_KEYS))
+                assert n * rows * kv <= Attention.DECODE_CTAS + rows * kv
+                assert n >= prev                    # a longer context never gets fewer splits
+                prev = n

@@ -94,6 +94,15 @@ class Attention:
     DECODE_MIN_KEYS = 128
     DECODE_CTAS = 4 * 444
 
+    @classmethod
+    def decode_splits(cls, rows: int, kv_heads: int, longest: int) -> int:
+        """Ways to split each decoded token's keys over CTAs, for ``rows`` tokens whose sequences
+        hold at most ``longest`` positions (see the constants above)."""
+        per_split = max(1, rows * kv_heads)                 # CTAs one split puts on the GPU
+        by_keys = -(-longest // cls.DECODE_KEYS)
+        to_fill = min(-(-cls.DECODE_FILL // per_split), -(-longest // cls.DECODE_MIN_KEYS))
+        return max(1, min(-(-cls.DECODE_CTAS // per_split), max(by_keys, to_fill)))
+
     def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
         over their keys so that a small batch still fills the GPU."""
@@ -117,10 +126,7 @@ class Attention:
             if self.window is not None:
                 longest = min(longest, self.window)
             rows = ctx.n_tokens if decode_only else singles.numel()
-            per_split = rows * self.kv_heads                   # CTAs one split puts on the GPU
-            by_keys = -(-longest // self.DECODE_KEYS)
-            to_fill = min(-(-self.DECODE_FILL // per_split), -(-longest // self.DECODE_MIN_KEYS))
-            nsplit = max(1, min(-(-self.DECODE_CTAS // per_split), max(by_keys, to_fill)))
+            nsplit = self.decode_splits(rows, self.kv_heads, longest)
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
                                      self.window, self.scale, nsplit)
         return out
