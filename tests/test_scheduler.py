@@ -173,13 +173,13 @@ def test_random_loads_give_the_same_replies_as_a_roomy_pool(seed):
 
 
 def test_decode_attention_split_rule():
-    """How many CTAs share a decoded token's keys: about 512 keys each; more splits while the GPU
+    """How many CTAs share a decoded token's keys: about 1,024 keys each; more splits while the GPU
     would stay empty (never below 128 keys a split); never more CTAs than fit in a few waves."""
     from tokenomos_b200.parts.attention import Attention
     f = Attention.decode_splits
-    assert f(8, 8, 4096) == 8 and f(64, 8, 4096) == 4 and f(32, 8, 4096) == 7     # 512 keys; the CTA cap
+    assert f(8, 8, 4096) == 4 and f(64, 8, 4096) == 4 and f(8, 8, 16384) == 16    # 1,024 keys a CTA
     assert f(1, 8, 4096) == 32 and f(1, 8, 100) == 1 and f(8, 8, 1024) == 4       # filling the GPU
-    assert f(1, 8, 32768) == 64 and f(64, 8, 32768) == 4
+    assert f(1, 8, 32768) == 32 and f(64, 8, 32768) == 4                           # the CTA cap
     for rows in (1, 2, 3, 8, 17, 64, 256, 1000):
         for kv in (1, 2, 8):
             prev = 0

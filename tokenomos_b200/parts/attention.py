@@ -85,11 +85,13 @@ class Attention:
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
     prefill_tc = os.environ.get("TOKENOMOS_B200_ATTN_TC", "1") != "0"
     # How the decode kernel splits a token's keys over CTAs, measured on a B200 at batch 1 to 64
-    # and 512 to 32,768 cached positions: about DECODE_KEYS keys a CTA; more CTAs than that gives
-    # while fewer than DECODE_FILL of them would be on the GPU (never below DECODE_MIN_KEYS keys a
-    # CTA); never more than DECODE_CTAS CTAs (three fit on an SM by shared memory, and a few waves
-    # of them even out the last, partial one)
-    DECODE_KEYS = 512
+    # and 512 to 32,768 cached positions: about DECODE_KEYS keys a CTA, counted on the longest
+    # sequence the engine allows, which is all a captured step knows (in practice a CTA then
+    # reads about half as many); more CTAs than that gives while fewer than DECODE_FILL of them
+    # would be on the GPU (never below DECODE_MIN_KEYS keys a CTA); never more than DECODE_CTAS
+    # CTAs (three fit on an SM by shared memory, and a few waves of them even out the last,
+    # partial one)
+    DECODE_KEYS = 1024
     DECODE_FILL = 256
     DECODE_MIN_KEYS = 128
     DECODE_CTAS = 4 * 444
