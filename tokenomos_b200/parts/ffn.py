@@ -25,7 +25,9 @@ class SwiGLU:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w = self.gate_up.weight
-        if self.run == RUN and ops.gemm_skinny_ok(x, w):
+        # (up to 8 rows: with 9 to 16 the library's product and the activation kernel are faster,
+        # 0.91 ms a decode step at 16 rows against 1.00 ms)
+        if self.run == RUN and x.shape[0] <= 8 and ops.gemm_skinny_ok(x, w):
             act = ops.gemm_skinny(x, w, self.gate_up.bias, swiglu=True)
         else:
             act = ops.swiglu(self.gate_up(x), self.run)
