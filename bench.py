@@ -38,9 +38,20 @@ CONFIG_1P2B = {
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
     "intermediate_size": 8192, "vocab_size": 65536, "rope_theta": 1000000.0, "norm_eps": 1e-5,
     "conv_L_cache": 3, "conv_bias": False, "tie_embedding": True,
+    # what the reference's declaration reads beside the keys above (Tokenomos
+    # models/lfm3/arch.py:61-67,98; models/load/checkpoint.py:160-165): the rotary parameters per
+    # attention kind, the tying flag under its other name, and a per-head output gate, whose
+    # 32 x 2048 matrix per attention layer is under 0.1 % of a step's bytes. Both arms run this
+    # one folder.
+    "rope_parameters": {"full_attention": {"rope_type": "default", "rope_theta": 1000000.0}},
+    "tie_word_embeddings": True, "attention_gate": True,
 }
 PROMPT = 2048
 CONTEXT = 4096
+# the far end of "decode to 4,096": prompts this long, decoded until the context is full
+PROMPT_FAR = 3584
+# device time the timed blocks of a decode measurement cover at least
+MIN_TIMED_MS = 200.0
 
 # BASELINE.json configs[3] and configs[4]: serving workloads on the 350M- and 2.6B-size models
 ATTN_AT_16 = (2, 5, 8, 10, 12, 14)
@@ -102,24 +113,60 @@ class Clocks:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def lfm3_tensor_shapes(config: dict) -> list[tuple[str, tuple, bool]]:
+    """(name, shape, is a norm weight) of every tensor of an LFM3 text folder, from the
+    config.json keys alone (names as Tokenomos models/lfm3/arch.py:76-126). Stated here, apart
+    from either engine's declaration, because both arms of the bench load the folder it makes:
+    each arm's loader then checks the list against its own."""
+    d, H, Hkv = config["hidden_size"], config["num_attention_heads"], config["num_key_value_heads"]
+    D = config.get("head_dim", d // H)
+    I, V, W = config["intermediate_size"], config["vocab_size"], config["conv_L_cache"]
+    out = [("model.embed_tokens.weight", (V, d), False)]
+    for i, kind in enumerate(config["layer_types"]):
+        p = f"model.layers.{i}."
+        if kind == "conv":
+            out += [(p + "conv.in_proj.weight", (3 * d, d), False), (p + "conv.out_proj.weight", (d, d), False),
+                    (p + "conv.conv.weight", (d, 1, W), False)]
+            if config.get("conv_bias"):
+                out.append((p + "conv.conv.bias", (d,), False))
+        else:
+            a = p + "self_attn."
+            out += [(a + "q_proj.weight", (H * D, d), False), (a + "k_proj.weight", (Hkv * D, d), False),
+                    (a + "v_proj.weight", (Hkv * D, d), False), (a + "o_proj.weight", (d, H * D), False),
+                    (a + "q_norm.weight", (D,), True), (a + "k_norm.weight", (D,), True)]
+            if config.get("attention_gate"):
+                out.append((a + "gate_proj.weight", (H, d), False))
+        out += [(p + "feed_forward.w1.weight", (I, d), False), (p + "feed_forward.w3.weight", (I, d), False),
+                (p + "feed_forward.w2.weight", (d, I), False), (p + "operator_norm.weight", (d,), True),
+                (p + "ffn_norm.weight", (d,), True)]
+    out.append(("model.embedding_norm.weight", (d,), True))
+    if not config.get("tie_word_embeddings", config.get("tie_embedding", True)):
+        out.append(("lm_head.weight", (V, d), False))
+    return out
+
+
 def write_folder(folder: Path, layers: int, config: dict | None = None) -> dict:
-    """The configuration's model folder with random weights drawn on the GPU (the same tensor
-    list and order as the random-weights mode; a CPU draw of 1.2 G values takes far longer)."""
+    """The configuration's model folder with random weights drawn on the GPU: matrices, the
+    embedding and conv taps N(0, 0.02), norm weights 1, bfloat16, seed 0 (a CPU draw of 1.2 G
+    values takes far longer). Imports neither engine."""
     import torch
     from safetensors.torch import save_file
-
-    from tokenomos_b200 import models
-    from tokenomos_b200.weights import random_tensors
 
     config = dict(config or CONFIG_1P2B)
     config["layer_types"] = config["layer_types"][:layers]
     config["num_hidden_layers"] = len(config["layer_types"])
-    arch = models.architecture_of(config)
-    decls = arch.declare(arch.config_class.from_dict(config)).tensor_decls()
-    tensors = random_tensors(decls, seed=0, std=0.02, dtype=torch.bfloat16, device="cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    tensors = {}
+    for name, shape, is_norm in lfm3_tensor_shapes(config):
+        if is_norm:
+            tensors[name] = torch.ones(shape, dtype=torch.bfloat16)
+        else:
+            t = torch.randn(shape, generator=gen, dtype=torch.float32, device="cuda") * 0.02
+            tensors[name] = t.to(torch.bfloat16).cpu()
     folder.mkdir(parents=True, exist_ok=True)
     (folder / "config.json").write_text(json.dumps(config))
-    save_file({k: v.cpu() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    save_file(tensors, str(folder / "model.safetensors"))
     return config
 
 
@@ -193,19 +240,30 @@ def device_decode(model, cfg, batch: int, steps: int, warmup: int, page: int, se
     torch.cuda.synchronize()
     ctx_start = cache.length(0)
     calls0 = _lib.calls()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        one()
-    end.record()
-    torch.cuda.synchronize()
+    # blocks of exactly K steps, each between two CUDA events with a synchronize on both sides;
+    # the block is repeated until MIN_TIMED_MS of device time are covered (three blocks at
+    # least, as long as the context has room) and the median block is the result
+    blocks = []
+    room = context - ctx_start - 2
+    while True:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one()
+        end.record()
+        torch.cuda.synchronize()
+        blocks.append(start.elapsed_time(end))
+        room -= steps
+        if room < steps or len(blocks) >= 64 or (len(blocks) >= 3 and sum(blocks) >= MIN_TIMED_MS):
+            break
     while pending:
         pending.pop(0).tokens()
-    ms = start.elapsed_time(end) / steps
+    ms = statistics.median(blocks) / steps
     graph = step_fn.decode_graph(batch)
     out = {"ms_per_step": ms, "tok_s": batch / ms * 1e3, "ctx_start": ctx_start,
            "ctx_end": cache.length(0), "launches_per_step": graph.launches,
-           "host_calls": _lib.calls() - calls0}
+           "host_calls": _lib.calls() - calls0, "blocks": len(blocks),
+           "timed_ms": sum(blocks)}
     for r in range(batch):
         cache.release(r)
     del eng
@@ -234,20 +292,7 @@ def device_prefill(model, cfg, page: int, reps: int = 3, tokens: int = PROMPT) -
         if i >= 2:
             times.append(start.elapsed_time(end))
     ms = statistics.median(times)
-    # flops of the step: 2 * tokens * parameters of every matrix the tokens pass (the head runs
-    # on one row), plus causal attention (q.k and p.v over half the square)
-    d, inter, H, Hkv, D = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads,
-                           cfg.num_key_value_heads, cfg.head_dim)
-    flops = 0
-    for kind in cfg.layer_types:
-        per_tok = 3 * d * inter
-        if kind == "conv":
-            per_tok += 3 * d * d + d * d
-        else:
-            per_tok += (H + 2 * Hkv) * D * d + H * D * d
-            flops += 2 * 2 * H * D * tokens * (tokens + 1) / 2
-        flops += 2 * tokens * per_tok
-    flops += 2 * cfg.vocab_size * d
+    flops = prefill_flops(cfg.to_dict(), tokens)
     del eng
     torch.cuda.empty_cache()
     return {"ms": ms, "tokens": tokens, "tok_s": tokens / ms * 1e3, "flops": flops}
@@ -416,6 +461,169 @@ def run_workload(name: str, page: int) -> int:
     return 0
 
 
+def bench_config(layers: int, batch: int, config: dict) -> dict:
+    """The ``config`` record of the JSON line: every size, flat; the same for both arms."""
+    return {
+        "model": "LFM3 1.2B-size (BASELINE configs[2]) + per-head output gate", "global_batch": batch,
+        "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
+        "layers": layers, "layers_of_config": 16, "hidden_size": config["hidden_size"],
+        "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
+        "head_dim": config["head_dim"], "intermediate_size": config["intermediate_size"],
+        "vocab_size": config["vocab_size"], "conv_L_cache": config["conv_L_cache"],
+        "attention_gate": bool(config.get("attention_gate")),
+        "l2": "inputs larger than L2 (weights read every step)",
+    }
+
+
+REF_ROOT = ROOT / "baseline" / "_ref"
+
+
+def reference_arm(args, warmup: int) -> dict:
+    """The same metric on the unmodified reference: its Python package as copied from its
+    ``src`` folder into ``baseline/_ref`` (its wheel needs maturin and a Rust toolchain, which
+    the offline wheelhouse lacks; the Rust module serves the JSON grammar only, Tokenomos
+    api/llm.py:27, and is stubbed with empty modules). The path is the reference's own decode
+    bench (Tokenomos bench/decode.py:62-137): ``models.load``, ``Engine(...)``, ``warmup()``,
+    ``generate`` of random prompts; the steady decode step is the median gap between the stamps
+    of consecutive decode-step enqueues with every row live, the prefill the device time of one
+    2,048-token request with one new token. Nothing of tokenomos_b200 is imported here."""
+    import tempfile
+    import types
+
+    sys.path.insert(0, str(REF_ROOT))
+    for name in ("tokenomos._rs", "tokenomos._rs.grammar"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    import torch
+    from tokenomos import models
+    from tokenomos.core.engine import Engine, Request
+
+    torch.cuda.set_device(0)
+    tmp = tempfile.TemporaryDirectory(prefix="tokenomos_ref_bench_")
+    folder = Path(tmp.name) / "lfm3_1p2b_random"
+    config = write_folder(folder, args.layers)
+    model = models.load(str(folder), "cuda", models.configure(str(folder), work="bf16"))
+    vocab = config["vocab_size"]
+    g = torch.Generator().manual_seed(2)
+    clocks = Clocks()
+    clocks.start()
+
+    def engine(batch: int, new: int, prompt: int):
+        page = 32                                        # the reference's default
+        max_len = prompt + new + 8
+        eng = Engine(model, slots=batch, page=page, max_len=max_len, new_cap=new, reserve_new=new,
+                     pages=batch * -(-max_len // page) + 8, graphs=True)
+        eng.warmup()
+        return eng
+
+    def decode(batch: int, steps: int, prompt: int) -> dict:
+        # enough decode steps for the K-step block to repeat as in the other arm
+        new = warmup + 8 + max(3 * steps, int(MIN_TIMED_MS / 0.5))
+        new = min(new, CONTEXT - prompt - 8) if prompt == PROMPT_FAR else new
+        eng = engine(batch, new, prompt)
+        reqs = [Request(torch.randint(0, vocab, (prompt,), generator=g).tolist(), max_new=new)
+                for _ in range(batch)]
+        eng.generate([Request(list(r.prompt), max_new=4) for r in reqs[:8]])
+        eng.stats = type(eng.stats)()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        results = eng.generate(reqs)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        assert all(len(r.tokens) == new for r in results)
+        st = eng.stats.stamps                            # (perf_counter, bucket, rows bound)
+        full = [i for i, (_, _, r) in enumerate(st) if r == batch]
+        lo, hi = full[0] + warmup, full[-1] - 2
+        gaps = [st[i + 1][0] - st[i][0] for i in range(lo, hi) if st[i][2] == batch and st[i + 1][2] == batch]
+        step_ms = statistics.median(gaps) * 1e3
+        span = st[hi][0] - st[lo][0]
+        out = {"ms_per_step": step_ms, "tok_s": batch / step_ms * 1e3, "steady_steps": len(gaps),
+               "span_tok_s": batch * (hi - lo) / span, "wall_s": wall,
+               "d2h_bytes_per_step": 4 * int(eng.ev_dev.numel())}
+        if batch == args.batch and prompt == PROMPT:
+            times = []
+            for i in range(5):
+                one = Request(torch.randint(0, vocab, (PROMPT,), generator=g).tolist(), max_new=1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                eng.generate([one])
+                b.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    times.append(a.elapsed_time(b))
+            out["prefill_ms"] = statistics.median(times)
+        del eng
+        torch.cuda.empty_cache()
+        return out
+
+    main_run = decode(args.batch, args.steps, PROMPT)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode(b, min(args.steps, 64), PROMPT)["tok_s"], 1)
+        for b in (1, args.batch, 64):
+            points[f"decode_b{b}_far"] = round(decode(b, min(args.steps, 64), PROMPT_FAR)["tok_s"], 1)
+    clock_report = clocks.stop()
+    tmp.cleanup()
+    pk = peaks()
+    flops = prefill_flops(config, PROMPT)
+    return {
+        "impl": "reference",
+        "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": bench_config(args.layers, args.batch, config),
+        "engine": {"page_size": 32, "timing": "median gap between decode-step enqueues, every row live "
+                   f"({main_run['steady_steps']} steps), the host one step ahead of the device"},
+        "clocks": clock_report,
+        "e2e": {"value": round(main_run["span_tok_s"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": main_run["d2h_bytes_per_step"],
+                "ms_per_step": round(args.batch / main_run["span_tok_s"] * 1e3, 4)},
+        "prefill": {"value": round(PROMPT / main_run["prefill_ms"] * 1e3, 1), "tokens": PROMPT,
+                    "ms": round(main_run["prefill_ms"], 3),
+                    "frac": round(flops / (main_run["prefill_ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "points": points,
+    }
+
+
+def run_reference(args, warmup: int) -> int:
+    if not (REF_ROOT / "tokenomos" / "__init__.py").exists():
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref/tokenomos is absent: the reference's wheel cannot be built "
+                          "offline (its backend is maturin, pyproject.toml:1-3), and its Python "
+                          "package was not copied there"}))
+        return 0
+    try:
+        line = reference_arm(args, warmup)
+    except Exception as e:  # noqa: BLE001 - the arm reports why it could not run
+        text = " ".join(f"{type(e).__name__}: {e}".split())
+        print(json.dumps({"impl": "reference", "unavailable": text[:400]}))
+        return 0
+    print(json.dumps(line))
+    return 0
+
+
+def prefill_flops(config: dict, tokens: int) -> float:
+    """Flops of one prompt of ``tokens``: 2 * tokens * parameters of every matrix the tokens
+    pass (the head runs on one row), plus causal attention (q.k and p.v over half the square)."""
+    d, inter = config["hidden_size"], config["intermediate_size"]
+    H, Hkv, D = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    flops = 0.0
+    for kind in config["layer_types"]:
+        per_tok = 3 * d * inter
+        if kind == "conv":
+            per_tok += 3 * d * d + d * d
+        else:
+            per_tok += (H + 2 * Hkv) * D * d + H * D * d
+            flops += 2 * 2 * H * D * tokens * (tokens + 1) / 2
+        flops += 2 * tokens * per_tok
+    return flops + 2 * config["vocab_size"] * d
+
+
+METRIC = "decode tokens/s (1.2B-size LFM3, batch 8, context 2048+)"
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
@@ -434,16 +642,12 @@ def main() -> int:
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
     args = ap.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference's wheel needs the maturin build backend and a Rust "
-                          "toolchain (pyproject.toml:1-3); neither is in the offline wheelhouse, so "
-                          "pip install --no-index into baseline/_ref fails"}))
-        return 0
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus > 1 is not built")
         return 2
     warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        return run_reference(args, warmup)
 
     import torch
 
@@ -463,7 +667,7 @@ def main() -> int:
 
     tmp = tempfile.TemporaryDirectory(prefix="tokenomos_b200_bench_")
     folder = Path(tmp.name) / "lfm3_1p2b_random"
-    write_folder(folder, args.layers)
+    config = write_folder(folder, args.layers)
     pages = args.batch * (CONTEXT // args.page) + 2
     llm = LLM(str(folder), work="bf16", slots=args.batch, page=args.page, max_len=CONTEXT,
               pages=pages, prefill_budget=PROMPT, graphs=True)
@@ -482,6 +686,9 @@ def main() -> int:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(device_decode(model, cfg, b, min(args.steps, 64), warmup,
                                                          args.page)["tok_s"], 1)
+        for b in (1, args.batch, 64):
+            points[f"decode_b{b}_far"] = round(device_decode(
+                model, cfg, b, min(args.steps, 64), warmup, args.page, prompt=PROMPT_FAR)["tok_s"], 1)
     e2e = e2e_decode(llm, cfg, args.batch, args.steps, warmup)
     clock_report = clocks.stop()
     llm.close()
@@ -493,21 +700,17 @@ def main() -> int:
                   + args.batch * conv_layers * 2 * (cfg.conv_L_cache - 1) * cfg.hidden_size * 2)
     achieved = step_bytes / (main_run["ms_per_step"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tokens/s (1.2B-size LFM3, batch 8, context 2048+)",
+        "impl": "ours",
+        "metric": METRIC,
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights N(0, 0.02)",
-        "config": {
-            "model": "LFM3 1.2B-size (BASELINE configs[2])", "global_batch": args.batch,
-            "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
-            "layers": args.layers, "layers_of_config": 16, "hidden_size": cfg.hidden_size,
-            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-            "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size,
-            "vocab_size": cfg.vocab_size, "conv_L_cache": cfg.conv_L_cache, "page_size": args.page,
-            "decode_ctx_start": main_run["ctx_start"], "decode_ctx_end": main_run["ctx_end"],
-            "l2": "inputs larger than L2 (weights read every step)",
-        },
+        "config": bench_config(args.layers, args.batch, config),
+        "engine": {"page_size": args.page, "decode_ctx_start": main_run["ctx_start"],
+                   "decode_ctx_end": main_run["ctx_end"], "timed_blocks": main_run["blocks"],
+                   "timed_ms": round(main_run["timed_ms"], 1),
+                   "timing": "median of blocks of exactly `steps` steps, CUDA events around each"},
         "clocks": clock_report,
         "e2e": {k: (round(v, 4 if k == "ms_per_step" else 1) if isinstance(v, float) else v)
                 for k, v in e2e.items()},

@@ -6,12 +6,13 @@ replies."""
 from __future__ import annotations
 
 import random
+from collections import deque
 
 import pytest
 import torch
 
 from tokenomos_b200.cache.manager import CacheManager
-from tokenomos_b200.engine.scheduler import Request, Scheduler
+from tokenomos_b200.engine.scheduler import NeedsDrain, Request, Scheduler
 from tokenomos_b200.parts.contract import PagedKV, SlotState
 
 SPECS = {(0, "conv"): SlotState((2, 8)), (1, "kv"): PagedKV(2, 16)}
@@ -170,6 +171,123 @@ def test_random_loads_give_the_same_replies_as_a_roomy_pool(seed):
     for r in reqs:
         assert r.output == expected(r.prompt, r.max_new)
     assert tight.cache.free_slots() == tight.cache.max_requests
+
+
+class FakeDevice:
+    """Stands in for the GPU when the host runs a step behind it: per request it keeps the
+    tokens that have gone through the "model" and the token its last step sampled (what
+    ``last_token[slot]`` holds on the device), which a share with ``fed_on_device`` feeds without
+    the host knowing its value."""
+
+    def __init__(self):
+        self.seen: dict[int, list[int]] = {}
+        self.last: dict[int, int] = {}
+
+    def run(self, planned) -> list[int]:
+        sampled = []
+        for p in planned:
+            r = p.req
+            if p.start == 0:
+                self.seen[r.rid] = []
+            history = self.seen[r.rid]
+            assert len(history) == p.start
+            if p.fed_on_device:
+                assert p.count == 1 and r.inflight == 1
+                history.append(self.last[r.rid])
+            else:
+                assert r.inflight == 0            # every value of the share is known on the host
+                history.extend(r.span(p.start, p.count))
+            if p.sample:
+                self.last[r.rid] = fake_next(history)
+                sampled.append(self.last[r.rid])
+        return sampled
+
+
+def drive_async(sched: Scheduler, arrivals=None, depth=1, log=None, limit=10000):
+    """``plan -> launch`` with ``deliver`` ``depth`` steps behind, as the engine's loop does with
+    captured steps; ``NeedsDrain`` delivers everything in flight first. Returns (steps, drains)."""
+    dev, inflight = FakeDevice(), deque()
+    arrivals = deque(arrivals or [])
+    steps = drains = 0
+
+    def deliver_all():
+        while inflight:
+            sched.deliver(*inflight.popleft())
+
+    while arrivals or not sched.idle():
+        if arrivals:
+            sched.add(arrivals.popleft())
+        try:
+            planned = sched.plan()
+        except NeedsDrain:
+            assert inflight
+            deliver_all()
+            drains += 1
+            continue
+        assert planned
+        if log is not None:
+            log.append([(p.req.rid, p.start, p.count, p.sample, p.fed_on_device) for p in planned])
+        sampled = dev.run(planned)
+        sched.launch(planned)
+        inflight.append((planned, sampled))
+        while len(inflight) > depth:
+            sched.deliver(*inflight.popleft())
+        sched.cache.check()
+        steps += 1
+        assert steps < limit
+    deliver_all()
+    return steps, drains
+
+
+def test_one_step_behind_gives_the_same_replies_and_no_step_for_a_sampled_out_request():
+    """The in-flight protocol without a GPU. A request whose every token is sampled is not
+    planned again: a reply of N tokens takes one step for the prompt and N - 1 decode steps, and
+    every step after the prompt's is decode-only (planning the finished request once more, for
+    the cache entry of its last token, made this count N + 1 and the last step a mixed one)."""
+    s = make(budget=64)
+    r = Request(list(range(10)), max_new=6)
+    s.add(r)
+    log = []
+    steps, drains = drive_async(s, log=log)
+    assert r.output == expected(r.prompt, 6) and r.finish == "length"
+    assert steps == 6 and drains == 1            # the drain: nothing to run, the last token in flight
+    assert [step[0][1:] for step in log[1:]] == [(10 + i, 1, True, True) for i in range(5)]
+    assert s.cache.free_pages() == 199 and s.cache.free_slots() == 8
+
+
+def test_one_step_behind_sees_a_stop_token_late_and_drops_the_extra_token():
+    s = make(budget=64)
+    prompt = [3, 1, 4, 1, 5]
+    full = expected(prompt, 30)
+    stop = full[4]
+    want = expected(prompt, 30, stop=(stop,))
+    r = Request(prompt, max_new=30, stop=(stop,))
+    s.add(r)
+    log = []
+    steps, _ = drive_async(s, log=log)
+    assert r.output == want and r.finish == "stop"
+    # the stop token is sampled by step len(want) - 1 (counting from 0) and read one step later:
+    # exactly one step more than the synchronous drive takes
+    assert steps == len(want) + 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_one_step_behind_random_loads_match_the_synchronous_drive(seed):
+    """Random arrivals into a tight pool: preemptions force ``NeedsDrain``, stops are seen late,
+    and the replies equal those of the plain drive (and of no scheduling at all)."""
+    rng = random.Random(100 + seed)
+    specs = [(rng.randint(1, 30), rng.randint(1, 25)) for _ in range(12)]
+    stops = tuple(rng.sample(range(50), 3))
+    sched = make(pages=rng.choice([30, 40, 60]), page=rng.choice([2, 4]), slots=rng.choice([2, 3, 5]),
+                 budget=rng.choice([7, 16, 40]), max_len=80)
+    reqs = [Request([rng.randint(0, 49) for _ in range(p)], max_new=n, stop=stops) for p, n in specs]
+    drive_async(sched, arrivals=reqs, depth=rng.choice([1, 1, 2]))
+    for r in reqs:
+        assert r.output == expected(r.prompt, r.max_new, stops), r.rid
+        assert r.finish == ("stop" if r.output[-1] in stops else "length")
+        assert r.inflight == 0
+    assert sched.cache.free_slots() == sched.cache.max_requests
+    assert sched.cache.free_pages() == sched.cache.num_pages - 1
 
 
 def test_decode_attention_split_rule():

@@ -1,20 +1,29 @@
-"""In-Python use, in the reference's manner (Tokenomos api/llm.py:36-56,71-143,227-234)::
+"""The Python entry point: ``LLM(path).generate(prompts, SamplingParams(...))``.
 
     from tokenomos_b200 import LLM, SamplingParams
-    with LLM(path, max_len=4096) as llm:
-        outs = llm.generate([[1, 2, 3], "some text"], SamplingParams(max_tokens=32))
+    with LLM(folder, max_len=4096) as llm:
+        replies = llm.generate([[1, 2, 3], [7, 8]], SamplingParams(max_tokens=32, temperature=0.8))
 
-``generate`` takes token id lists, or text when the folder has a ``tokenizer.json`` (folders
-written by the random-weights mode have none: use id lists). The engine loop runs in a
-background thread serving its inbox; an exception there is stored and surfaces in ``wait``.
-Stops: the generation config's EOS ids plus any ``stop_token_ids`` given.
+The names (``LLM``, ``SamplingParams``, ``Output``, ``generate``, ``submit``, ``wait``,
+``stream``) and the meaning of the options are the reference's (Tokenomos api/llm.py:36-56,
+71-143, 227-265); what is behind them is this engine. An ``LLM`` owns the loaded model, an
+``Engine`` and one worker thread that runs the engine's loop. Callers hand requests over through
+the engine's inbox and get them back through futures, so any number of threads may call
+``generate`` at once and their requests share the running batch.
+
+Prompts are lists of token ids. Text is accepted when the folder has a ``tokenizer.json``
+(folders written by the random-weights mode have none). A reply ends at ``max_tokens``, at one
+of the folder's end-of-sequence ids (``generation_config.json``), or at one of
+``SamplingParams.stop_token_ids``; the stop token is part of the reply.
 """
 
 from __future__ import annotations
 
 import json
+import queue
 import threading
-from concurrent.futures import Future, wait
+from concurrent.futures import Future
+from concurrent.futures import TimeoutError as FutureTimeout
 from dataclasses import dataclass
 from pathlib import Path
 
@@ -27,6 +36,9 @@ from tokenomos_b200.sampling.params import SamplingParams
 
 __all__ = ["LLM", "SamplingParams", "Output"]
 
+# how often a caller that waits looks whether the worker is still alive
+POLL_S = 0.1
+
 
 @dataclass
 class Output:
@@ -36,99 +48,152 @@ class Output:
     finish: str
 
 
+def folder_stop_ids(folder: Path) -> tuple[int, ...]:
+    """The end-of-sequence ids ``generation_config.json`` names: one id, a list, or none."""
+    path = folder / "generation_config.json"
+    if not path.is_file():
+        return ()
+    named = json.loads(path.read_text("utf-8")).get("eos_token_id")
+    if named is None:
+        return ()
+    ids = named if isinstance(named, (list, tuple)) else (named,)
+    return tuple(sorted({int(i) for i in ids if i is not None}))
+
+
+class _Worker(threading.Thread):
+    """The thread the engine's loop lives on. Whatever ends the loop other than ``halt`` is
+    kept in ``error`` for the callers, who would otherwise wait for futures nobody resolves."""
+
+    def __init__(self, engine: Engine, device: torch.device):
+        super().__init__(name="tokenomos-b200-engine", daemon=True)
+        self.engine, self.device = engine, device
+        self.halted = threading.Event()
+        self.error: BaseException | None = None
+
+    def run(self) -> None:
+        try:
+            if self.device.type == "cuda" and self.device.index is not None:
+                torch.cuda.set_device(self.device)
+            self.engine.run(self.halted)
+        except BaseException as exc:  # noqa: BLE001 - handed to the waiting callers
+            self.error = exc
+
+    def halt(self) -> None:
+        self.halted.set()
+        self.join()
+
+
 class LLM:
     def __init__(self, model: str, device: str = "cuda", arch=None, work: str | None = None,
                  **engine_kw):
-        """``arch``: a configured declaration (``models.configure(path, work=...)``); ``work``:
-        shorthand for the work dtype (``bf16`` or ``fp32``); ``engine_kw`` go to ``Engine``
-        (``slots``, ``page``, ``max_len``, ``pages``, ``prefill_budget``, ``graphs``)."""
+        """``model``: a folder with config.json and safetensors. ``arch``: what
+        ``models.configure(folder, work=...)`` returned, when the caller configured it; ``work``
+        alone picks the work dtype (``bf16``, the default, or ``fp32``). Every other keyword goes
+        to ``Engine``: ``slots``, ``page``, ``max_len``, ``pages``, ``prefill_budget``,
+        ``graphs``, ``warmup``."""
         self.path = Path(model)
-        if arch is None:
-            arch = models.configure(model, work=work)
-        self.model = models.load(model, device, arch)
-        self.tokenizer = None
-        tok = self.path / "tokenizer.json"
-        if tok.exists():
-            from tokenizers import Tokenizer
-            self.tokenizer = Tokenizer.from_file(str(tok))
-        gen_path = self.path / "generation_config.json"
-        gen = json.loads(gen_path.read_text("utf-8")) if gen_path.exists() else {}
-        eos = gen.get("eos_token_id", [])
-        eos = set(eos if isinstance(eos, list) else [eos])
-        self.eos = tuple(sorted(e for e in eos if e is not None))
-        self.engine = Engine(self.model, device=device, **engine_kw)
-        self._stop, self._error = threading.Event(), None
         self._device = torch.device(device)
-        self._thread = threading.Thread(target=self._serve, name="tokenomos-b200-engine", daemon=True)
-        self._thread.start()
+        self.model = models.load(model, device, arch or models.configure(model, work=work))
+        self.tokenizer = self._tokenizer()
+        self.eos = folder_stop_ids(self.path)
+        self.engine = Engine(self.model, device=device, **engine_kw)
+        self._worker = _Worker(self.engine, self._device)
+        self._worker.start()
 
-    def request(self, ids: list[int], p: SamplingParams) -> Request:
-        """An engine Request for prompt ``ids`` (stops: the model's EOS plus ``p``'s)."""
-        p.validate()
-        return Request(
-            list(ids), max_new=p.max_tokens, temperature=p.temperature, top_p=p.top_p,
-            top_k=p.top_k, min_p=p.min_p, seed=p.seed,
-            stop=tuple(dict.fromkeys(self.eos + tuple(p.stop_token_ids))))
+    def _tokenizer(self):
+        path = self.path / "tokenizer.json"
+        if not path.is_file():
+            return None
+        from tokenizers import Tokenizer
+        return Tokenizer.from_file(str(path))
 
-    # ---- the serving thread ----
-
-    def _serve(self) -> None:
-        try:
-            if self._device.index is not None:
-                torch.cuda.set_device(self._device)
-            self.engine.run(self._stop)
-        except BaseException as e:  # noqa: BLE001 - stored for the callers' threads
-            self._error = e
-            raise
-
-    def submit(self, req: Request) -> Future:
-        """Queue one engine request; the future resolves to it once ``req.result`` is set."""
-        fut: Future = Future()
-        req.on_done = lambda r: fut.set_result(r)
-        self.engine.submit(req)
-        return fut
+    # ---- one request ----
 
     def encode(self, text: str) -> list[int]:
         if self.tokenizer is None:
             raise ValueError(f"{self.path} has no tokenizer.json: pass token id lists")
         return self.tokenizer.encode(text, add_special_tokens=False).ids
 
+    def request(self, ids: list[int], p: SamplingParams) -> Request:
+        """The engine request for one prompt: ``p``'s options, and as stops the folder's
+        end-of-sequence ids followed by ``p.stop_token_ids`` (each id once)."""
+        p.validate()
+        stops = list(self.eos)
+        stops.extend(t for t in p.stop_token_ids if t not in stops)
+        return Request(prompt=list(ids), max_new=p.max_tokens, temperature=p.temperature,
+                       top_p=p.top_p, top_k=p.top_k, min_p=p.min_p, seed=p.seed, stop=tuple(stops))
+
+    def submit(self, req: Request) -> Future:
+        """Hand ``req`` to the engine. The future's result is ``req`` itself, with ``result``
+        filled in, as soon as the engine has finished it. A request the engine can never serve
+        raises here, in the caller's thread."""
+        self._check_worker()
+        done: Future = Future()
+        req.on_done = done.set_result
+        self.engine.submit(req)
+        return done
+
     def wait(self, futs: list[Future]) -> list[Request]:
-        """Every future's Request; raises if the engine thread died."""
-        pending = set(futs)
-        while pending:
-            if self._error is not None:
-                raise RuntimeError("engine thread failed") from self._error
-            _, pending = wait(pending, timeout=0.2)
-        return [f.result() for f in futs]
+        """The finished requests behind ``futs``, in their order. Raises ``RuntimeError`` (with
+        the cause chained) if the engine's thread has died, instead of waiting for ever."""
+        finished = []
+        for fut in futs:
+            while True:
+                try:
+                    finished.append(fut.result(timeout=POLL_S))
+                    break
+                except FutureTimeout:
+                    self._check_worker()
+        return finished
 
     def output(self, req: Request) -> Output:
-        r = req.result
-        text = ""
-        if self.tokenizer is not None:
-            text = self.tokenizer.decode(r.tokens, skip_special_tokens=True)
-        return Output(text, r.tokens, len(req.prompt), r.finish)
+        reply = req.result
+        text = self.tokenizer.decode(reply.tokens, skip_special_tokens=True) if self.tokenizer else ""
+        return Output(text=text, token_ids=reply.tokens, prompt_tokens=len(req.prompt),
+                      finish=reply.finish)
+
+    # ---- many ----
+
+    def generate(self, prompts: list, params: SamplingParams | None = None) -> list[Output]:
+        """One reply per prompt, in order. A prompt is a list of token ids, or text."""
+        params = params or SamplingParams()
+        futs = [self.submit(self.request(self._ids(prompt), params)) for prompt in prompts]
+        return [self.output(req) for req in self.wait(futs)]
+
+    def stream(self, prompt, params: SamplingParams | None = None):
+        """Yields the reply's token ids in runs, as the engine delivers them (the host reads a
+        step's tokens while the next step runs). The runs joined are ``generate``'s reply."""
+        runs: queue.Queue = queue.Queue()
+        req = self.request(self._ids(prompt), params or SamplingParams())
+        req.on_tokens = lambda toks: runs.put(list(toks))
+        fut = self.submit(req)
+        while True:
+            try:
+                yield runs.get(timeout=POLL_S)
+            except queue.Empty:
+                self._check_worker()
+                if fut.done() and runs.empty():
+                    return
+
+    def _ids(self, prompt) -> list[int]:
+        return self.encode(prompt) if isinstance(prompt, str) else list(prompt)
+
+    # ---- the worker ----
 
     @property
     def failure(self) -> BaseException | None:
-        """What ended the engine thread, or None while it serves."""
-        return self._error
+        """The exception that ended the engine's thread; None while it serves."""
+        return self._worker.error
+
+    def _check_worker(self) -> None:
+        if self._worker.error is not None:
+            raise RuntimeError("engine thread failed") from self._worker.error
 
     def close(self) -> None:
-        self._stop.set()
-        self._thread.join()
+        self._worker.halt()
 
-    def __enter__(self):
+    def __enter__(self) -> "LLM":
         return self
 
-    def __exit__(self, *exc):
+    def __exit__(self, *exc) -> None:
         self.close()
-
-    # ---- requests ----
-
-    def generate(self, prompts: list, params: SamplingParams | None = None) -> list[Output]:
-        """``prompts``: token id lists, or text (tokenized as is)."""
-        p = params or SamplingParams()
-        futs = [self.submit(self.request(x if isinstance(x, list) else self.encode(x), p))
-                for x in prompts]
-        return [self.output(r) for r in self.wait(futs)]

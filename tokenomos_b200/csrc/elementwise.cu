@@ -429,20 +429,22 @@ TK_API int tk_swiglu(const void* gu, void* out, int rows, int inter, int block, 
 // per-head sigmoid gate: x[t, h, :] = round(x[t, h, :] * round(sigmoid(g[t, h])))
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void head_gate_kernel(T* x, const T* g, int64_t total,
+__global__ void head_gate_kernel(T* x, const T* g, int64_t ldg, int64_t total, int heads,
                                  int head_dim) {
     pdl_launch_dependents();
     pdl_wait();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (; i < total; i += step) {
-        const float gate = to_f<T>(g[i / head_dim]);
+        const int64_t th = i / head_dim;          // token * heads + head
+        const float gate = to_f<T>(g[(th / heads) * ldg + th % heads]);
         const float s = round_as<T>(1.0f / (1.0f + expf(-gate)));
         x[i] = from_f<T>(to_f<T>(x[i]) * s);
     }
 }
 
-TK_API int tk_head_gate(void* x, const void* g, int rows, int heads, int head_dim, int dtype,
+// g: [rows, heads] with rows `ldg` elements apart (a column block of a wider projection's output)
+TK_API int tk_head_gate(void* x, const void* g, int64_t ldg, int rows, int heads, int head_dim, int dtype,
                         cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && heads > 0 && head_dim > 0, "head_gate: bad sizes");
     if (rows == 0) return 0;
@@ -451,10 +453,10 @@ TK_API int tk_head_gate(void* x, const void* g, int rows, int heads, int head_di
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                         : 148 * 16);
     if (dtype == TK_F32)
-        tk_launch(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, (const float*)g, total, head_dim);
+        tk_launch(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, (const float*)g, ldg, total, heads, head_dim);
     else if (dtype == TK_BF16)
         tk_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
-            (__nv_bfloat16*)x, (const __nv_bfloat16*)g, total, head_dim);
+            (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, total, heads, head_dim);
     else
         TK_CHECK_ARG(false, "head_gate: unknown dtype %d", dtype);
     TK_CHECK_LAUNCH("head_gate");

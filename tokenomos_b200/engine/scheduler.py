@@ -189,8 +189,10 @@ class Scheduler:
                 break
             total = len(req.prompt) + len(req.output) + req.inflight
             count = min(total - req.computed, budget)
-            if count <= 0:
-                continue                      # everything is sampled; waiting for its tokens
+            if count <= 0 or len(req.output) + req.inflight >= req.max_new:
+                # nothing left to compute: its last token is sampled (in flight until the next
+                # delivery), and the cache entry of a token nobody will follow is never read
+                continue
             fed = req.inflight > 0
             if fed and not (count == 1 and req.inflight == 1):
                 raise NeedsDrain("only a single decoded token can be fed on the device")

@@ -139,14 +139,16 @@ def swiglu(gu: torch.Tensor, block: int = 0) -> torch.Tensor:
 
 
 def head_gate(x: torch.Tensor, g: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
-    """In place: ``x[t, h, :] *= sigmoid(g[t, h])``."""
+    """In place: ``x[t, h, :] *= sigmoid(g[t, h])``; ``g`` [T, heads] may be a column block of a
+    wider tensor (rows any distance apart)."""
     _cuda(x, g)
-    if not (x.is_contiguous() and g.is_contiguous() and g.dtype == x.dtype):
-        raise KernelError("head_gate: contiguous tensors of one storage type")
+    if not (x.is_contiguous() and g.dim() == 2 and g.stride(1) == 1 and g.dtype == x.dtype):
+        raise KernelError("head_gate: contiguous x, g with contiguous rows, one storage type")
     rows = x.numel() // (heads * head_dim)
-    if g.numel() != rows * heads:
+    if tuple(g.shape) != (rows, heads):
         raise KernelError("head_gate: one gate per (token, head)")
-    _lib.call("tk_head_gate", _ptr(x), _ptr(g), rows, heads, head_dim, _dtype_code(x), _stream())
+    _lib.call("tk_head_gate", _ptr(x), _ptr(g), g.stride(0), rows, heads, head_dim, _dtype_code(x),
+              _stream())
     return x
 
 

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "tk_gather_rows_select": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_add_rmsnorm": [P, L, P, P, F, P, F, P, P, I, I, I, P],
     "tk_swiglu": [P, P, I, I, I, I, P],
-    "tk_head_gate": [P, P, I, I, I, I, P],
+    "tk_head_gate": [P, P, L, I, I, I, I, P],
     "tk_qk_norm_rope_write": [P, L, P, P, P, P, F, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "tk_attn_generic_rows": [],
     "tk_attn_generic": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P],

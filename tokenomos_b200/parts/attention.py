@@ -24,7 +24,11 @@ class Attention:
     def __init__(self, qkv: Linear, o: Linear, heads: int, kv_heads: int, head_dim: int, rope,
                  eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
                  window: int | None = None, scale: float | None = None,
-                 gate: Linear | None = None, kv_source: int | None = None):
+                 gate: Linear | None = None, kv_source: int | None = None,
+                 gate_fused: bool = False):
+        """``gate``: the per-head gate's projection as a part of its own; ``gate_fused``: its rows
+        are the last of ``qkv``'s instead (after q, k, v, then zero rows up to a multiple of 8), so
+        that one product yields both."""
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
         self.qkv, self.o, self.gate = qkv, o, gate
@@ -37,7 +41,11 @@ class Attention:
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.kv_source = kv_source
         own_kv = 0 if kv_source is not None else kv_heads
-        if qkv.out_features != (heads + 2 * own_kv) * head_dim:
+        self.qkv_width = (heads + 2 * own_kv) * head_dim
+        self.gate_fused = gate_fused
+        if gate_fused and gate is not None:
+            raise ValueError("attention: the gate is either fused into qkv or a projection of its own")
+        if qkv.out_features != self.qkv_width + (-(-heads // 8) * 8 if gate_fused else 0):
             raise ValueError("attention: the fused projection does not match the head counts")
         if rope.dim != head_dim:
             # the kernel rotates the first `dim` dims and passes the rest through
@@ -53,9 +61,15 @@ class Attention:
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
-        out = self._core(self.qkv(x), ctx, call)
-        if self.gate is not None:
-            ops.head_gate(out, self.gate(x).contiguous(), self.heads, self.head_dim)
+        proj = self.qkv(x)
+        if self.gate_fused:
+            n = self.qkv_width
+            out = self._core(proj[:, :n], ctx, call)
+            ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
+        else:
+            out = self._core(proj, ctx, call)
+            if self.gate is not None:
+                ops.head_gate(out, self.gate(x), self.heads, self.head_dim)
         return self.o(out.view(T, self.heads * self.head_dim))
 
     def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
@@ -140,8 +154,14 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
     rope = builder_of("position", rope_spec["kind"])(rope_spec["params"], {}, rt)
     source = params.get("kv_source")
     mats = [tensors["q"]] if source is not None else [tensors["q"], tensors["k"], tensors["v"]]
-    gate = Linear(tensors["gate"]) if "gate" in tensors else None
+    gated = "gate" in tensors
+    if gated:
+        # the gate reads the same input as q, k, v: its rows join theirs (padded to whole
+        # 16-byte chunks of the output row), one product instead of two
+        g = tensors["gate"]
+        pad = -g.shape[0] % 8
+        mats.append(torch.cat((g, g.new_zeros(pad, g.shape[1]))) if pad else g)
     return Attention(
         Linear.fused(mats), Linear(tensors["o"]), params["heads"], params["kv_heads"],
         params["head_dim"], rope, params["eps"], tensors.get("q_norm"), tensors.get("k_norm"),
-        params.get("window"), params.get("scale"), gate, source)
+        params.get("window"), params.get("scale"), None, source, gate_fused=gated)
