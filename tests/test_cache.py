@@ -157,3 +157,79 @@ def test_random_orders_keep_the_books(seed):
         c.release(rid)
     c.check()
     assert c.free_pages(("full",)) == c.num_pages - 1 and c.free_slots() == 4
+
+
+def _replay_books(cache, steps):
+    """A replay trace at the level of the books: what ``trace_util.run_in_process`` asks of the
+    cache manager, without a model."""
+    for s in steps:
+        for e in s["entries"]:
+            if e["id"] not in cache.requests:
+                cache.admit(e["id"])
+            cache.extend(e["id"], len(e["tokens"]))
+        for e in s["entries"]:
+            cache.commit(e["id"], len(e["tokens"]))
+        for rid in s["end"]:
+            cache.release(rid)
+        cache.check()
+
+
+@pytest.mark.parametrize("page", [4, 8, 16])
+def test_a_replay_pool_sized_by_its_own_pages_is_exactly_enough_and_shows_a_leak(page):
+    """The replay tests size the pool as ``max_live_tokens(steps, page)`` in the configuration's
+    own page size: the mixed trace then runs on exactly the pages its live requests need at the
+    worst moment (one page fewer cannot hold it), and a manager that leaks a single page when a
+    request ends cannot finish the trace. (Broken on purpose below: ``release`` keeps one page
+    of the first request that ends.)"""
+    import trace_util
+
+    rng = random.Random(page)
+    reqs = {f"r{i}": [0] * n for i, n in enumerate([5, 17, 33, 70, 96, 41])}
+    steps = trace_util.mixed(reqs, live=4, seed=3)
+    need = trace_util.max_live_tokens(steps, page)
+    specs = {(0, "conv"): SlotState((2, 8)), (1, "kv"): PagedKV(2, 16)}
+    pages = need // page + 1
+
+    def manager(n):
+        return CacheManager(specs, page, n, 8, torch.float32, "meta", max_len=max(need, page))
+
+    _replay_books(manager(pages), steps)
+    with pytest.raises(OutOfPages):
+        _replay_books(manager(pages - 1), steps)
+
+    leaky = manager(pages)
+    real_release, leaked = leaky.release, []
+
+    def release_but_keep_a_page(rid):
+        st = leaky.requests[rid]
+        if not leaked and st.tables[("full",)]:
+            leaked.append(st.tables[("full",)].pop())        # this page never goes back
+        real_release(rid)
+
+    leaky.release = release_but_keep_a_page
+    with pytest.raises((OutOfPages, CacheError)):
+        _replay_books(leaky, steps)
+    assert leaked
+
+
+def test_poisoned_pool_keeps_free_pages_and_rows_as_nan():
+    c = CacheManager(SPECS, 4, 8, 3, torch.float32, "cpu", poison=True)
+    kv, conv = c.states[(1, "kv")], c.states[(0, "conv")]
+    assert torch.isnan(kv[1:]).all() and not torch.isnan(kv[0]).any()
+    assert torch.isnan(conv[1:]).all() and not torch.isnan(conv[0]).any()
+    st = c.admit("a")
+    c.extend("a", 6)
+    pages = list(st.tables[("full",)])
+    kv[pages] = 1.0
+    conv[st.slot] = 2.0
+    c.commit("a", 6)
+    c.release("a")
+    assert torch.isnan(kv[pages]).all() and torch.isnan(conv[st.slot]).all()
+    # a window group's pages are poisoned as soon as the window has passed them
+    st = c.admit("b")
+    c.extend("b", 24)
+    first = st.tables[("window", 10)][0]
+    wkv = c.states[(2, "kv")]
+    wkv[first] = 3.0
+    c.commit("b", 24)
+    assert st.tables[("window", 10)][0] == 0 and torch.isnan(wkv[first]).all()

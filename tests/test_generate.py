@@ -19,6 +19,14 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
+# How far below the plain implementation's best logit a 16-bit greedy token may lie, per
+# configuration: two to four times the worst gap measured on a B200 over 192 generated tokens
+# each (A 0.000, B 0.012, C 0.035, D 0.005 nats, with 192, 187, 185 and 190 of the tokens the
+# plain implementation's own argmax). The reference holds its engine to 0.15 nats against its
+# dense forward (Tokenomos tests/core/test_engine.py:98-102).
+MARGIN_BF16 = {"A": 0.02, "B": 0.05, "C": 0.08, "D": 0.04}
+
+
 def prompts_for(name, lengths, seed=0):
     vocab = TINY[name]["config"]["vocab_size"]
     g = torch.Generator().manual_seed(seed)
@@ -35,15 +43,16 @@ def teacher_forced_ok(config, w, prompt, reply, margin):
             assert row.max().item() - row[tok].item() <= margin, (i, tok, int(row.argmax()))
 
 
-@pytest.mark.parametrize("work, margin", [("fp32", 1e-4), ("bf16", 0.12)])
+@pytest.mark.parametrize("work", ["fp32", "bf16"])
 @pytest.mark.parametrize("name, lengths, steps", [("A", [5, 17, 33], 16), ("B", [1, 9, 40, 64], 24)])
-def test_greedy_generation_through_llm(name, lengths, steps, work, margin, model_folders):
+def test_greedy_generation_through_llm(name, lengths, steps, work, model_folders):
+    margin = 1e-4 if work == "fp32" else MARGIN_BF16[name]
     from tokenomos_b200 import LLM, SamplingParams
     folder = model_folders[name][torch.bfloat16]
     config, w = plain_lfm3.read_folder(folder)
     prompts = prompts_for(name, lengths)
     with LLM(str(folder), work=work, page=TINY[name]["page"], max_len=256, slots=4, pages=40,
-             prefill_budget=48) as llm:
+             prefill_budget=48, poison=True) as llm:
         outs = llm.generate(prompts, SamplingParams(max_tokens=steps))
     for prompt, out in zip(prompts, outs):
         assert out.prompt_tokens == len(prompt) and out.finish == "length"
@@ -53,8 +62,8 @@ def test_greedy_generation_through_llm(name, lengths, steps, work, margin, model
             assert out.token_ids == plain_lfm3.generate_greedy(config, w, prompt, steps)
 
 
-@pytest.mark.parametrize("name, work, margin", [("A", "fp32", 1e-4), ("B", "fp32", 1e-4), ("D", "bf16", 0.25),
-                                                ("C", "bf16", 0.25)])
+@pytest.mark.parametrize("name, work, margin", [("A", "fp32", 1e-4), ("B", "fp32", 1e-4),
+                                                ("D", "bf16", MARGIN_BF16["D"]), ("C", "bf16", MARGIN_BF16["C"])])
 def test_mixed_steps_through_captured_graphs(name, work, margin, model_folders):
     """Prompt portions beside decoded tokens, replayed from captured steps (fixed-size layouts
     padded with a dummy sequence, empty tiles and unused rows) and queued one step ahead of the
@@ -63,7 +72,8 @@ def test_mixed_steps_through_captured_graphs(name, work, margin, model_folders):
     folder = model_folders[name][torch.bfloat16]
     config, w = plain_lfm3.read_folder(folder)
     prompts = prompts_for(name, [37, 5, 64, 18, 51, 9, 70, 26], seed=4)
-    kw = dict(work=work, page=TINY[name]["page"], max_len=128, slots=5, pages=60, prefill_budget=24)
+    kw = dict(work=work, page=TINY[name]["page"], max_len=128, slots=5, pages=60, prefill_budget=24,
+              poison=True)
     p = SamplingParams(max_tokens=20)
     with LLM(str(folder), graphs=False, **kw) as llm:
         eager = llm.generate(prompts, p)
@@ -89,7 +99,8 @@ def test_mixed_step_whose_bucket_has_as_many_tokens_as_sequences(model_folders):
     folder = model_folders[name][torch.bfloat16]
     config, w = plain_lfm3.read_folder(folder)
     prompts = prompts_for(name, [3 + (i * 7) % 11 for i in range(39)] + [50], seed=9)
-    kw = dict(work="bf16", page=TINY[name]["page"], max_len=96, slots=40, pages=200, prefill_budget=58)
+    kw = dict(work="bf16", page=TINY[name]["page"], max_len=96, slots=40, pages=200, prefill_budget=58,
+              poison=True)
     p = SamplingParams(max_tokens=12)
     with LLM(str(folder), graphs=True, **kw) as llm:
         llm.engine.step_fn.capture_after = 0
@@ -98,7 +109,34 @@ def test_mixed_step_whose_bucket_has_as_many_tokens_as_sequences(model_folders):
         llm.engine.cache.check()
     assert (64, 64) in shapes, shapes
     for prompt, o in zip(prompts, outs):
-        teacher_forced_ok(config, w, prompt, o.token_ids, 0.25)
+        teacher_forced_ok(config, w, prompt, o.token_ids, MARGIN_BF16[name])
+
+
+def test_warmup_records_every_step_shape_before_the_first_request(model_folders):
+    """``warmup=True``: the decode step of every batch bucket up to ``slots`` and the mixed step
+    of every (token, sequence) bucket under the budget are captured before serving (the
+    reference warms its engine up the same way and tests it, Tokenomos
+    tests/core/test_engine.py:172-194); serving then records nothing more and gives the tokens
+    of an engine that captured as it went."""
+    from tokenomos_b200 import LLM, SamplingParams
+    name = "D"
+    folder = model_folders[name][torch.bfloat16]
+    prompts = prompts_for(name, [37, 5, 64, 18, 51, 9, 70, 26], seed=4)
+    kw = dict(work="fp32", page=TINY[name]["page"], max_len=128, slots=5, pages=60, prefill_budget=24)
+    p = SamplingParams(max_tokens=12)
+    with LLM(str(folder), graphs=True, **kw) as llm:
+        llm.engine.step_fn.capture_after = 0
+        lazy = llm.generate(prompts, p)
+    with LLM(str(folder), graphs=True, warmup=True, **kw) as llm:
+        step_fn = llm.engine.step_fn
+        decode, mixed = set(step_fn._graphs), set(step_fn._step_graphs)
+        assert decode == {1, 2, 4, 5}                          # buckets up to the 5 slots
+        assert mixed == {(32, 4), (32, 16)}                    # 24 tokens at most, 5 + 1 sequences
+        assert llm.engine.stats.steps == 0
+        warm = llm.generate(prompts, p)
+        assert set(step_fn._graphs) == decode and set(step_fn._step_graphs) == mixed
+        assert llm.engine.stats.graph_steps > 0
+    assert [o.token_ids for o in warm] == [o.token_ids for o in lazy]
 
 
 def test_seeded_sampling_repeats_alone_and_in_batches(model_folders):
@@ -147,12 +185,55 @@ def test_pages_run_out_same_tokens_as_a_roomy_pool(model_folders):
         roomy = llm.generate(prompts, p)
         assert llm.engine.stats.preemptions == 0
     # 8 usable pages of 16 tokens: the six requests cannot all stay resident
-    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=6, pages=9) as llm:
+    with LLM(str(folder), work="fp32", page=16, max_len=64, slots=6, pages=9, poison=True) as llm:
         tight = llm.generate(prompts, p)
         assert llm.engine.stats.preemptions > 0
         llm.engine.cache.check()
         assert llm.engine.cache.free_pages() == 8
     assert [o.token_ids for o in tight] == [o.token_ids for o in roomy]
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_pages_run_out_in_bfloat16_with_captured_mixed_steps(graphs, model_folders):
+    """Preemption and recomputation on the 16-bit kernels (head size 64: the tensor-core
+    attention, the fused conv), with mixed steps captured and in flight when the pool runs dry.
+    A recomputed request sees its earlier tokens through other kernels (a prompt portion instead
+    of single tokens), so in 16 bits the replies are held to the plain implementation by teacher
+    forcing, not to the roomy pool's stream."""
+    from tokenomos_b200 import LLM, SamplingParams
+    name = "D"
+    folder = model_folders[name][torch.bfloat16]
+    config, w = plain_lfm3.read_folder(folder)
+    prompts = prompts_for(name, [20, 31, 9, 27, 14, 22], seed=3)
+    p = SamplingParams(max_tokens=30)
+    # 8 usable pages of 16 tokens: the six requests cannot all stay resident
+    with LLM(str(folder), work="bf16", page=16, max_len=64, slots=6, pages=9, prefill_budget=40,
+             graphs=graphs, poison=True) as llm:
+        llm.engine.step_fn.capture_after = 0
+        tight = llm.generate(prompts, p)
+        assert llm.engine.stats.preemptions > 0
+        assert llm.engine.stats.graph_steps > 0 or not graphs
+        llm.engine.cache.check()
+        assert llm.engine.cache.free_pages() == 8
+    for prompt, o in zip(prompts, tight):
+        assert len(o.token_ids) == 30
+        teacher_forced_ok(config, w, prompt, o.token_ids, MARGIN_BF16[name])
+
+
+def test_a_kernel_that_gave_up_on_a_barrier_fails_the_waiting_caller(model_folders, monkeypatch):
+    """The tcgen05 kernels bound their waits and leave a word where they gave up; the engine
+    reads it before it hands out the last replies of a batch. The word is made on the host here
+    (no kernel is made to wait): the status call is replaced by one that reports place 2."""
+    from tokenomos_b200 import LLM, SamplingParams, ops
+    folder = model_folders["A"][torch.bfloat16]
+    with LLM(str(folder), work="bf16", page=16, max_len=64, slots=2, pages=6) as llm:
+        ok = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=3))
+        assert len(ok[0].token_ids) == 3 and llm.failure is None
+        monkeypatch.setattr(ops, "gemm_tc_status", lambda: 2)
+        with pytest.raises(RuntimeError, match="engine thread failed") as err:
+            llm.generate([[1, 2, 3]], SamplingParams(max_tokens=3))
+        assert "gave up waiting on a barrier (place 2)" in str(err.value.__cause__)
+        assert isinstance(llm.failure, RuntimeError)
 
 
 @pytest.mark.filterwarnings("ignore::pytest.PytestUnhandledThreadExceptionWarning")

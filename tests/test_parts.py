@@ -159,252 +159,115 @@ def test_shared_kv_layer_reads_another_layers_cache(dtype):
     _close(got, torch.cat(want), dtype, "shared KV reader")
 
 
-def test_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
-    """A mixer defined here: an exponential moving average over the sequence with one state row
-    per request (its running value). It is registered with the parts registry, named by a new
-    architecture's declaration, loaded from a model folder and stepped in portions, with no
-    change to the framework's files."""
+def _toy_folder(tmp_path, mixer, ffn, seed=4):
+    import toy_parts
+    from tokenomos_b200.weights import write_model_folder
+    raw = toy_parts.toy_config(mixer, ffn)
+    return raw, write_model_folder(tmp_path / f"toy_{mixer}_{ffn}", raw, seed=seed, std=0.3)
+
+
+def _toy_weights(folder):
+    from safetensors.torch import load_file
+    return {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+
+
+@pytest.mark.parametrize("mixer, ffn", [("ema_host", "swiglu"), ("ema_device", "swiglu"),
+                                        ("attention_scaled", "routed"), ("attention_learned", "routed")])
+def test_toy_parts_register_build_and_step(mixer, ffn, tmp_path):
+    """Parts defined in ``tests/toy_parts.py`` (a mixer with state of its own, once planned on
+    the host and once from device tensors with a state spec class of its own; a feed-forward that
+    routes tokens to experts; two position encodings, one of them not a rotation and with a
+    tensor of its own) are registered, named by a new architecture's declaration, loaded from a
+    model folder and stepped whole, in portions and beside another request, with no change to the
+    framework's files. The logits agree with each other and with the plain restatement."""
+    import toy_parts
     from tokenomos_b200 import models
     from tokenomos_b200.cache.manager import CacheManager
     from tokenomos_b200.engine.step import StepEntry, StepFunction
-    from tokenomos_b200.parts.contract import SlotState
-    from tokenomos_b200.parts.registry import register
-    from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_NORM, ROLE_VECTOR, BlockSpec,
-                                           LayerCall, ModelSpec, PartSpec, TensorDecl)
-    from tokenomos_b200.weights import write_model_folder
 
-    class EmaMixer:
-        def __init__(self, decay: torch.Tensor):
-            self.decay = torch.sigmoid(decay)          # [width], float32
-
-        def state_specs(self):
-            return {"ema": SlotState((self.decay.numel(),), torch.float32)}
-
-        def forward(self, x, ctx, call):
-            state = ctx.states[(call, "ema")]
-            out = torch.empty_like(x)
-            start = 0
-            for s, n in enumerate(ctx.host.seq_lens):
-                slot = ctx.host.seq_slot[s]
-                run = state[slot].clone() if ctx.host.seq_ctx[s] > 0 else torch.zeros_like(state[slot])
-                for t in range(start, start + n):
-                    run = self.decay * run + (1 - self.decay) * x[t].float()
-                    out[t] = run.to(x.dtype)
-                state[slot] = run
-                start += n
-            return out
-
-    register("mixer", "toy_ema", lambda params, tensors, rt: EmaMixer(tensors["decay"]))
-
-    class ToyConfig:
-        def __init__(self, width, vocab, layers, eps):
-            self.width, self.vocab, self.layers, self.eps = width, vocab, layers, eps
-
-        @classmethod
-        def from_dict(cls, raw):
-            return cls(raw["width"], raw["vocab_size"], raw["layers"], raw["eps"])
-
-    class ToyArch:
-        names = ("ToyEmaForCausalLM",)
-        config_class = ToyConfig
-
-        def declare(self, cfg, tensor_names=()):
-            def norm(name):
-                return PartSpec("rmsnorm", {"eps": cfg.eps},
-                                {"weight": TensorDecl(f"{name}.weight", (cfg.width,), ROLE_NORM)})
-            blocks = []
-            for i in range(cfg.layers):
-                p = f"toy.{i}."
-                blocks.append(BlockSpec("prenorm", {
-                    "mixer": PartSpec("toy_ema", {}, {"decay": TensorDecl(f"{p}decay", (cfg.width,), ROLE_VECTOR)}),
-                    "ffn": PartSpec("swiglu", {}, {
-                        "gate": TensorDecl(f"{p}w1.weight", (2 * cfg.width, cfg.width)),
-                        "up": TensorDecl(f"{p}w3.weight", (2 * cfg.width, cfg.width)),
-                        "down": TensorDecl(f"{p}w2.weight", (cfg.width, 2 * cfg.width))}),
-                    "pre_mixer_norm": norm(f"{p}n1"), "pre_ffn_norm": norm(f"{p}n2"),
-                    "post_mixer_norm": None, "post_ffn_norm": None}))
-            return ModelSpec(cfg.width, cfg.vocab,
-                             TensorDecl("toy.embed.weight", (cfg.vocab, cfg.width), ROLE_EMBEDDING),
-                             tuple(blocks), tuple(LayerCall(i) for i in range(cfg.layers)),
-                             norm("toy.final"), None)
-
-    models.register(ToyArch())
-    raw = {"architectures": ["ToyEmaForCausalLM"], "width": 24, "vocab_size": 50, "layers": 2, "eps": 1e-5}
-    folder = write_model_folder(tmp_path / "toy", raw, seed=4, std=0.3)
+    raw, folder = _toy_folder(tmp_path, mixer, ffn)
     model = models.load(folder, "cuda", models.configure(folder, work="fp32"))
-    assert isinstance(model.blocks[0].mixer, EmaMixer)
-    cache = CacheManager(model.state_specs(), 4, 8, 3, torch.float32, "cuda", max_len=64)
-    assert tuple(cache.states[(1, "ema")].shape) == (4, 24)
-    step = StepFunction(model, cache)
-    ids = torch.randint(0, 50, (19,)).tolist()
-    cache.admit("w")
-    whole = step.run([StepEntry("w", ids, list(range(19)))])
-    cache.release("w")
-    cache.admit("other")      # takes the slot "w" had, and leaves its state behind
-    step.run([StepEntry("other", [1, 2, 3], [])])
-    cache.admit("p")
-    parts = [step.run([StepEntry("p", ids[a:b], list(range(b - a))), StepEntry("other", [7], [])][:1 + (a > 0)])
-             for a, b in ((0, 5), (5, 6), (6, 19))]
-    assert torch.allclose(torch.cat(parts), whole, atol=1e-5)
-    # and against a plain restatement of the toy model
-    from safetensors.torch import load_file
-    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
-    r = w["toy.embed.weight"][ids]
-    for i in range(2):
-        p = f"toy.{i}."
-        x = plain_lfm3.rmsnorm(r, w[f"{p}n1.weight"], 1e-5)
-        decay = torch.sigmoid(w[f"{p}decay"].float()).double()
-        run, m = torch.zeros(24, dtype=torch.float64), []
-        for t in range(19):
-            run = decay * run + (1 - decay) * x[t]
-            m.append(run)
-        r = r + torch.stack(m)
-        x = plain_lfm3.rmsnorm(r, w[f"{p}n2.weight"], 1e-5)
-        r = r + plain_lfm3.swiglu(x, w, p, torch.float64)
-    want = plain_lfm3.rmsnorm(r, w["toy.final.weight"], 1e-5) @ w["toy.embed.weight"].T
-    assert (whole.double().cpu() - want).abs().max().item() < 1e-4 * want.abs().max().item()
-
-
-def test_toy_routed_ffn_and_toy_position_encoding_register_build_and_step(tmp_path):
-    """Two more parts defined here, with no change to the framework's files: a feed-forward that
-    routes every token to one of three small experts (router logits and probabilities in 32-bit)
-    and a position encoding (rotary angles of positions divided by a factor), both registered
-    with the parts registry and named by a new architecture's declaration beside the framework's
-    own attention mixer. The model is loaded from a folder and stepped whole, in portions and
-    beside another request; the logits agree with each other and with a plain restatement."""
-    from tokenomos_b200 import models, ops
-    from tokenomos_b200.cache.manager import CacheManager
-    from tokenomos_b200.engine.step import StepEntry, StepFunction
-    from tokenomos_b200.parts.linear import Linear
-    from tokenomos_b200.parts.registry import register
-    from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_NORM, BlockSpec, LayerCall, ModelSpec,
-                                           PartSpec, TensorDecl)
-    from tokenomos_b200.weights import write_model_folder
-
-    E, FACTOR = 3, 4.0
-
-    class RoutedFFN:
-        def __init__(self, router, experts):
-            self.router = router.float()                      # [E, width]
-            self.experts = experts                            # [(gate_up Linear, down Linear)]
-
-        def forward(self, x):
-            probs = torch.softmax(x.float() @ self.router.T, dim=-1)
-            weight, choice = probs.max(dim=-1)
-            out = torch.zeros_like(x)
-            for e, (gate_up, down) in enumerate(self.experts):
-                rows = (choice == e).nonzero().flatten()
-                if rows.numel():
-                    y = down(ops.swiglu(gate_up(x[rows].contiguous())))
-                    out[rows] = (weight[rows, None] * y.float()).to(x.dtype)
-            return out
-
-    def build_routed(params, tensors, rt):
-        experts = [(Linear.fused([tensors[f"gate{e}"], tensors[f"up{e}"]]), Linear(tensors[f"down{e}"]))
-                   for e in range(params["experts"])]
-        return RoutedFFN(tensors["router"], experts)
-
-    class ScaledRope:
-        """Rotary tables of ``position / factor``: the kernels multiply positions by
-        ``inv_freq``, so dividing the frequencies does it."""
-
-        def __init__(self, head_dim, theta, factor, device):
-            idx = torch.arange(0, head_dim, 2, dtype=torch.float32)
-            self.inv_freq = (1.0 / (theta ** (idx / head_dim)) / factor).to(device).contiguous()
-            self.dim = head_dim
-
-        def tables(self, ctx):
-            return self.inv_freq
-
-    register("feed_forward", "toy_routed", build_routed)
-    register("position", "toy_scaled_rope",
-             lambda params, tensors, rt: ScaledRope(params["head_dim"], params["theta"], params["factor"], rt.device))
-
-    class ToyConfig:
-        def __init__(self, raw):
-            self.width, self.vocab, self.layers, self.eps = raw["width"], raw["vocab_size"], raw["layers"], raw["eps"]
-            self.heads, self.kv_heads, self.head_dim, self.inter = raw["heads"], raw["kv_heads"], raw["head_dim"], raw["inter"]
-
-        @classmethod
-        def from_dict(cls, raw):
-            return cls(raw)
-
-    class ToyArch:
-        names = ("ToyRoutedForCausalLM",)
-        config_class = ToyConfig
-
-        def declare(self, c, tensor_names=()):
-            def norm(name, n):
-                return PartSpec("rmsnorm", {"eps": c.eps}, {"weight": TensorDecl(f"{name}.weight", (n,), ROLE_NORM)})
-            blocks = []
-            for i in range(c.layers):
-                p = f"toy.{i}."
-                H, Hkv, D, d = c.heads, c.kv_heads, c.head_dim, c.width
-                mixer = PartSpec("attention", {
-                    "heads": H, "kv_heads": Hkv, "head_dim": D, "eps": c.eps, "window": None,
-                    "position": {"kind": "toy_scaled_rope", "params": {"head_dim": D, "theta": 100.0, "factor": FACTOR}},
-                }, {"q": TensorDecl(f"{p}q.weight", (H * D, d)), "k": TensorDecl(f"{p}k.weight", (Hkv * D, d)),
-                    "v": TensorDecl(f"{p}v.weight", (Hkv * D, d)), "o": TensorDecl(f"{p}o.weight", (d, H * D)),
-                    "q_norm": TensorDecl(f"{p}qn.weight", (D,), ROLE_NORM),
-                    "k_norm": TensorDecl(f"{p}kn.weight", (D,), ROLE_NORM)})
-                ffn_tensors = {"router": TensorDecl(f"{p}router.weight", (E, d))}
-                for e in range(E):
-                    ffn_tensors[f"gate{e}"] = TensorDecl(f"{p}e{e}.w1.weight", (c.inter, d))
-                    ffn_tensors[f"up{e}"] = TensorDecl(f"{p}e{e}.w3.weight", (c.inter, d))
-                    ffn_tensors[f"down{e}"] = TensorDecl(f"{p}e{e}.w2.weight", (d, c.inter))
-                blocks.append(BlockSpec("prenorm", {
-                    "mixer": mixer, "ffn": PartSpec("toy_routed", {"experts": E}, ffn_tensors),
-                    "pre_mixer_norm": norm(f"{p}n1", d), "pre_ffn_norm": norm(f"{p}n2", d),
-                    "post_mixer_norm": None, "post_ffn_norm": None}))
-            return ModelSpec(c.width, c.vocab, TensorDecl("toy.embed.weight", (c.vocab, c.width), ROLE_EMBEDDING),
-                             tuple(blocks), tuple(LayerCall(i) for i in range(c.layers)),
-                             norm("toy.final", c.width), None)
-
-    models.register(ToyArch())
-    raw = {"architectures": ["ToyRoutedForCausalLM"], "width": 40, "vocab_size": 60, "layers": 2, "eps": 1e-5,
-           "heads": 4, "kv_heads": 2, "head_dim": 16, "inter": 24}
-    folder = write_model_folder(tmp_path / "toy_routed", raw, seed=7, std=0.3)
-    model = models.load(folder, "cuda", models.configure(folder, work="fp32"))
-    assert isinstance(model.blocks[0].ffn, RoutedFFN)
-    assert isinstance(model.blocks[1].mixer.rope, ScaledRope)
-    cache = CacheManager(model.state_specs(), 4, 24, 3, torch.float32, "cuda", max_len=64)
+    kinds = {"ema_host": toy_parts.EmaMixerHost, "ema_device": toy_parts.EmaMixerDevice}
+    if mixer in kinds:
+        assert isinstance(model.blocks[0].mixer, kinds[mixer])
+        assert model.capture_safe == (mixer == "ema_device")
+    else:
+        want_rope = toy_parts.ScaledRope if mixer == "attention_scaled" else toy_parts.LearnedPosition
+        assert isinstance(model.blocks[1].mixer.rope, want_rope) and model.capture_safe
+        assert isinstance(model.blocks[0].ffn, toy_parts.RoutedFFN)
+    cache = CacheManager(model.state_specs(), 4, 24, 3, torch.float32, "cuda", max_len=64, poison=True)
+    if mixer.startswith("ema"):
+        assert tuple(cache.states[(1, "ema")].shape) == (4, raw["width"])
+        assert cache.states[(1, "ema")].dtype == torch.float32
     step = StepFunction(model, cache)
     T = 21
-    ids = torch.randint(0, 60, (T,)).tolist()
+    ids = torch.randint(0, raw["vocab_size"], (T,)).tolist()
     cache.admit("w")
     whole = step.run([StepEntry("w", ids, list(range(T)))])
     cache.release("w")
-    cache.admit("other")
+    cache.admit("other")      # takes the slot and the pages "w" had
     step.run([StepEntry("other", [1, 2, 3], [])])
     cache.admit("p")
     parts = [step.run([StepEntry("p", ids[a:b], list(range(b - a))), StepEntry("other", [7], [])][:1 + (a > 0)])
              for a, b in ((0, 6), (6, 7), (7, 9), (9, T))]
     assert torch.allclose(torch.cat(parts), whole, atol=1e-5)
-
-    # the plain restatement: same formulas, float64, whole sequence
-    from safetensors.torch import load_file
-    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
-    H, Hkv, D = 4, 2, 16
-    r = w["toy.embed.weight"][ids]
-    cos, sin = plain_lfm3.rope_tables(torch.arange(T) / FACTOR, D, D // 2, 100.0, torch.float64)
-    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
-    for i in range(2):
-        p = f"toy.{i}."
-        x = plain_lfm3.rmsnorm(r, w[f"{p}n1.weight"], 1e-5)
-        q = plain_lfm3.rmsnorm((x @ w[f"{p}q.weight"].T).view(T, H, D), w[f"{p}qn.weight"], 1e-5)
-        k = plain_lfm3.rmsnorm((x @ w[f"{p}k.weight"].T).view(T, Hkv, D), w[f"{p}kn.weight"], 1e-5)
-        q, k = plain_lfm3.rotate(q, cos, sin), plain_lfm3.rotate(k, cos, sin).repeat_interleave(H // Hkv, 1)
-        v = (x @ w[f"{p}v.weight"].T).view(T, Hkv, D).repeat_interleave(H // Hkv, 1)
-        sc = (torch.einsum("ihd,jhd->hij", q, k) * D ** -0.5).masked_fill(~causal[None], float("-inf"))
-        r = r + torch.einsum("hij,jhd->ihd", sc.softmax(-1), v).reshape(T, H * D) @ w[f"{p}o.weight"].T
-        x = plain_lfm3.rmsnorm(r, w[f"{p}n2.weight"], 1e-5)
-        probs = torch.softmax(x @ w[f"{p}router.weight"].T, dim=-1)
-        weight, choice = probs.max(dim=-1)
-        f = torch.zeros_like(x)
-        for t in range(T):
-            e = int(choice[t])
-            g, u = x[t] @ w[f"{p}e{e}.w1.weight"].T, x[t] @ w[f"{p}e{e}.w3.weight"].T
-            f[t] = weight[t] * ((torch.nn.functional.silu(g) * u) @ w[f"{p}e{e}.w2.weight"].T)
-        r = r + f
-    want = plain_lfm3.rmsnorm(r, w["toy.final.weight"], 1e-5) @ w["toy.embed.weight"].T
+    want = toy_parts.toy_forward(raw, _toy_weights(folder), ids)
     assert (whole.double().cpu() - want).abs().max().item() < 2e-4 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("mixer, ffn", [("ema_host", "swiglu"), ("ema_device", "swiglu"),
+                                        ("attention_scaled", "routed"), ("attention_learned", "routed")])
+def test_toy_architectures_generate_through_the_entry_point_with_and_without_graphs(mixer, ffn, tmp_path):
+    """The same toy models through ``LLM.generate``: scheduler, mixed steps, captured CUDA graphs.
+    With ``graphs=True`` a model whose parts are all ``capture_safe`` is recorded and replayed
+    (the device-side EMA, the routed feed-forward, both position encodings); the host-planned EMA
+    is not ``capture_safe``, the engine says so in a warning and runs it eagerly. Either way the
+    tokens equal the eager engine's, and every token is the plain restatement's choice given the
+    same history."""
+    import warnings
+
+    import toy_parts
+    from tokenomos_b200 import LLM, SamplingParams
+
+    raw, folder = _toy_folder(tmp_path, mixer, ffn, seed=11)
+    w = _toy_weights(folder)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, raw["vocab_size"], (n,), generator=g).tolist() for n in (9, 3, 17, 6, 12)]
+    kw = dict(work="fp32", page=4, max_len=48, slots=3, pages=40, prefill_budget=10, poison=True)
+    p = SamplingParams(max_tokens=10)
+    with LLM(str(folder), graphs=False, **kw) as llm:
+        eager = llm.generate(prompts, p)
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        with LLM(str(folder), graphs=True, **kw) as llm:
+            llm.engine.step_fn.capture_after = 0
+            graphed = llm.generate(prompts, p)
+            stats = llm.engine.stats
+            captured = llm.engine.graphs
+    if mixer == "ema_host":
+        assert not captured and stats.graph_steps == 0
+        assert any("not capture_safe: EmaMixerHost" in str(c.message) for c in caught)
+    else:
+        assert captured and stats.graph_steps > 0 and stats.decode_steps > 0
+    for prompt, a, b in zip(prompts, eager, graphed):
+        assert a.token_ids == b.token_ids
+        logits = toy_parts.toy_forward(raw, w, prompt + b.token_ids)
+        for i, tok in enumerate(b.token_ids):
+            row = logits[len(prompt) + i - 1]
+            assert row.max().item() - row[tok].item() <= 1e-4, (mixer, i, tok, int(row.argmax()))
+
+
+@pytest.mark.filterwarnings("ignore::pytest.PytestUnhandledThreadExceptionWarning")
+def test_a_part_that_reads_host_lists_in_a_captured_step_fails_loudly(tmp_path):
+    """A mixer that claims ``capture_safe`` but plans from ``ctx.host``'s per-sequence lists would
+    be recorded once and then replay the first batch's plan for ever. The lists do not exist in a
+    captured step: the first capture raises, and the caller sees it."""
+    from tokenomos_b200 import LLM, SamplingParams
+    from tokenomos_b200.parts.contract import LayoutUnavailable
+
+    raw, folder = _toy_folder(tmp_path, "ema_lying", "swiglu")
+    with LLM(str(folder), work="fp32", page=4, max_len=32, slots=2, pages=20, graphs=True) as llm:
+        with pytest.raises(RuntimeError, match="engine thread failed") as err:
+            llm.generate([[1, 2, 3]], SamplingParams(max_tokens=4))
+        assert isinstance(err.value.__cause__, LayoutUnavailable)
+        assert "ctx.host.seq_lens does not exist in a captured step" in str(err.value.__cause__)

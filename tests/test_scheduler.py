@@ -294,7 +294,8 @@ def test_decode_attention_split_rule():
     """How many CTAs share a decoded token's keys: about 1,024 keys each; more splits while the GPU
     would stay empty (never below 128 keys a split); never more CTAs than fit in a few waves."""
     from tokenomos_b200.parts.attention import Attention
-    f = Attention.decode_splits
+    from tokenomos_b200.parts.registry import Tuning
+    f, t = Attention.decode_splits, Tuning()
     assert f(8, 8, 4096) == 4 and f(64, 8, 4096) == 4 and f(8, 8, 16384) == 16    # 1,024 keys a CTA
     assert f(1, 8, 4096) == 32 and f(1, 8, 100) == 1 and f(8, 8, 1024) == 4       # filling the GPU
     assert f(1, 8, 32768) == 32 and f(64, 8, 32768) == 4                           # the CTA cap
@@ -303,7 +304,7 @@ def test_decode_attention_split_rule():
             prev = 0
             for longest in (1, 64, 128, 129, 500, 2048, 4096, 10 ** 5):
                 n = f(rows, kv, longest)
-                assert 1 <= n <= max(1, -(-longest // Attention.DECODE_MIN_KEYS))
-                assert n * rows * kv <= Attention.DECODE_CTAS + rows * kv
+                assert 1 <= n <= max(1, -(-longest // t.decode_min_keys))
+                assert n * rows * kv <= t.decode_ctas_per_sm * t.sm_count + rows * kv
                 assert n >= prev                    # a longer context never gets fewer splits
                 prev = n

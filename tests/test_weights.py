@@ -67,6 +67,34 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert "1 with a wrong shape" in msg and "stored [16, 64]" in msg and "[32, 64]" in msg
 
 
+def test_vision_language_folder_loads_its_text_stack_and_ignores_the_rest(tmp_path):
+    """A multimodal folder nests the text stack under ``model.language_model.`` and stores a
+    vision tower and a projector beside it; a tied checkpoint may also store ``lm_head.weight``.
+    None of those is the text model's business. A stray tensor *under* the text stack's prefix
+    still is (checked by adding one: the load must then fail)."""
+    folder = write_model_folder(tmp_path / "m", TINY_A, seed=0)
+    path = folder / "model.safetensors"
+    tensors = {k.replace("model.", "model.language_model.", 1): v for k, v in load_file(str(path)).items()}
+    tensors["model.vision_tower.patch_embed.weight"] = torch.zeros(4, 3)
+    tensors["model.multi_modal_projector.linear.weight"] = torch.zeros(5)
+    tensors["lm_head.weight"] = torch.zeros(TINY_A["vocab_size"], TINY_A["hidden_size"])
+    save_file(tensors, str(path))
+    cfg = {"architectures": ["Lfm3VlForConditionalGeneration"], "text_config": TINY_A,
+           "vision_config": {"hidden_size": 8}}
+    (folder / "config.json").write_text(json.dumps(cfg))
+    ckpt = Checkpoint(folder)
+    arch = models.architecture_of(cfg)
+    spec = arch.declare(arch.config_class.from_dict(cfg), ckpt.names())
+    assert spec.scope == ("model.language_model.",)
+    got = load_tensors(ckpt, spec.tensor_decls(), torch.float32, "cpu", spec.scope)
+    assert "model.language_model.embed_tokens.weight" in got and "lm_head.weight" not in got
+    assert not any("vision" in k or "projector" in k for k in got)
+    tensors["model.language_model.layers.0.stray.weight"] = torch.zeros(2)
+    save_file(tensors, str(path))
+    with pytest.raises(WeightError, match="1 unexpected: model.language_model.layers.0.stray.weight"):
+        load_tensors(Checkpoint(folder), spec.tensor_decls(), torch.float32, "cpu", spec.scope)
+
+
 def test_conv_width_must_match_config(tmp_path):
     folder = write_model_folder(tmp_path / "m", TINY_A, seed=0)
     cfg = json.loads((folder / "config.json").read_text())

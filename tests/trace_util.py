@@ -117,7 +117,7 @@ def collect(steps: list[dict], per_step: dict[int, torch.Tensor]) -> dict[str, t
 
 
 def run_in_process(folder, dtype: str, steps: list[dict], max_tokens: int, page: int,
-                   max_requests: int = 8) -> dict[int, torch.Tensor]:
+                   max_requests: int = 8, poison: bool = True) -> dict[int, torch.Tensor]:
     """Drive the framework's own loader, cache manager and step function with the trace."""
     from tokenomos_b200 import models
     from tokenomos_b200.cache.manager import CacheManager
@@ -126,8 +126,10 @@ def run_in_process(folder, dtype: str, steps: list[dict], max_tokens: int, page:
     conf = models.configure(folder, work=dtype)
     model = models.load(folder, "cuda", conf)
     pages = -(-max_tokens // page) + 1
+    # every page and state row that no request holds is full of NaN: a read past a request's
+    # own positions, or of a state row the request before left, shows in the logits
     cache = CacheManager(model.state_specs(), page, pages, max_requests, conf.work, "cuda",
-                         max_len=max(max_tokens, page))
+                         max_len=max(max_tokens, page), poison=poison)
     step_fn = StepFunction(model, cache)
     out = {}
     for s in steps:

@@ -20,12 +20,12 @@ core/pools.py:90-108, kernels/engine/slots.py:20-108).
 from __future__ import annotations
 
 import heapq
+import math
 from dataclasses import dataclass, field
 
 import torch
 
-from tokenomos_b200.parts.contract import (PagedKV, SharedState, SlotState, StateKey, StateSpec,
-                                           WindowKV)
+from tokenomos_b200.parts.contract import StateKey, StateSpec
 
 
 class OutOfPages(RuntimeError):
@@ -93,10 +93,15 @@ class RequestState:
 
 class CacheManager:
     def __init__(self, specs: dict[StateKey, StateSpec], page_size: int, num_pages: int,
-                 max_requests: int, dtype: torch.dtype, device, max_len: int | None = None):
+                 max_requests: int, dtype: torch.dtype, device, max_len: int | None = None,
+                 poison: bool = False):
         """``num_pages``: pages of each group's pool, the null page included. ``max_requests``:
         live requests (slots 1..max_requests). ``max_len``: longest sequence (sets the block
-        table's width; default: what the pool could hold)."""
+        table's width; default: what the pool could hold). ``poison`` (for tests): every page
+        and every state row that no live request holds is kept full of NaN (all of them at the
+        start, each again when it is given back), so that a kernel that reads a position it must
+        not read, or a stale state row, shows in the logits; the null page and the null row stay
+        zero."""
         if page_size < 1 or num_pages < 2 or max_requests < 1:
             raise ValueError("cache: page_size >= 1, num_pages >= 2 (page 0 is the null page), "
                              "max_requests >= 1")
@@ -110,21 +115,29 @@ class CacheManager:
         self.state_groups: dict[StateKey, tuple] = {}
         self.slots = FreeList(max_requests + 1, first=1)
         self.requests: dict[object, RequestState] = {}
+        # what a spec needs is said by the spec itself (``storage`` and the attributes that go
+        # with it, see parts.contract), so a part may bring a spec class of its own
         for key, spec in specs.items():
-            if isinstance(spec, (PagedKV, WindowKV)):
+            storage = getattr(spec, "storage", None)
+            if storage == "paged":
                 g = self.groups.get(spec.group)
                 if g is None:
-                    window = spec.window if isinstance(spec, WindowKV) else None
-                    g = self.groups[spec.group] = Group(spec.group, window, FreeList(num_pages))
+                    g = self.groups[spec.group] = Group(spec.group, spec.window, FreeList(num_pages))
+                elif g.window != spec.window:
+                    raise ValueError(f"state {key}: cache group {spec.group} holds a window of "
+                                     f"{g.window}, this spec asks for {spec.window}")
                 g.members.append(key)
-                shape = (num_pages, 2, spec.kv_heads, page_size, spec.head_dim)
+                shape = (num_pages, *spec.page_shape(page_size))
                 self.states[key] = torch.zeros(shape, dtype=dtype, device=self.device)
                 self.state_groups[key] = spec.group
-            elif isinstance(spec, SlotState):
+            elif storage == "slot":
                 self.states[key] = torch.zeros((max_requests + 1, *spec.shape),
                                                dtype=spec.dtype or dtype, device=self.device)
+            elif storage != "shared":
+                raise ValueError(f"state {key}: a spec's storage is 'paged', 'slot' or 'shared', "
+                                 f"not {storage!r}")
         for key, spec in specs.items():
-            if isinstance(spec, SharedState):
+            if spec.storage == "shared":
                 src = (spec.source, spec.name)
                 if src not in self.states:
                     raise ValueError(f"state {key} reads {src}, which owns no memory")
@@ -134,6 +147,22 @@ class CacheManager:
 
         # the groups whose pages a window gives back as a request advances
         self._windowed = [(k, g) for k, g in self.groups.items() if g.window is not None]
+        self.poison = bool(poison)
+        if self.poison:
+            for key, spec in specs.items():
+                if spec.storage != "shared" and self.states[key].dtype.is_floating_point:
+                    self.states[key][1:] = float("nan")
+
+    def _poison_pages(self, group: Group, pages: list[int]) -> None:
+        if pages:
+            index = torch.tensor(pages, dtype=torch.long, device=self.device)
+            for key in group.members:
+                self.states[key].index_fill_(0, index, float("nan"))
+
+    def _poison_slot(self, slot: int) -> None:
+        for key, spec in self.specs.items():
+            if spec.storage == "slot" and self.states[key].dtype.is_floating_point:
+                self.states[key][slot] = float("nan")
 
     # ---- sizes ----
 
@@ -141,8 +170,16 @@ class CacheManager:
         """Bytes one page costs across every paged layer (all groups)."""
         total = 0
         for key, spec in self.specs.items():
-            if isinstance(spec, (PagedKV, WindowKV)):
-                total += 2 * spec.kv_heads * self.page_size * spec.head_dim * self.dtype.itemsize
+            if spec.storage == "paged":
+                total += math.prod(spec.page_shape(self.page_size)) * self.dtype.itemsize
+        return total
+
+    def bytes_per_slot(self) -> int:
+        """Bytes one request's fixed-size state rows cost across every layer."""
+        total = 0
+        for key, spec in self.specs.items():
+            if spec.storage == "slot":
+                total += math.prod(spec.shape) * (spec.dtype or self.dtype).itemsize
         return total
 
     def free_pages(self, group: tuple | None = None) -> int:
@@ -253,6 +290,8 @@ class CacheManager:
         for k, g in self._windowed:
             table = st.tables[k]
             passed = min(self._first_needed_block(g, st.length), len(table))
+            if self.poison:
+                self._poison_pages(g, [table[b] for b in range(st.first_live.get(k, 0), passed)])
             for b in range(st.first_live.get(k, 0), passed):
                 g.pages.give(table[b])
                 table[b] = 0
@@ -267,6 +306,10 @@ class CacheManager:
             for page in st.tables[k]:
                 if page:
                     g.pages.give(page)
+            if self.poison:
+                self._poison_pages(g, [page for page in st.tables[k] if page])
+        if self.poison:
+            self._poison_slot(st.slot)
         self.slots.give(st.slot)
 
     def _get(self, rid) -> RequestState:

@@ -13,6 +13,7 @@ from __future__ import annotations
 import queue
 import threading
 import time
+import warnings
 from dataclasses import dataclass, field
 
 import torch
@@ -49,31 +50,76 @@ class Stats:
 class Engine:
     def __init__(self, model, slots: int = 64, page: int = 16, max_len: int = 4096,
                  pages: int | None = None, prefill_budget: int = 2048, graphs: bool = True,
-                 kv_fraction: float = 0.8, device: str = "cuda"):
+                 kv_fraction: float = 0.8, device: str = "cuda", poison: bool = False,
+                 warmup: bool = False):
         """``slots``: live requests. ``page``: tokens per cache page. ``max_len``: longest
         sequence (prompt + reply). ``pages``: pages per cache group, the null page included
         (None: ``kv_fraction`` of the free memory, at most what ``slots`` sequences of
-        ``max_len`` need). ``prefill_budget``: tokens per step. ``graphs``: decode-only steps
-        replay a CUDA graph per batch-size bucket."""
+        ``max_len`` need). ``prefill_budget``: tokens per step. ``graphs``: steps replay
+        captured CUDA graphs (decode-only steps per batch-size bucket, mixed steps per token and
+        sequence bucket). ``poison`` (for tests): the cache manager keeps every page and state
+        row that no request holds full of NaN. ``warmup``: call ``warmup()`` before
+        the first request is served."""
         self.model = model
         self.device = torch.device(device)
         specs = model.state_specs()
         if pages is None:
+            # the fixed-size state rows come first, the pages share what is left (as the
+            # reference sizes its pools, Tokenomos core/pools.py:34-68)
             probe = CacheManager(specs, page, 2, 1, model.dtype, "meta", max_len)
             per_page = max(1, probe.bytes_per_page())
-            free = torch.cuda.mem_get_info(self.device)[0]
+            free = torch.cuda.mem_get_info(self.device)[0] - (slots + 1) * probe.bytes_per_slot()
+            if free <= 0:
+                raise ValueError(f"{slots} state rows of {probe.bytes_per_slot()} bytes exceed the free "
+                                 "memory: fewer slots")
             pages = int(free * kv_fraction) // per_page
             pages = max(2, min(pages, slots * -(-max_len // page) + 1))
-        self.cache = CacheManager(specs, page, pages, slots, model.dtype, self.device, max_len)
+        self.cache = CacheManager(specs, page, pages, slots, model.dtype, self.device, max_len,
+                                  poison=poison)
         self.step_fn = StepFunction(model, self.cache)
         self.scheduler = Scheduler(self.cache, prefill_budget, slots)
-        self.graphs = graphs
+        # a step is recorded as a CUDA graph only if every part of the model can be (see
+        # parts.contract: capture_safe); otherwise every step runs eagerly
+        self.graphs = bool(graphs) and model.capture_safe
+        if graphs and not self.graphs:
+            warnings.warn("graphs=True, but these parts are not capture_safe: "
+                          f"{', '.join(model.not_capture_safe())}; every step runs eagerly", stacklevel=2)
         # decode steps queued on the device whose tokens the host has not read: (plan, handle)
         self._inflight: deque = deque()
         self.depth = 1
         self._checked_at = 0       # stats.steps when the kernels' error word was last read
         self.inbox: queue.Queue[Request] = queue.Queue()
         self.stats = Stats()
+        self.prefill_budget, self.slots = prefill_budget, slots
+        if warmup:
+            self.warmup()
+
+    def warmup(self) -> tuple[int, int]:
+        """Touch every kernel variant and record every step shape serving will meet, before the
+        first request (the reference's engine does the same before it serves, Tokenomos
+        core/engine.py:635-664): two short requests run one eager mixed step (it builds the
+        kernel library if need be, loads the library handles and tells which tile lists the
+        model's parts ask for), then the decode step of every batch-size bucket up to ``slots``
+        and the mixed step of every (token, sequence) bucket under the token budget are
+        captured. Without it each shape is captured when serving first meets it (a mixed one
+        the third time). Returns the numbers of decode and mixed shapes recorded; the statistics
+        start afresh."""
+        vocab, cache = self.model.vocab, self.cache
+        longest = min(cache.max_len, (cache.num_pages - 1) * cache.page_size) - 2
+        count = min(2, self.slots)
+        n = max(2, min(longest // max(1, count), self.prefill_budget // 2 + 3))
+        was, self.graphs = self.graphs, False
+        try:
+            self.generate([Request([(7 * i + r) % vocab for i in range(n)], max_new=2) for r in range(count)])
+        finally:
+            self.graphs = was
+        recorded = (0, 0)
+        if self.graphs:
+            recorded = self.step_fn.capture_shapes(self.slots, self.prefill_budget, self.slots)
+        torch.cuda.synchronize(self.device)
+        self.stats = Stats()
+        self._checked_at = 0
+        return recorded
 
     # ---- requests in ----
 
@@ -94,7 +140,25 @@ class Engine:
             except queue.Empty:
                 return
 
+    # a continuously busy engine reads the kernels' error words this often (steps)
+    CHECK_EVERY = 512
+
+    def _check_kernels(self) -> None:
+        """The tcgen05 kernels bound every wait on a barrier instead of hanging, and record
+        where they gave up. Reading the words waits for the device, so it happens where the host
+        waits anyway: before the last replies of a batch are handed out, when the engine drains,
+        and every ``CHECK_EVERY`` steps of an engine that never goes idle."""
+        if self.stats.steps == self._checked_at or self.cache.device.type != "cuda":
+            return
+        self._checked_at = self.stats.steps
+        for what, where in (("GEMM", ops.gemm_tc_status()), ("attention", ops.attention_prefill_tc_status())):
+            if where:
+                raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
+                                   "the tokens of the steps since the last check are not to be trusted")
+
     def _finish(self, finished: list[Request]) -> list[Request]:
+        if finished and self.scheduler.idle():
+            self._check_kernels()            # nothing is in flight: the check costs nothing
         for req in finished:
             req.result = Result(list(req.output), req.finish)
             if req.on_done is not None:
@@ -109,16 +173,10 @@ class Engine:
         return finished
 
     def drain(self) -> list[Request]:
-        """Read every step in flight: after this the host knows every sampled token. Also the
-        place where a kernel that gave up waiting on a barrier (the tcgen05 GEMM bounds every
-        wait instead of hanging) turns into an exception."""
+        """Read every step in flight: after this the host knows every sampled token. Also a
+        place where a kernel that gave up waiting on a barrier turns into an exception."""
         finished = self._finish(self._drain())
-        if self.stats.steps != self._checked_at and self.cache.device.type == "cuda":
-            self._checked_at = self.stats.steps
-            for what, where in (("GEMM", ops.gemm_tc_status()), ("attention", ops.attention_prefill_tc_status())):
-                if where:
-                    raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
-                                       "the tokens of the steps since the last check are not to be trusted")
+        self._check_kernels()
         return finished
 
     def _decode_step(self, planned, finished: list[Request]) -> list[Request]:
@@ -158,6 +216,8 @@ class Engine:
         ends therefore decodes one token too many, which is dropped. Any other step (prompt
         portions, a preemption) first reads what is in flight and then runs synchronously."""
         finished: list[Request] = []
+        if self.stats.steps - self._checked_at >= self.CHECK_EVERY:
+            self._check_kernels()
         try:
             planned = self.scheduler.plan()
         except NeedsDrain:
@@ -231,8 +291,9 @@ class Engine:
         return self._finish(finished)
 
     def run(self, stop: threading.Event | None = None) -> None:
-        """Serve the inbox until nothing is queued or running (``stop`` None), or until ``stop``
-        is set (a serving thread; it blocks briefly on the inbox while idle)."""
+        """The engine's loop. Without ``stop`` it returns once every queued request is answered;
+        with ``stop`` (an event, for a worker thread) it keeps serving, sleeping on the inbox for
+        a moment whenever there is nothing to do, until the event is set."""
         start = time.perf_counter()
         while True:
             self._take_inbox()
@@ -248,7 +309,8 @@ class Engine:
         self.stats.wall_s += time.perf_counter() - start
 
     def generate(self, requests: list[Request]) -> list[Result]:
-        """Submit ``requests`` and serve until the engine is idle."""
+        """The replies to ``requests``, in their order: queues them all, then runs the loop on the
+        caller's thread until nothing is left to do."""
         for r in requests:
             self.submit(r)
         self.run()

@@ -167,7 +167,7 @@ class _DecodeGraph:
             cu_seqlens=arange, seq_ctx=view("seq_ctx"), seq_slot=view("seq_slot"),
             block_tables={g: view(("table", g)).view(b, self.width) for g in self.groups},
             states=cache.states, state_groups=cache.state_groups, page_size=cache.page_size,
-            host=HostLayout([1] * b, [0] * b, [0] * b, True, cache.max_len),
+            host=HostLayout.of_captured_step(True, cache.max_len),
             tile_source=_ConstTiles(arange[:b], zeros, ones))
         self.ids_host, self.use_prev = view("ids_host"), view("use_prev")
         self.sampling = view("sampling")
@@ -297,7 +297,7 @@ class _StepGraph:
             cu_seqlens=view("cu"), seq_ctx=view("seq_ctx"), seq_slot=view("seq_slot"),
             block_tables={g: view(("table", g)).view(S, self.width) for g in self.groups},
             states=cache.states, state_groups=cache.state_groups, page_size=cache.page_size,
-            host=HostLayout([], [], [], False, cache.max_len), tile_source=_FixedTiles(views))
+            host=HostLayout.of_captured_step(False, cache.max_len), tile_source=_FixedTiles(views))
         self.view = view
         self.graph = None
         self.launches = 0
@@ -415,6 +415,7 @@ class StepFunction:
         self._step_graph_uses: dict[tuple, int] = {}
         self._graph_pool = None
         self._tile_keys: set = set()     # what the model's parts ask the tile source for
+        self._tiles_known = False        # an eager step with a prompt portion has run: the set is complete
         # a mixed step's bucket is captured once this many steps have fallen into it
         self.capture_after = 2
         # the token each request's last step sampled, by state slot (slot 0: padded rows)
@@ -540,6 +541,8 @@ class StepFunction:
         the requests' lengths to the caller (the scheduler does it when it takes the tokens)."""
         ctx, ids, want = self.layout(entries)
         out = self.model.forward(self.model.embed(ids), ctx)
+        if not ctx.host.decode_only:
+            self._tiles_known = True
         logits = self.model.logits(out, want) if want.numel() else None
         if commit:
             for e in entries:
@@ -655,12 +658,12 @@ class StepFunction:
         wanted row per entry at most), capturing it when its bucket has been met
         ``capture_after`` times; None while it is not worth a capture, or if no bucket fits."""
         total = sum(len(e.tokens) for e in entries)
-        if any(len(e.want) > 1 for e in entries) or not self._tile_keys:
+        if any(len(e.want) > 1 for e in entries) or not self._tiles_known:
             return None
         tokens = self._bucket(total, STEP_TOKEN_BUCKETS)
         # a step that does not fill its bucket needs one more sequence: the dummy one
         seqs = self._bucket(len(entries) + (0 if tokens == total else 1), STEP_SEQ_BUCKETS)
-        if tokens is None or seqs is None or tokens > self.cache.max_len:
+        if tokens is None or seqs is None:
             return None
         key = (tokens, seqs)
         g = self._step_graphs.get(key)
@@ -677,6 +680,41 @@ class StepFunction:
         elif not self._tile_keys <= set(g.tile_keys) | {"singles"}:
             return None          # a part asked for tiles the capture did not know: run eagerly
         return g
+
+    def capture_shapes(self, decode_rows: int, step_tokens: int, step_seqs: int) -> tuple[int, int]:
+        """Record ahead of time what serving would record at first use: the decode step of every
+        bucket up to ``decode_rows`` sequences, and the mixed step of every (token, sequence)
+        bucket a step of at most ``step_tokens`` tokens and ``step_seqs`` sequences can fall
+        into. Mixed shapes need to know which tile lists the model's parts ask for, which the
+        first eager step with a prompt portion tells; without one they are left for later.
+        Returns how many decode and mixed shapes are now recorded."""
+        for b in DECODE_BUCKETS:
+            bucket = min(b, max(1, self.cache.max_requests))
+            if bucket not in self._graphs:
+                self.decode_graph(bucket)
+            if b >= decode_rows:
+                break
+        if self._tiles_known:
+            top_tokens = self._bucket(step_tokens, STEP_TOKEN_BUCKETS)
+            top_seqs = self._bucket(step_seqs + 1, STEP_SEQ_BUCKETS)      # + the dummy sequence
+            below = 0
+            for seqs in STEP_SEQ_BUCKETS:
+                if top_seqs is None or seqs > top_seqs:
+                    break
+                for tokens in STEP_TOKEN_BUCKETS:
+                    if top_tokens is None or tokens > top_tokens:
+                        break
+                    # a step of this sequence bucket has more than `below` sequences (one of
+                    # them may be the dummy), each with a token
+                    if tokens < below or (tokens, seqs) in self._step_graphs:
+                        continue
+                    g = _StepGraph(self, tokens, seqs, self._tile_keys)
+                    if self._graph_pool is None:
+                        self._graph_pool = torch.cuda.graph_pool_handle()
+                    g.capture(self.model, self._graph_pool)
+                    self._step_graphs[(tokens, seqs)] = g
+                below = seqs
+        return len(self._graphs), len(self._step_graphs)
 
     def launch_step_graph(self, g: "_StepGraph", entries: list[StepEntry], sampling_rows: list[tuple],
                           fed_on_device: list[bool], reserved: bool = False) -> DecodeHandle:

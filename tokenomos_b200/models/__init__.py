@@ -16,7 +16,7 @@ import torch
 
 from tokenomos_b200.models.lfm3 import Lfm3
 from tokenomos_b200.parts import build_model
-from tokenomos_b200.parts.registry import Runtime
+from tokenomos_b200.parts.registry import Runtime, Tuning
 from tokenomos_b200.weights.checkpoint import Checkpoint, load_tensors
 
 ARCHS: dict[str, object] = {}
@@ -68,8 +68,8 @@ def load(path: str | Path, device: torch.device | str = "cuda", arch: Configured
     conf = arch or configure(path)
     ckpt = Checkpoint(path)
     spec = conf.arch.declare(conf.config, ckpt.names())
-    rt = Runtime(conf.work, torch.device(device))
-    tensors = load_tensors(ckpt, spec.tensor_decls(), rt.dtype, rt.device)
+    rt = Runtime(conf.work, torch.device(device), Tuning.for_device(device))
+    tensors = load_tensors(ckpt, spec.tensor_decls(), rt.dtype, rt.device, spec.scope)
     model = build_model(spec, tensors, rt)
     model.config = conf.config
     model.spec = spec
@@ -79,7 +79,7 @@ def load(path: str | Path, device: torch.device | str = "cuda", arch: Configured
 def from_tensors(conf: Configured, tensors: dict, device: torch.device | str = "cuda"):
     """A model from tensors already in memory (the random-weights mode without a folder)."""
     spec = conf.arch.declare(conf.config, tensors.keys())
-    rt = Runtime(conf.work, torch.device(device))
+    rt = Runtime(conf.work, torch.device(device), Tuning.for_device(device))
     model = build_model(spec, tensors, rt)
     model.config = conf.config
     model.spec = spec

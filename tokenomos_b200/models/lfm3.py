@@ -104,4 +104,7 @@ class Lfm3:
             final_norm=norm(f"{root}embedding_norm", d),
             head=None if cfg.tie_embedding else TensorDecl("lm_head.weight", (cfg.vocab_size, d),
                                                            ROLE_MATRIX),
+            # a vision-language folder also stores its vision tower and projector, and a tied
+            # checkpoint may store a copy of the head: neither belongs to the text stack
+            scope=(root,) if cfg.tie_embedding else (root, "lm_head."),
         )

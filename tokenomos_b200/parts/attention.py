@@ -15,9 +15,9 @@ import os
 import torch
 
 from tokenomos_b200 import ops
-from tokenomos_b200.parts.contract import PagedKV, SharedState, StepContext, WindowKV
+from tokenomos_b200.parts.contract import HeadLayout, PagedKV, SharedState, StepContext, WindowKV
 from tokenomos_b200.parts.linear import Linear
-from tokenomos_b200.parts.registry import Runtime, builder_of, register
+from tokenomos_b200.parts.registry import DEFAULT_TUNING, Runtime, Tuning, builder_of, register
 
 
 class Attention:
@@ -25,7 +25,7 @@ class Attention:
                  eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
                  window: int | None = None, scale: float | None = None,
                  gate: Linear | None = None, kv_source: int | None = None,
-                 gate_fused: bool = False):
+                 gate_fused: bool = False, tuning: Tuning = DEFAULT_TUNING):
         """``gate``: the per-head gate's projection as a part of its own; ``gate_fused``: its rows
         are the last of ``qkv``'s instead (after q, k, v, then zero rows up to a multiple of 8), so
         that one product yields both."""
@@ -34,6 +34,9 @@ class Attention:
         self.qkv, self.o, self.gate = qkv, o, gate
         self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
         self.rope = rope
+        self.tuning = tuning
+        # this part reads the batch from device tensors only; its position part must as well
+        self.capture_safe = bool(getattr(rope, "capture_safe", False))
         self.eps = float(eps)
         self.q_norm = q_norm.float().contiguous() if q_norm is not None else None
         self.k_norm = k_norm.float().contiguous() if k_norm is not None else None
@@ -47,10 +50,8 @@ class Attention:
             raise ValueError("attention: the gate is either fused into qkv or a projection of its own")
         if qkv.out_features != self.qkv_width + (-(-heads // 8) * 8 if gate_fused else 0):
             raise ValueError("attention: the fused projection does not match the head counts")
-        if rope.dim != head_dim:
-            # the kernel rotates the first `dim` dims and passes the rest through
-            if rope.dim > head_dim:
-                raise ValueError("attention: rotary width above the head size")
+        self.head_layout = HeadLayout(heads, own_kv, head_dim, self.q_norm,
+                                      self.k_norm if own_kv else None, self.eps)
 
     def state_specs(self) -> dict:
         if self.kv_source is not None:
@@ -78,11 +79,9 @@ class Attention:
         given): q/k norm, rotation, cache write, attention over the cache."""
         pool = ctx.states[(call, "kv")]
         table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
-        own_kv = 0 if self.kv_source is not None else self.kv_heads
-        q = ops.qk_norm_rope_write(
-            qkv, pool if own_kv else None, self.q_norm, self.k_norm if own_kv else None,
-            self.eps, self.rope.tables(ctx), ctx.positions, ctx.tok_seq,
-            table if own_kv else None, self.heads, own_kv, self.head_dim, ctx.page_size)
+        own_kv = self.head_layout.kv_heads
+        q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
+                                table if own_kv else None)
         if ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
             return self._attend_mma(q, pool, table, ctx, out)
         rows = ops.attention_rows()
@@ -98,26 +97,18 @@ class Attention:
 
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
     prefill_tc = os.environ.get("TOKENOMOS_B200_ATTN_TC", "1") != "0"
-    # How the decode kernel splits a token's keys over CTAs, measured on a B200 at batch 1 to 64
-    # and 512 to 32,768 cached positions: about DECODE_KEYS keys a CTA, counted on the longest
-    # sequence the engine allows, which is all a captured step knows (in practice a CTA then
-    # reads about half as many); more CTAs than that gives while fewer than DECODE_FILL of them
-    # would be on the GPU (never below DECODE_MIN_KEYS keys a CTA); never more than DECODE_CTAS
-    # CTAs (three fit on an SM by shared memory, and a few waves of them even out the last,
-    # partial one)
-    DECODE_KEYS = 1024
-    DECODE_FILL = 256
-    DECODE_MIN_KEYS = 128
-    DECODE_CTAS = 4 * 444
 
-    @classmethod
-    def decode_splits(cls, rows: int, kv_heads: int, longest: int) -> int:
+    @staticmethod
+    def decode_splits(rows: int, kv_heads: int, longest: int, tuning: Tuning = DEFAULT_TUNING) -> int:
         """Ways to split each decoded token's keys over CTAs, for ``rows`` tokens whose sequences
-        hold at most ``longest`` positions (see the constants above)."""
+        hold at most ``longest`` positions, which is all a captured step knows (in practice a CTA
+        then reads about half as many keys as the rule aims at). The thresholds are ``Tuning``'s,
+        measured at batch 1 to 64 and 512 to 32,768 cached positions."""
         per_split = max(1, rows * kv_heads)                 # CTAs one split puts on the GPU
-        by_keys = -(-longest // cls.DECODE_KEYS)
-        to_fill = min(-(-cls.DECODE_FILL // per_split), -(-longest // cls.DECODE_MIN_KEYS))
-        return max(1, min(-(-cls.DECODE_CTAS // per_split), max(by_keys, to_fill)))
+        by_keys = -(-longest // tuning.decode_keys)
+        to_fill = min(-(-tuning.decode_fill // per_split), -(-longest // tuning.decode_min_keys))
+        most = tuning.decode_ctas_per_sm * tuning.sm_count
+        return max(1, min(-(-most // per_split), max(by_keys, to_fill)))
 
     def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
@@ -142,7 +133,7 @@ class Attention:
             if self.window is not None:
                 longest = min(longest, self.window)
             rows = ctx.n_tokens if decode_only else singles.numel()
-            nsplit = self.decode_splits(rows, self.kv_heads, longest)
+            nsplit = self.decode_splits(rows, self.kv_heads, longest, self.tuning)
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
                                      self.window, self.scale, nsplit)
         return out
@@ -151,7 +142,9 @@ class Attention:
 @register("mixer", "attention")
 def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
     rope_spec = params["position"]
-    rope = builder_of("position", rope_spec["kind"])(rope_spec["params"], {}, rt)
+    # tensors whose role name starts with "position." belong to the position encoding
+    own = {k[len("position."):]: v for k, v in tensors.items() if k.startswith("position.")}
+    rope = builder_of("position", rope_spec["kind"])(rope_spec["params"], own, rt)
     source = params.get("kv_source")
     mats = [tensors["q"]] if source is not None else [tensors["q"], tensors["k"], tensors["v"]]
     gated = "gate" in tensors
@@ -162,6 +155,7 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
         pad = -g.shape[0] % 8
         mats.append(torch.cat((g, g.new_zeros(pad, g.shape[1]))) if pad else g)
     return Attention(
-        Linear.fused(mats), Linear(tensors["o"]), params["heads"], params["kv_heads"],
-        params["head_dim"], rope, params["eps"], tensors.get("q_norm"), tensors.get("k_norm"),
-        params.get("window"), params.get("scale"), None, source, gate_fused=gated)
+        Linear.fused(mats, tuning=rt.tuning), Linear(tensors["o"], tuning=rt.tuning), params["heads"],
+        params["kv_heads"], params["head_dim"], rope, params["eps"], tensors.get("q_norm"),
+        tensors.get("k_norm"), params.get("window"), params.get("scale"), None, source,
+        gate_fused=gated, tuning=rt.tuning)

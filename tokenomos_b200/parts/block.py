@@ -16,7 +16,7 @@ import torch
 from tokenomos_b200 import ops
 from tokenomos_b200.parts.contract import SharedState, StateKey, StateSpec, StepContext
 from tokenomos_b200.parts.linear import Linear
-from tokenomos_b200.parts.registry import register
+from tokenomos_b200.parts.registry import DEFAULT_TUNING, Tuning, register
 from tokenomos_b200.parts.spec import LayerCall
 
 
@@ -25,6 +25,10 @@ class PreNormBlock:
         self.mixer, self.ffn = mixer, ffn
         self.pre_mixer, self.pre_ffn = pre_mixer, pre_ffn
         self.post_mixer, self.post_ffn = post_mixer, post_ffn
+        # the arrangement itself launches nothing; it can be recorded if all its parts can
+        self.capture_safe = all(getattr(part, "capture_safe", False)
+                                for part in (mixer, ffn, pre_mixer, pre_ffn, post_mixer, post_ffn)
+                                if part is not None)
 
     def forward(self, h, residual, pending, ctx: StepContext, call: int):
         """``pending``: the previous block's post-norm still to apply to ``h`` before it joins
@@ -44,12 +48,12 @@ def build_prenorm(parts: dict) -> PreNormBlock:
 
 class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
-                 head: Linear | None):
+                 head: Linear | None, tuning: Tuning = DEFAULT_TUNING):
         self.embedding = embedding
         self.blocks = blocks
         self.order = list(order)
         self.final_norm = final_norm
-        self.head = head if head is not None else Linear(embedding)
+        self.head = head if head is not None else Linear(embedding, tuning=tuning)
         self.tied = head is None
         self.vocab, self.width = embedding.shape
         self.dtype = embedding.dtype
@@ -59,6 +63,22 @@ class Stack:
             if call.state_from is not None and not 0 <= call.state_from < i:
                 raise ValueError(f"layer list entry {i} reads the state of entry {call.state_from}, "
                                  "which must come earlier in the list")
+
+    @property
+    def capture_safe(self) -> bool:
+        """Whether a step of this model may be recorded as a CUDA graph: every block (and so
+        every part in it) and the final norm say so."""
+        return all(getattr(part, "capture_safe", False) for part in (*self.blocks, self.final_norm))
+
+    def not_capture_safe(self) -> list[str]:
+        """The kinds of the parts that keep this model from being recorded."""
+        out = []
+        for block in (*self.blocks, self.final_norm):
+            if not getattr(block, "capture_safe", False):
+                inner = [type(p).__name__ for p in vars(block).values()
+                         if hasattr(p, "forward") and not getattr(p, "capture_safe", False)]
+                out.extend(inner or [type(block).__name__])
+        return sorted(set(out))
 
     def state_specs(self) -> dict[StateKey, StateSpec]:
         """Per entry of the layer list, the memory its mixer asks for. An entry that reads

@@ -7,7 +7,8 @@ from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import Runtime, builder_of
 from tokenomos_b200.parts.spec import BlockSpec, ModelSpec, PartSpec
 
-# which registry family each slot of a block belongs to
+# the registry family of the slots the shipped arrangements use; a part in any other slot
+# names its family itself (``PartSpec.family``)
 SLOT_FAMILY = {
     "mixer": "mixer",
     "ffn": "feed_forward",
@@ -28,9 +29,10 @@ def _block(spec: BlockSpec, tensors: dict, rt: Runtime):
     for slot, part in spec.parts.items():
         if part is None:
             continue
-        family = SLOT_FAMILY.get(slot)
+        family = part.family or SLOT_FAMILY.get(slot)
         if family is None:
-            raise ValueError(f"block slot {slot!r} has no part family; slots: {sorted(SLOT_FAMILY)}")
+            raise ValueError(f"block slot {slot!r}: its part names no family, and the slot is not one "
+                             f"of {sorted(SLOT_FAMILY)}")
         parts[slot] = _part(family, part, tensors, rt)
     return builder_of("block", spec.kind)(parts)
 
@@ -39,5 +41,6 @@ def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
     """``tensors``: name -> tensor on ``rt.device``, kept as the weight loader keeps them."""
     blocks = [_block(b, tensors, rt) for b in spec.blocks]
     final_norm = _part("norm", spec.final_norm, tensors, rt)
-    head = Linear(tensors[spec.head.name]) if spec.head is not None else None
-    return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head)
+    head = Linear(tensors[spec.head.name], tuning=rt.tuning) if spec.head is not None else None
+    return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head,
+                 tuning=rt.tuning)

@@ -17,6 +17,21 @@ State memory comes in two shapes:
   on a cleared row.
 
 ``SharedState`` owns nothing: the call reads the state of another call of the layer list.
+
+A spec says what the cache manager has to do for it through three attributes, so a part may
+bring a spec class of its own: ``storage`` (``"paged"``, ``"slot"`` or ``"shared"``); for paged
+storage ``group`` (specs with equal groups share page numbers and block tables), ``window``
+(None: every position is kept) and ``page_shape(page_size)`` (the shape of one page); for slot
+storage ``shape`` and ``dtype``; for shared storage ``source`` and ``name``.
+
+Captured steps. With ``graphs=True`` the engine records a step's kernels once per shape and
+replays them with new contents in the same device buffers. A part can be recorded if its
+``forward`` launches the same kernels whatever the batch holds: it reads the batch only from the
+device tensors of the ``StepContext``, from ``ctx.tiles`` / ``ctx.singles`` and from the two host
+facts that are fixed for a shape, ``ctx.host.decode_only`` and ``ctx.host.longest``. Such a part
+sets ``capture_safe = True``. The per-sequence lists of ``ctx.host`` do not exist in a captured
+step and raise ``LayoutUnavailable`` there; a model with any part that is not ``capture_safe``
+is never captured (the engine runs its steps eagerly).
 """
 
 from __future__ import annotations
@@ -33,10 +48,15 @@ class PagedKV:
 
     kv_heads: int
     head_dim: int
+    storage = "paged"
+    window = None
 
     @property
     def group(self) -> tuple:
         return ("full",)
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (2, self.kv_heads, page_size, self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -46,10 +66,14 @@ class WindowKV:
     kv_heads: int
     head_dim: int
     window: int
+    storage = "paged"
 
     @property
     def group(self) -> tuple:
         return ("window", self.window)
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (2, self.kv_heads, page_size, self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -58,6 +82,7 @@ class SlotState:
 
     shape: tuple[int, ...]
     dtype: torch.dtype | None = None
+    storage = "slot"
 
 
 @dataclass(frozen=True)
@@ -66,22 +91,54 @@ class SharedState:
 
     source: int
     name: str = "kv"
+    storage = "shared"
 
 
+# the specs the framework's own parts use; any object with the attributes above is one too
 StateSpec = PagedKV | WindowKV | SlotState | SharedState
 # (index of the call in the model's layer list, name of the state within the part)
 StateKey = tuple[int, str]
 
 
-@dataclass
-class HostLayout:
-    """The step's layout as Python lists, for parts that plan launches on the host."""
+class LayoutUnavailable(RuntimeError):
+    """A part asked for the per-sequence host lists of a captured step, which has none."""
 
-    seq_lens: list[int]          # new tokens of each sequence in this step
-    seq_ctx: list[int]           # tokens of each sequence already in the cache
-    seq_slot: list[int]          # state row of each sequence
-    decode_only: bool            # every sequence brings exactly one token
-    longest: int = 0             # upper bound of (cached + new) tokens over the sequences
+
+class HostLayout:
+    """What the host knows of a step's layout. ``decode_only`` (every sequence brings exactly
+    one token) and ``longest`` (an upper bound of cached + new tokens over the sequences) are
+    always there. ``seq_lens`` (new tokens of each sequence), ``seq_ctx`` (tokens already cached)
+    and ``seq_slot`` (state rows) are Python lists for parts that plan launches on the host;
+    a captured step is recorded once for every batch of its shape, so there they raise."""
+
+    def __init__(self, seq_lens: list[int], seq_ctx: list[int], seq_slot: list[int],
+                 decode_only: bool, longest: int = 0, captured: bool = False):
+        self._lists = (seq_lens, seq_ctx, seq_slot)
+        self.decode_only, self.longest, self.captured = decode_only, longest, captured
+
+    @classmethod
+    def of_captured_step(cls, decode_only: bool, longest: int) -> "HostLayout":
+        return cls([], [], [], decode_only, longest, captured=True)
+
+    def _list(self, i: int, name: str) -> list[int]:
+        if self.captured:
+            raise LayoutUnavailable(
+                f"ctx.host.{name} does not exist in a captured step: the step is recorded once and "
+                "replayed for every batch of its shape. Read the layout from the context's device "
+                "tensors, or leave capture_safe unset on the part so that its model runs eagerly")
+        return self._lists[i]
+
+    @property
+    def seq_lens(self) -> list[int]:
+        return self._list(0, "seq_lens")
+
+    @property
+    def seq_ctx(self) -> list[int]:
+        return self._list(1, "seq_ctx")
+
+    @property
+    def seq_slot(self) -> list[int]:
+        return self._list(2, "seq_slot")
 
 
 @dataclass
@@ -151,8 +208,32 @@ class Norm(Protocol):
         ...
 
 
+@dataclass(frozen=True)
+class HeadLayout:
+    """What a position encoding needs to know of the projection it is handed: ``qkv`` rows hold
+    ``heads`` query heads, then ``kv_heads`` key heads, then ``kv_heads`` value heads, each of
+    ``head_dim`` (``kv_heads`` 0: queries only); the per-head norm weights (float32 [head_dim] or
+    None) and eps that go with them."""
+
+    heads: int
+    kv_heads: int
+    head_dim: int
+    q_norm: torch.Tensor | None
+    k_norm: torch.Tensor | None
+    eps: float
+
+
 @runtime_checkable
 class PositionEncoding(Protocol):
-    """Whatever turns positions into what a mixer applies to its queries and keys."""
+    """Owns everything between the fused q/k/v projection and attention over the cache: how
+    position enters the queries and keys, and the write of the new keys and values. Attention
+    calls it once per layer and step and knows nothing of rotations or tables."""
 
-    def tables(self, ctx: StepContext) -> object: ...
+    def encode_qk(self, qkv: torch.Tensor, ctx: StepContext, heads: HeadLayout,
+                  pool: torch.Tensor | None, table: torch.Tensor | None) -> torch.Tensor:
+        """``qkv`` [T, (H + 2 Hkv) D] (rows may be strided) -> the queries [T, H, D] as attention
+        will use them (normed, position applied), contiguous. The step's keys (treated likewise)
+        and values are written into ``pool`` [pages, 2, Hkv, P, D] at each token's position,
+        through ``table`` (the block table of the layer's cache group); ``pool`` None: the layer
+        has no keys of its own."""
+        ...

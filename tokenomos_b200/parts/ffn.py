@@ -15,6 +15,8 @@ RUN = 8
 
 
 class SwiGLU:
+    capture_safe = True
+
     def __init__(self, gate_up: Linear, down: Linear, run: int = 0):
         """``run`` 0: ``gate_up``'s rows are all gate rows, then all up rows. ``run`` 8: they
         alternate in runs of 8 channels, so that a decode CTA that owns 16 rows holds gate and up
@@ -27,7 +29,8 @@ class SwiGLU:
         w = self.gate_up.weight
         # (up to 8 rows: with 9 to 16 the library's product and the activation kernel are faster,
         # 0.91 ms a decode step at 16 rows against 1.00 ms)
-        if self.run == RUN and x.shape[0] <= 8 and ops.gemm_skinny_ok(x, w):
+        if (self.run == RUN and x.shape[0] <= self.gate_up.tuning.swiglu_fused_rows
+                and ops.gemm_skinny_ok(x, w)):
             act = ops.gemm_skinny(x, w, self.gate_up.bias, swiglu=True)
         else:
             act = ops.swiglu(self.gate_up(x), self.run)
@@ -45,6 +48,7 @@ def interleave_rows(gate: torch.Tensor, up: torch.Tensor, run: int) -> torch.Ten
 @register("feed_forward", "swiglu")
 def build_swiglu(params: dict, tensors: dict, rt: Runtime) -> SwiGLU:
     gate, up = tensors["gate"], tensors["up"]
+    down = Linear(tensors["down"], tuning=rt.tuning)
     if gate.dtype == torch.bfloat16 and gate.shape[0] % RUN == 0:
-        return SwiGLU(Linear(interleave_rows(gate, up, RUN)), Linear(tensors["down"]), RUN)
-    return SwiGLU(Linear.fused([gate, up]), Linear(tensors["down"]))
+        return SwiGLU(Linear(interleave_rows(gate, up, RUN), tuning=rt.tuning), down, RUN)
+    return SwiGLU(Linear.fused([gate, up], tuning=rt.tuning), down)

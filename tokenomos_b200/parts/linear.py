@@ -20,26 +20,30 @@ import torch
 import torch.nn.functional as F
 
 from tokenomos_b200 import ops
+from tokenomos_b200.parts.registry import DEFAULT_TUNING, Tuning
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None):
-        """``weight`` [out, in] in the work dtype (or float32); ``bias`` float32 [out] or None."""
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                 tuning: Tuning = DEFAULT_TUNING):
+        """``weight`` [out, in] in the work dtype (or float32); ``bias`` float32 [out] or None;
+        ``tuning``: the thresholds ``route`` picks kernels by."""
         self.weight = weight.contiguous()
-        self.bias = bias
+        self.bias = bias.float().contiguous() if bias is not None else None
         self.out_features, self.in_features = weight.shape
-        self._bias_lp = None
-        if bias is not None and weight.dtype == torch.bfloat16:
-            self._bias_lp = bias.to(torch.bfloat16)
+        self.tuning = tuning
+        # which route took how many products (tests read it to see that every branch ran)
+        self.routed: dict[str, int] = {}
 
     @classmethod
-    def fused(cls, weights: list[torch.Tensor], biases: list[torch.Tensor | None] | None = None):
+    def fused(cls, weights: list[torch.Tensor], biases: list[torch.Tensor | None] | None = None,
+              tuning: Tuning = DEFAULT_TUNING):
         """One projection from several that read the same input, outputs side by side."""
         biases = biases or [None] * len(weights)
         if any(b is not None for b in biases) and not all(b is not None for b in biases):
             raise ValueError("fused projection: either every part has a bias or none")
         bias = torch.cat(biases) if biases[0] is not None else None
-        return cls(torch.cat(weights, dim=0), bias)
+        return cls(torch.cat(weights, dim=0), bias, tuning)
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         w = self.weight
@@ -52,36 +56,40 @@ class Linear:
         if not x.is_cuda:
             raise ops.KernelError("Linear: CUDA tensors only (there is no CPU path)")
         route = self.route(x)
+        self.routed[route] = self.routed.get(route, 0) + 1
         if route == "tc":
             return ops.gemm_tc(x, w, self.bias, out_dtype)
         if route == "skinny":
             return ops.gemm_skinny(x, w, self.bias, out_dtype)
-        if out_dtype == torch.float32:
-            return self._float_out(x)
-        if self.in_features % 8 or (x.stride(0) % 8 and x.shape[0] > 1):
+        if route == "simt":
             return ops.gemm(x, w, self.bias, out_dtype or x.dtype)
-        return F.linear(x, w, self._bias_lp)
+        # the library's product has no 32-bit bias: the bias is added to the 32-bit result and
+        # the sum rounded once, as every other route does
+        if out_dtype == torch.float32 or self.bias is not None:
+            y = torch.mm(x, w.t(), out_dtype=torch.float32)
+            if self.bias is not None:
+                y += self.bias
+            return y if out_dtype == torch.float32 else y.to(x.dtype)
+        return F.linear(x, w)
 
     def route(self, x: torch.Tensor) -> str:
-        """Which kernel takes ``x`` [M, in]: measured on a B200 with 2048- to 8192-wide matrices
-        in CUDA graphs, the register-streaming kernel is the fastest up to 8 rows (and up to 16
-        for matrices of a few thousand rows), the TMA + tcgen05 kernel for very tall matrices
-        (the head) from 5 to 64 rows, the library elsewhere."""
-        m, n = x.shape[0], self.out_features
-        if m > 64:
-            return "library"             # no slicing, no checks: prompt portions come here
-        if not ops.gemm_skinny_ok(x[:1], self.weight):
-            return "library"
-        if m <= 4:
+        """Which kernel takes ``x`` [M, in] (thresholds: ``Tuning``): the register-streaming
+        kernel for a few rows, the TMA + tcgen05 kernel for very tall matrices (the head) and for
+        deep ones (a down projection) at small batches, the library elsewhere; the CUDA-core
+        kernel for shapes the others refuse."""
+        t, m, n, k = self.tuning, x.shape[0], self.out_features, self.in_features
+        if k % 8 or x.stride(1) != 1 or (x.stride(0) % 8 and m > 1) or x.data_ptr() % 16:
+            return "simt"                # no 16-byte rows: neither the library nor TMA takes it
+        if m > max(t.tc_tall_rows, t.tc_deep_rows, t.skinny_small_rows):
+            return "library"             # no further checks: prompt portions come here
+        skinny_ok = ops.gemm_skinny_ok(x[:1], self.weight)
+        if skinny_ok and m <= t.skinny_tall_rows:
             return "skinny"              # the head too: 0.67 ms a decode step at one row against 0.70
-        if n >= 32768 and m <= 64:
+        if n >= t.tc_tall_n and m <= t.tc_tall_rows and ops.gemm_tc_ok(x, self.weight):
             return "tc"
-        if m <= 8 or (m <= 16 and n <= 4096):
+        if skinny_ok and (m <= t.skinny_rows or (m <= t.skinny_small_rows and n <= t.skinny_small_n
+                                                 and k < t.tc_deep_k)):
             return "skinny"
+        if k >= t.tc_deep_k and t.skinny_rows < m <= t.tc_deep_rows and ops.gemm_tc_ok(x, self.weight):
+            return "tc"
         return "library"
-
-    def _float_out(self, x: torch.Tensor) -> torch.Tensor:
-        """16-bit operands, 32-bit result (the head: logits are not rounded to 16-bit)."""
-        if self.in_features % 8 == 0 and self.bias is None and x.is_contiguous():
-            return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
-        return ops.gemm(x, self.weight, self.bias, torch.float32)

@@ -15,6 +15,8 @@ from tokenomos_b200.parts.registry import Runtime, register
 
 
 class RMSNorm:
+    capture_safe = True
+
     def __init__(self, weight: torch.Tensor, eps: float):
         self.weight = weight.float().contiguous()
         self.eps = float(eps)

@@ -14,12 +14,64 @@ import torch
 
 
 @dataclass(frozen=True)
+class Tuning:
+    """Thresholds that pick between kernels that compute the same thing. They change speed,
+    never results beyond rounding, and they belong to a device and a range of sizes, not to a
+    part: the defaults were measured on a B200 (148 SMs) with 1,024- to 8,192-wide layers, in
+    CUDA graphs, weights cycled beyond L2. ``for_device`` reads the SM count of another GPU.
+
+    Dense products of 16-bit matrices, by rows of the input (``Linear.route``):
+    ``skinny_rows``: up to here the register-streaming kernel, for any matrix;
+    ``skinny_small_rows`` / ``skinny_small_n``: up to that many rows for matrices of at most that
+    many output rows; ``tc_tall_n`` / ``tc_tall_rows`` / ``tc_tall_from``: matrices at least that
+    tall (a vocabulary head) go to the TMA + tcgen05 kernel from ``tc_tall_from`` to
+    ``tc_tall_rows`` rows; ``tc_deep_k`` / ``tc_deep_rows``: matrices with an inner size of at
+    least ``tc_deep_k`` (a feed-forward's down projection) go there above the skinny range up to
+    ``tc_deep_rows`` rows; everything else is the library's.
+    ``swiglu_fused_rows``: up to here gate/up and the activation are one kernel.
+    Decode attention (``Attention.decode_splits``): about ``decode_keys`` keys of the longest
+    allowed sequence per CTA; more CTAs than that gives while fewer than ``decode_fill`` would be
+    on the GPU (never below ``decode_min_keys`` keys each); never more than
+    ``decode_ctas_per_sm`` CTAs per SM (three fit by shared memory, and a few waves of them even
+    out the last, partial one).
+    ``conv_tile``: tokens a conv tile walks in order (a 2,048-token portion of 2,048 channels:
+    18 us at 8, 33 us at 32)."""
+
+    sm_count: int = 148
+    skinny_rows: int = 8
+    skinny_small_rows: int = 16
+    skinny_small_n: int = 4096
+    skinny_tall_rows: int = 4
+    tc_tall_n: int = 32768
+    tc_tall_rows: int = 64
+    tc_deep_k: int = 8192
+    tc_deep_rows: int = 64
+    swiglu_fused_rows: int = 8
+    decode_keys: int = 1024
+    decode_fill: int = 256
+    decode_min_keys: int = 128
+    decode_ctas_per_sm: int = 12
+    conv_tile: int = 8
+
+    @classmethod
+    def for_device(cls, device) -> "Tuning":
+        device = torch.device(device)
+        if device.type == "cuda" and torch.cuda.is_available():
+            return cls(sm_count=torch.cuda.get_device_properties(device).multi_processor_count)
+        return cls()
+
+
+DEFAULT_TUNING = Tuning()
+
+
+@dataclass(frozen=True)
 class Runtime:
     """What every part is built for: the work dtype (storage of activations, matrices and
-    caches) and the device."""
+    caches), the device, and the device's kernel-choice thresholds."""
 
     dtype: torch.dtype
     device: torch.device
+    tuning: Tuning = DEFAULT_TUNING
 
 
 Builder = Callable[[dict, dict, Runtime], object]

@@ -3,18 +3,23 @@
 Frequencies ``inv_i = theta ** (-2 i / dim)`` for ``i < angles``, zero for the rest of
 ``dim / 2`` (a zero-tail partial rotation: those dims pass through with cos 1, sin 0), computed
 once on the CPU in float32; the angle of a token is ``float(position) * inv_i`` and cos / sin are
-rounded to the storage type (Tokenomos models/blocks/rope.py:33-35,51-59). The kernels compute
-cos and sin from ``inv_freq`` and the positions, so the part only owns the frequency table.
+rounded to the storage type (Tokenomos models/blocks/rope.py:33-35,51-59). One kernel norms the
+q and k heads, rotates them by angles it computes from ``inv_freq`` and the positions, and
+writes the new keys and values into the cache.
 """
 
 from __future__ import annotations
 
 import torch
 
+from tokenomos_b200 import ops
+from tokenomos_b200.parts.contract import HeadLayout, StepContext
 from tokenomos_b200.parts.registry import Runtime, register
 
 
 class Rope:
+    capture_safe = True
+
     def __init__(self, head_dim: int, angles: int, theta: float, device, dim: int | None = None):
         dim = dim or head_dim
         if dim % 2 or dim > head_dim:
@@ -27,9 +32,14 @@ class Rope:
         self.inv_freq = inv.to(device).contiguous()
         self.dim = dim
 
-    def tables(self, ctx) -> torch.Tensor:
-        """What the attention kernels take: the frequency table (positions come from ``ctx``)."""
-        return self.inv_freq
+    def encode_qk(self, qkv: torch.Tensor, ctx: StepContext, heads: HeadLayout,
+                  pool: torch.Tensor | None, table: torch.Tensor | None) -> torch.Tensor:
+        if self.dim > heads.head_dim:
+            raise ValueError(f"rotary width {self.dim} above the head size {heads.head_dim}")
+        return ops.qk_norm_rope_write(
+            qkv, pool, heads.q_norm, heads.k_norm if heads.kv_heads else None, heads.eps,
+            self.inv_freq, ctx.positions, ctx.tok_seq, table, heads.heads, heads.kv_heads,
+            heads.head_dim, ctx.page_size)
 
 
 @register("position", "rope")

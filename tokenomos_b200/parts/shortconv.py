@@ -12,17 +12,14 @@ from tokenomos_b200.parts.contract import SlotState, StepContext
 from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import Runtime, register
 
-# tokens a conv tile walks in order; any value >= width - 1 is correct. Short tiles give the
-# kernel more threads (a 2,048-token portion of 2,048 channels: 18 us at 8, 33 us at 32)
-CONV_TILE = 8
-
-
 # channels per run when the in-projection's rows hold B, C and X of the same channels in turn
 # (what the decode kernel's epilogue needs side by side)
 RUN = 8
 
 
 class ShortConv:
+    capture_safe = True
+
     def __init__(self, in_proj: Linear, out_proj: Linear, conv: torch.Tensor,
                  conv_bias: torch.Tensor | None = None, run: int = 0):
         """``conv`` [dim, width]: tap ``width - 1`` multiplies the current token. ``run`` 0:
@@ -35,7 +32,8 @@ class ShortConv:
         self.dim, self.width = conv.shape
         if in_proj.out_features != 3 * self.dim or out_proj.in_features != self.dim:
             raise ValueError("short conv: projections do not match the conv's channel count")
-        self.tile = max(CONV_TILE, self.width - 1)
+        # tokens a conv tile walks in order; any value >= width - 1 is correct
+        self.tile = max(in_proj.tuning.conv_tile, self.width - 1)
 
     def state_specs(self) -> dict:
         return {"conv": SlotState((self.width - 1, self.dim))}
@@ -76,6 +74,6 @@ def build_short_conv(params: dict, tensors: dict, rt: Runtime) -> ShortConv:
         w_in = interleave_bcx(w_in, RUN)
         b_in = interleave_bcx(b_in, RUN) if b_in is not None else None
     return ShortConv(
-        Linear(w_in, b_in),
-        Linear(tensors["out_proj"], tensors.get("out_proj_bias")),
+        Linear(w_in, b_in, rt.tuning),
+        Linear(tensors["out_proj"], tensors.get("out_proj_bias"), rt.tuning),
         conv, tensors.get("conv_bias"), run)

@@ -33,11 +33,16 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class PartSpec:
-    """One part: the registry ``kind``, its sizes and constants, and its tensors by role name."""
+    """One part: the registry ``kind``, its sizes and constants, and its tensors by role name.
+    ``family``: the registry the kind is looked up in (``mixer``, ``feed_forward``, ``norm``,
+    ``position``); None: the family the slot's name implies (``parts.build.SLOT_FAMILY``), which
+    covers the slots of the arrangements that ship. An arrangement with slots of its own (a
+    second mixer, an extra branch) names the family on each of their parts."""
 
     kind: str
     params: dict = field(default_factory=dict)
     tensors: dict[str, TensorDecl] = field(default_factory=dict)
+    family: str | None = None
 
 
 @dataclass(frozen=True)
@@ -66,6 +71,10 @@ class ModelSpec:
     order: tuple[LayerCall, ...]
     final_norm: PartSpec
     head: TensorDecl | None  # None: the head is the embedding (tied)
+    # name prefixes the model owns in its folder: a stored tensor under one of them that the
+    # model does not declare is an error; tensors elsewhere (another tower of a multimodal
+    # folder, a stored copy of a tied head) are not this model's business. Empty: every name.
+    scope: tuple[str, ...] = ()
 
     def tensor_decls(self) -> list[TensorDecl]:
         """Every tensor the model reads, in a fixed order (the order random weights are drawn)."""

@@ -5,10 +5,9 @@ by tensor name (Tokenomos models/load/checkpoint.py:138-174 reads the same two l
 anything and raises one ``WeightError`` that lists every missing tensor, every unexpected
 tensor and every wrong shape. How tensors are kept:
 
-- matrices and embeddings in the work dtype (bfloat16 or float32); a matrix *stored* in
-  32-bit stays 32-bit even in a bfloat16 model when ``keep_float32`` is set on its declaration's
-  role (vectors always are):
-- norm weights, biases and conv taps in float32 (a 16-bit value widens exactly);
+- matrices and embeddings in the work dtype (bfloat16 or float32);
+- norm weights, biases and conv taps in float32: a value stored in 32-bit stays 32-bit, a
+  16-bit one widens exactly;
 - integer tables as int32.
 """
 
@@ -74,13 +73,15 @@ class Checkpoint:
         return self._file(self.weight_map[name]).get_tensor(name)
 
 
-def check(source, decls: list[TensorDecl]) -> None:
-    """Raise ``WeightError`` unless ``source`` (``names()``, ``shape(name)``) holds exactly the
-    declared tensors (optional ones may be absent) with the declared shapes."""
+def check(source, decls: list[TensorDecl], scope: tuple[str, ...] = ()) -> None:
+    """Raise ``WeightError`` unless ``source`` (``names()``, ``shape(name)``) holds the declared
+    tensors (optional ones may be absent) with the declared shapes, and nothing undeclared
+    under the name prefixes in ``scope`` (empty: under any name)."""
     have = set(source.names())
     declared = {d.name: d for d in decls}
     missing = sorted(n for n, d in declared.items() if n not in have and not d.optional)
-    unexpected = sorted(have - set(declared))
+    unexpected = sorted(n for n in have - set(declared)
+                        if not scope or any(n.startswith(prefix) for prefix in scope))
     wrong = []
     for n, d in declared.items():
         if n in have:
@@ -109,9 +110,10 @@ def kept_dtype(decl: TensorDecl, stored: torch.dtype, work: torch.dtype) -> torc
     raise ValueError(f"tensor role {decl.role!r}")
 
 
-def load_tensors(source, decls: list[TensorDecl], work: torch.dtype, device) -> dict:
+def load_tensors(source, decls: list[TensorDecl], work: torch.dtype, device,
+                 scope: tuple[str, ...] = ()) -> dict:
     """name -> tensor on ``device`` for every declared tensor ``source`` holds, after ``check``."""
-    check(source, decls)
+    check(source, decls, scope)
     out = {}
     for d in decls:
         if not source.has(d.name):
