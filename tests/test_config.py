@@ -104,3 +104,24 @@ def test_declaration_lists_layers_by_config():
     assert [c.block for c in spec.order] == list(range(6))
     names = {d.name for d in spec.tensor_decls()}
     assert "model.layers.0.conv.conv.bias" in names and "model.layers.1.self_attn.q_norm.weight" in names
+
+
+@pytest.mark.parametrize("change, needle", [({"conv_L_cache": 9}, "9 taps"),
+                                            ({"head_dim": 272}, "head size of 272"),
+                                            ({"hidden_size": 51264, "num_attention_heads": 4, "head_dim": 16},
+                                             "width of 51264")])
+def test_sizes_no_kernel_takes_are_refused_when_the_model_is_built(change, needle):
+    """What the configuration allows and a kernel does not take is refused when the model is put
+    together (``models.load`` / ``from_tensors``), with the limit named, not at the first step."""
+    import torch
+
+    from conftest import TINY_A
+    from tokenomos_b200 import models
+    from tokenomos_b200.weights import random_tensors
+
+    raw = dict(TINY_A, **change)
+    conf = models.Configured(models.ARCHS["Lfm3ForCausalLM"], Lfm3Config.from_dict(raw), torch.float32)
+    decls = conf.arch.declare(conf.config).tensor_decls()
+    tensors = {d.name: torch.zeros(d.shape, device="meta") for d in decls if not d.optional}
+    with pytest.raises(ValueError, match=needle):
+        models.from_tensors(conf, tensors, device="meta")

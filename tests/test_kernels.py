@@ -486,6 +486,25 @@ def test_sample_greedy_is_the_first_maximum():
     assert got.tolist() == [17, V - 1, 0, int(logits[3].argmax()), int(logits[4].argmax())]
 
 
+def test_sample_row_without_a_finite_logit_gives_a_valid_token_and_is_reported():
+    """A row of NaN (or of -inf) has no best token. The sampler must not hand out the sentinel it
+    starts from (2**31 - 1, which the next step's embedding lookup would clamp silently): it
+    answers token 0, greedy or sampled, and leaves 1 + the row in a word the host reads."""
+    from tokenomos_b200 import ops
+    V = 300
+    ops.sample_status()
+    logits = torch.randn(4, V)
+    logits[1] = float("nan")
+    logits[3] = float("-inf")
+    got = sample_rows(logits.cuda(), [(0.0, 1.0, 0, 0.0, 0, 0), (0.0, 1.0, 0, 0.0, 0, 0),
+                                      (0.9, 0.8, 5, 0.0, 3, 1), (0.9, 0.8, 5, 0.0, 3, 1)])
+    assert got[0] == int(logits[0].argmax()) and got[1] == 0 and got[3] == 0 and 0 <= got[2] < V
+    assert ops.sample_status() in (2, 4)       # 1 + one of the two bad rows (the first to report)
+    assert ops.sample_status() == 0            # reading resets it
+    sample_rows(torch.randn(2, V).cuda(), [(0.0, 1.0, 0, 0.0, 0, 0)] * 2)
+    assert ops.sample_status() == 0
+
+
 @pytest.mark.parametrize("params", [(0.8, 1.0, 0, 0.0), (1.3, 1.0, 7, 0.0), (1.0, 0.6, 0, 0.0),
                                     (1.0, 1.0, 0, 0.15), (0.7, 0.8, 12, 0.02)])
 def test_sample_distribution(params):

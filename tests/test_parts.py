@@ -271,3 +271,31 @@ def test_a_part_that_reads_host_lists_in_a_captured_step_fails_loudly(tmp_path):
             llm.generate([[1, 2, 3]], SamplingParams(max_tokens=4))
         assert isinstance(err.value.__cause__, LayoutUnavailable)
         assert "ctx.host.seq_lens does not exist in a captured step" in str(err.value.__cause__)
+
+
+def test_linear_adds_its_bias_in_32_bit_on_every_route():
+    """A projection's bias is float32 and joins the 32-bit sum before the one rounding, whichever
+    kernel ``route`` picks for the row count (the weight-streaming kernel, the tcgen05 kernel,
+    the library). Inputs that make the difference visible: the product cancels the bias's
+    16-bit part exactly, so the result is the part of the bias that bfloat16 cannot hold; a
+    route that rounds the bias first gives zero instead."""
+    from tokenomos_b200.parts.linear import Linear
+
+    N, K = 64, 8192
+    g = torch.Generator().manual_seed(3)
+    bias = (1.0 + 0.5 * torch.rand(N, generator=g)).float()
+    coarse = bias.to(torch.bfloat16)
+    w = torch.zeros(N, K, dtype=torch.bfloat16)
+    w[:, 0] = -coarse                                  # x = e_0 makes the product -bf16(bias)
+    lin = Linear(w.cuda(), bias.cuda())
+    want = (bias.double() - coarse.double())
+    assert want.abs().min().item() > 0
+    for rows, route in ((1, "skinny"), (8, "skinny"), (16, "tc"), (65, "library")):
+        x = torch.zeros(rows, K, dtype=torch.bfloat16)
+        x[:, 0] = 1.0
+        got = lin(x.cuda()).double().cpu()
+        assert lin.routed.get(route, 0) > 0, (rows, route, lin.routed)
+        err = (got - want[None]).abs().max().item()
+        assert err <= 2 ** -8 * want.abs().max().item(), (rows, route, err)
+        got32 = lin(x.cuda(), out_dtype=torch.float32).double().cpu()
+        assert (got32 - want[None]).abs().max().item() <= 1e-6, (rows, route)

@@ -13,6 +13,7 @@
 // Masking, scale, rounding of P to bfloat16 and the unrounded row sum follow the generic kernel
 // (Tokenomos kernels/attention/paged.py:67-76,150,267; models/blocks/attention.py:31-40,173).
 // Keys past a query's position are never read: their shared-memory rows are zero-filled.
+#include "no_alloc.h"
 #include <math.h>
 
 #include "paged_tiles.cuh"

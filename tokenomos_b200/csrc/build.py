@@ -35,7 +35,7 @@ def sources() -> list[Path]:
 
 
 def _headers() -> list[Path]:
-    return sorted(HERE.glob("*.cuh"))
+    return sorted(list(HERE.glob("*.cuh")) + list(HERE.glob("*.h")))
 
 
 def find_nvcc() -> str:

@@ -17,6 +17,9 @@
  *     array until the process exits.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress,
  *     with that device current). Make that first call before any stream capture begins.
+ *     Host threads: any thread may make it; if two threads make the first call on one device
+ *     at the same moment, both look the address up and store the same value, which is
+ *     harmless. After it, the entry point reads that value and nothing else of its own.
  *   - It calls no cudaMalloc, cudaFree or allocating library routine.
  *   - All calls share the one array, and it keeps what the last call left. Nothing in it needs
  *     to start at zero: every slot a call reads was written by that call's own first kernel.

@@ -121,6 +121,17 @@ __device__ void mass_count(const float* row, int V, float inv_t, float top, floa
 }
 }  // namespace
 
+// 0, or 1 + the first row whose logits held no finite value (all NaN or -inf): such a row has
+// no best token; the kernel answers token 0 for it and records the row here, and the host reads
+// the word where it reads the other kernels' error words (tk_sample_status).
+__device__ int g_sample_error = 0;
+
+__device__ __forceinline__ int valid_token(int tok, int row) {
+    if (tok != 0x7fffffff) return tok;
+    atomicCAS(&g_sample_error, 0, row + 1);
+    return 0;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
               const float* top_p, const int* top_k,
@@ -138,8 +149,9 @@ sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
     const float t = temp[r];
     if (t <= 0.f) {
         if (threadIdx.x == 0) {
-            out[r] = b.i;
-            if (scatter_out != nullptr) scatter_out[scatter_index[r]] = b.i;
+            const int tok = valid_token(b.i, r);
+            out[r] = tok;
+            if (scatter_out != nullptr) scatter_out[scatter_index[r]] = tok;
         }
         return;
     }
@@ -185,7 +197,7 @@ sample_kernel(const float* logits, int64_t stride, int V, const float* temp,
     });
     g = block_best(g, bred);
     if (threadIdx.x == 0) {
-        const int tok = g.i == 0x7fffffff ? b.i : g.i;
+        const int tok = valid_token(g.i == 0x7fffffff ? b.i : g.i, r);
         out[r] = tok;
         if (scatter_out != nullptr) scatter_out[scatter_index[r]] = tok;
     }
@@ -203,4 +215,13 @@ TK_API int tk_sample(const float* logits, int64_t stride, int rows, int V, const
                                                        seed, step, out, scatter_index, scatter_out);
     TK_CHECK_LAUNCH("sample");
     return 0;
+}
+
+// 0 if every sampled row since the last call had a finite logit; else 1 + the first row that had
+// none. Resets the word.
+TK_API int tk_sample_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_sample_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_sample_error, &zero, sizeof(int));
+    return v;
 }

@@ -155,6 +155,10 @@ class Engine:
             if where:
                 raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
                                    "the tokens of the steps since the last check are not to be trusted")
+        row = ops.sample_status()
+        if row:
+            raise RuntimeError(f"the sampler met a row of logits without a finite value (row {row - 1} of "
+                               "its step) and answered token 0: the model's weights or its cache hold NaN")
 
     def _finish(self, finished: list[Request]) -> list[Request]:
         if finished and self.scheduler.idle():

@@ -20,8 +20,16 @@ __all__ = [
     "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
     "attention_prefill_tc_status",
     "conv_gated", "conv_min_tile",
-    "gemm", "gemm_skinny", "gemm_skinny_conv", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "gather_rows_select",
+    "gemm", "gemm_skinny", "gemm_skinny_conv", "gemm_skinny_ok", "gemm_tc", "gemm_tc_ok", "gemm_tc_status", "sample", "sample_status", "gather_rows_select",
 ]
+
+
+# What the kernels take, so that a model that asks for more is refused when it is built and not
+# at its first step (the entry points check the same limits: conv.cu and gemm_skinny.cu, the row
+# that add_rmsnorm keeps in shared memory, attention_generic.cu's MAX_D, qk_rope.cu)
+CONV_WIDTHS = (2, 8)
+NORM_MAX_WIDTH = 51200
+ATTENTION_MAX_HEAD_DIM = 256
 
 
 def available() -> None:
@@ -447,6 +455,12 @@ def gemm_tc_status() -> int:
     """0, or where a tensor-core GEMM gave up waiting on a barrier since the last call (the
     kernels bound every wait instead of hanging)."""
     return _lib.call("tk_gemm_tc_status")
+
+
+def sample_status() -> int:
+    """0, or 1 + the first row since the last call whose logits held no finite value (the sampler
+    answered token 0 for it)."""
+    return _lib.call("tk_sample_status")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,

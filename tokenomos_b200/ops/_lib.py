@@ -49,6 +49,7 @@ _SIGNATURES = {
     "tk_gemm_skinny_tune": [I, I, I],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_gemm_tc_status": [],
+    "tk_sample_status": [],
     "tk_gemm_tc_split_mode": [I],
     "tk_gemm_tc_tune": [I, I, I],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
@@ -100,7 +101,7 @@ def calls() -> int:
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
-            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
+            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
 
 
 _fns: dict = {}

@@ -31,6 +31,9 @@ class Attention:
         that one product yields both."""
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
+        if head_dim > ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError(f"attention: a head size of {head_dim} is above the "
+                             f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
         self.qkv, self.o, self.gate = qkv, o, gate
         self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
         self.rope = rope

@@ -21,6 +21,9 @@ class RMSNorm:
         self.weight = weight.float().contiguous()
         self.eps = float(eps)
         self.width = weight.numel()
+        if self.width > ops.NORM_MAX_WIDTH:
+            raise ValueError(f"RMSNorm: a width of {self.width} is above the {ops.NORM_MAX_WIDTH} the "
+                             "norm kernel keeps in shared memory")
 
     def add_norm(self, x: torch.Tensor, residual: torch.Tensor | None, pre: "RMSNorm | None" = None):
         """``stream = residual + [pre](x)``; returns ``(norm(stream), stream)``."""

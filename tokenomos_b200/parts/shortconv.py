@@ -30,6 +30,9 @@ class ShortConv:
         self.conv = conv.float().contiguous()
         self.conv_bias = conv_bias.float().contiguous() if conv_bias is not None else None
         self.dim, self.width = conv.shape
+        lo, hi = ops.CONV_WIDTHS
+        if not lo <= self.width <= hi:
+            raise ValueError(f"short conv: {self.width} taps; the conv kernels take {lo} to {hi}")
         if in_proj.out_features != 3 * self.dim or out_proj.in_features != self.dim:
             raise ValueError("short conv: projections do not match the conv's channel count")
         # tokens a conv tile walks in order; any value >= width - 1 is correct
