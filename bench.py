@@ -391,7 +391,7 @@ def run_sweep(model, cfg, page: int, pk: dict) -> int:
     return 0
 
 
-def run_workload(name: str, page: int) -> int:
+def run_workload(name: str, page: int, trace_path: str | None = None) -> int:
     """A whole serving workload through ``LLM.generate`` (continuous batching: prompts are cut
     into portions under the token budget and run beside the decoding requests): wall-clock
     tokens per second, prompt and generated."""
@@ -411,13 +411,15 @@ def run_workload(name: str, page: int) -> int:
     vocab = w["config"]["vocab_size"]
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
     pages = sum(-(-(n + w["new_tokens"] + 1) // page) for n in lengths) + 2
+    t0 = time.perf_counter()
     llm = LLM(str(folder), work="bf16", slots=w["slots"], page=page, max_len=w["max_len"], pages=pages,
-              prefill_budget=w["budget"], graphs=True)
+              prefill_budget=w["budget"], graphs=True, warmup=True)
+    warmup_seconds = time.perf_counter() - t0
+    shapes_after_warmup = len(llm.engine.step_fn._step_graphs) + len(llm.engine.step_fn._graphs)
     clocks = Clocks()
     try:
-        llm.generate(prompts[:2], SamplingParams(max_tokens=4))          # warm-up: builds, library handles
-        # the first pass also captures the CUDA graphs of the step shapes the workload meets (a
-        # one-time cost per shape, like a compile); the second pass is the steady state
+        # the engine warmed up before serving (every step shape the budget allows is captured
+        # then); the first pass shows what is left of the start-up cost
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         llm.generate(prompts, SamplingParams(max_tokens=w["new_tokens"]))
@@ -435,6 +437,11 @@ def run_workload(name: str, page: int) -> int:
             torch.cuda.synchronize()
             passes.append(time.perf_counter() - t0)
         seconds = sorted(passes)[1]
+        if trace_path:
+            # one more pass with a record per step: kind, rows, tokens, bucket, host and device ms
+            llm.engine.trace_on()
+            llm.generate(prompts, SamplingParams(max_tokens=w["new_tokens"]))
+            Path(trace_path).write_text(json.dumps(llm.engine.trace_take()))
         steps_per_pass = (llm.engine.stats.steps - steps_before) // 3
         decode_per_pass = (llm.engine.stats.decode_steps - decode_before) // 3
         graph_per_pass = (llm.engine.stats.graph_steps - graph_before) // 3
@@ -450,6 +457,7 @@ def run_workload(name: str, page: int) -> int:
         "value": round((sum(lengths) + generated) / seconds, 1), "unit": "tokens/s",
         "generated_per_s": round(generated / seconds, 1), "seconds": round(seconds, 3),
         "passes_seconds": [round(t, 3) for t in passes], "first_pass_seconds": round(first_seconds, 3),
+        "warmup_seconds": round(warmup_seconds, 3), "shapes_after_warmup": shapes_after_warmup,
         "captured_step_shapes": len(llm_graphs), "graph_steps": graph_per_pass,
         "requests": w["requests"], "prompt_tokens": sum(lengths), "generated": generated,
         "steps": steps_per_pass, "decode_steps": decode_per_pass, "preemptions": stats.preemptions,
@@ -639,6 +647,8 @@ def main() -> int:
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--trace", default=None,
+                    help="--workload: write one JSON record per step of an extra pass to this file")
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
     args = ap.parse_args()
@@ -659,7 +669,7 @@ def main() -> int:
         profile_case(args.profile, args.layers, args.batch, args.ctx, args.steps, args.page)
         return 0
     if args.workload:
-        return run_workload(args.workload, args.page)
+        return run_workload(args.workload, args.page, args.trace)
     pk = peaks()
     import tempfile
 

@@ -139,6 +139,40 @@ def test_warmup_records_every_step_shape_before_the_first_request(model_folders)
     assert [o.token_ids for o in warm] == [o.token_ids for o in lazy]
 
 
+def test_trace_records_say_what_every_step_was(model_folders):
+    """``trace_on`` / ``trace_take``: one record per step with its kind, rows, tokens, the captured
+    bucket it replayed, host milliseconds to plan and launch it and device milliseconds from two
+    CUDA events; nothing is recorded before ``trace_on``, and the records account for every
+    token the steps ran."""
+    from tokenomos_b200 import LLM, SamplingParams
+    name = "D"
+    folder = model_folders[name][torch.bfloat16]
+    prompts = prompts_for(name, [37, 5, 64, 18], seed=4)
+    kw = dict(work="bf16", page=TINY[name]["page"], max_len=128, slots=4, pages=40, prefill_budget=24)
+    with LLM(str(folder), graphs=True, warmup=True, **kw) as llm:
+        llm.generate(prompts[:1], SamplingParams(max_tokens=3))
+        assert llm.engine.trace_take() == []
+        llm.engine.trace_on()
+        before = llm.engine.stats.steps
+        outs = llm.generate(prompts, SamplingParams(max_tokens=8))
+        records = llm.engine.trace_take()
+        assert len(records) == llm.engine.stats.steps - before
+        assert llm.engine.trace_take() == []
+    kinds = {r["kind"] for r in records}
+    assert "decode" in kinds and "mixed" in kinds
+    for r in records:
+        assert set(r) >= {"step", "kind", "rows", "tokens", "bucket", "captured", "plan_ms", "launch_ms",
+                          "wait_ms", "gpu_ms"}
+        assert r["gpu_ms"] > 0 and r["plan_ms"] >= 0 and r["rows"] <= r["tokens"]
+        if r["kind"] == "decode":
+            assert r["captured"] and r["rows"] == r["tokens"] <= r["bucket"]
+        if r["kind"] == "mixed":
+            assert r["captured"] and r["tokens"] <= r["bucket"][0] and r["rows"] <= r["bucket"][1]
+    # every prompt token and every generated token but each reply's last went through a step
+    ran = sum(r["tokens"] for r in records)
+    assert ran == sum(len(p) for p in prompts) + sum(len(o.token_ids) - 1 for o in outs)
+
+
 def test_seeded_sampling_repeats_alone_and_in_batches(model_folders):
     from tokenomos_b200 import LLM, SamplingParams
     folder = model_folders["B"][torch.bfloat16]

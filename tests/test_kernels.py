@@ -110,6 +110,17 @@ def test_swiglu_and_head_gate(dtype):
     gate = torch.randn(6, 5).to(dtype)
     got = ops.head_gate(dev(x).clone(), dev(gate), 5, 24)
     close(got, x.double() * torch.sigmoid(gate.double())[:, :, None], dtype, "head gate")
+    # head sizes in whole 16-byte chunks (the vector form in bfloat16), the gate a column block
+    # of a wider tensor, enough rows for several trips of the grid-stride loop
+    for T, H, D in ((3, 4, 16), (700, 32, 64), (41, 6, 40)):
+        x = torch.randn(T, H, D).to(dtype)
+        wide = torch.randn(T, H + 11).to(dtype)
+        got = ops.head_gate(dev(x).clone(), dev(wide)[:, 3:3 + H], H, D)
+        want = x.double() * torch.sigmoid(wide[:, 3:3 + H].double())[:, :, None]
+        close(got, want, dtype, f"head gate {T}x{H}x{D}")
+        if dtype == torch.bfloat16:      # bit for bit what the scalar form gives (head size 24 above)
+            s = torch.sigmoid(wide[:, 3:3 + H].float()).to(dtype).float()
+            assert torch.equal(got.cpu(), (x.float() * s[:, :, None]).to(dtype))
 
 
 # ---- matrix product ----------------------------------------------------------------------------
@@ -777,6 +788,77 @@ def test_gemm_skinny_fused_swiglu_and_interleaved_layout(m, inter, k):
     unfused = ops.swiglu(ops.gemm_skinny(dev(x), dev(w)), 8)
     close(unfused, want, torch.bfloat16, "interleaved swiglu kernel")
     assert (fused.float() - unfused.float()).abs().max().item() <= 0.02 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("n, k", [(2048, 2048), (3104, 2048), (1024, 1024), (72, 200), (2048, 8192), (48, 64)])
+def test_gemm_skinny_with_the_norm_and_the_residual_add_inside(m, n, k):
+    """The two halves of a residual add + RMSNorm taken into the products on either side of it.
+    NORM: x is the un-normed stream; the kernel sums its squares while it streams and scales the
+    product by each row's 1 / rms, against (x * rstd) @ W.T in 64-bit. ADD: the product, rounded to
+    16 bits, joins the residual and the sum is rounded once, bit for bit what the product kernel
+    followed by the add + norm kernel's stream gives. Shapes: every CTA form the launch rule picks
+    (16-row and 8-row CTAs, two and four slices in flight), sizes that are no power of two."""
+    from tokenomos_b200 import ops
+    eps = 1e-5
+    x = (torch.randn(m, k) * 3.0).to(torch.bfloat16)           # far from unit rms
+    w = (torch.randn(n, k) * k ** -0.5).to(torch.bfloat16)
+    b = torch.randn(n)
+    rstd = (x.double().pow(2).mean(dim=1, keepdim=True) + eps).rsqrt()
+    for bias in (None, b):
+        got = ops.gemm_skinny(dev(x), dev(w), dev(bias) if bias is not None else None, norm_eps=eps)
+        want = (x.double() * rstd) @ w.double().T + (bias.double() if bias is not None else 0.0)
+        close(got, want, torch.bfloat16, f"skinny with norm {m}x{n}x{k}")
+    residual = (torch.randn(m, n) * 2.0).to(torch.bfloat16)
+    got = ops.gemm_skinny(dev(x), dev(w), dev(b), residual=dev(residual))
+    product = ops.gemm_skinny(dev(x), dev(w), dev(b))
+    _, stream = ops.add_rmsnorm(product, dev(residual), None, 0.0)
+    assert torch.equal(got, stream), (got.float() - stream.float()).abs().max().item()
+    # a row-strided residual
+    wide = (torch.randn(m, n + 16) * 2.0).to(torch.bfloat16)
+    got = ops.gemm_skinny(dev(x), dev(w), None, residual=dev(wide)[:, 8:8 + n])
+    _, stream = ops.add_rmsnorm(ops.gemm_skinny(dev(x), dev(w)), dev(wide)[:, 8:8 + n].contiguous(), None, 0.0)
+    assert torch.equal(got, stream)
+    with pytest.raises(ops.KernelError, match="at most 8 rows"):
+        ops.gemm_skinny(dev(torch.zeros(9, k, dtype=torch.bfloat16)), dev(w), norm_eps=eps)
+
+
+@pytest.mark.parametrize("m, inter, k", [(1, 64, 128), (8, 8192, 2048), (3, 104, 72)])
+def test_gemm_skinny_fused_swiglu_with_the_norm_inside(m, inter, k):
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.ffn import interleave_rows
+    eps = 1e-6
+    x = (torch.randn(m, k) * 2.5).to(torch.bfloat16)
+    gate = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inter, k) * 0.1).to(torch.bfloat16)
+    normed = x.double() * (x.double().pow(2).mean(dim=1, keepdim=True) + eps).rsqrt()
+    want = torch.nn.functional.silu(normed @ gate.double().T) * (normed @ up.double().T)
+    got = ops.gemm_skinny(dev(x), dev(interleave_rows(gate, up, 8)), swiglu=True, norm_eps=eps)
+    close(got, want, torch.bfloat16, "fused swiglu with norm")
+
+
+@pytest.mark.parametrize("W, d, K, M", [(3, 2048, 2048, 8), (4, 96, 96, 3), (2, 80, 80, 1)])
+def test_gemm_skinny_conv_with_the_norm_inside(W, d, K, M):
+    """The conv epilogue on a stream that is normed inside the kernel, against the same kernel on
+    the stream normed beforehand (weight one) in 64-bit and rounded: B, C, X differ by the
+    rounding of the normed input only."""
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.shortconv import interleave_bcx
+    eps = 1e-5
+    w = interleave_bcx((torch.randn(3 * d, K) * K ** -0.5).to(torch.bfloat16), 8)
+    taps = torch.randn(d, W)
+    x = (torch.randn(M, K) * 2.0).to(torch.bfloat16)
+    normed = (x.double() * (x.double().pow(2).mean(dim=1, keepdim=True) + eps).rsqrt()).to(torch.bfloat16)
+    ctx = [(0, 1, 5, 40, 3, 0, 9, 2)[i % 8] for i in range(M)]
+    slot = list(range(1, M + 1))
+    state0 = torch.randn(M + 2, W - 1, d).to(torch.bfloat16)
+    s1, s2 = dev(state0).clone(), dev(state0).clone()
+    want = ops.gemm_skinny_conv(dev(normed), dev(w), None, dev(taps), None, s1, i32(ctx), i32(slot))
+    got = ops.gemm_skinny_conv(dev(x), dev(w), None, dev(taps), None, s2, i32(ctx), i32(slot), norm_eps=eps)
+    scale = want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= 3e-2 * scale
+    assert (s1.float() - s2.float()).abs().max().item() <= 3e-2 * s1.float().abs().max().item()
+    assert torch.equal(s2[[0, M + 1]].cpu(), state0[[0, M + 1]])
 
 
 # ---- TMA + tcgen05 matrix product -----------------------------------------------------------------

@@ -54,23 +54,30 @@ def test_mixers_and_ffn_alone(name, dtype, model_folders):
     ctx, cache, _ = _ctx_for(model.state_specs(), TINY[name]["page"], lens, dtype)
     d = config["hidden_size"]
     x = torch.randn(sum(lens), d).to(dtype)
-    xs = torch.split(x.double(), lens)
     for i, kind in enumerate(s["layer_types"]):
         block = model.blocks[i]
-        got = block.mixer.forward(x.cuda(), ctx, i)
         p = f"model.layers.{i}."
+        # each part is fed what its own pre-norm makes of x. In a 16-bit model the norm's weight
+        # lives in the part's first projection (the block folds it in when it is built) and the
+        # norm that is left has weight one; the pair must still equal norm-with-weight then part.
+        folded = dtype == torch.bfloat16 and not s["sandwich"]
+        assert (block.eps_mixer is not None) == folded and (block.eps_ffn is not None) == folded
+        for norm, weight in ((block.pre_mixer, f"{p}operator_norm.weight"), (block.pre_ffn, f"{p}ffn_norm.weight")):
+            plain_weight = torch.ones_like(w[weight]) if folded else w[weight]
+            _close(norm(x.cuda()), plain_lfm3.rmsnorm(x.double(), plain_weight, s["eps"]), dtype,
+                   f"{name} layer {i} {weight}")
+        xs = torch.split(plain_lfm3.rmsnorm(x.double(), w[f"{p}operator_norm.weight"], s["eps"]), lens)
+        got = block.mixer.forward(block.pre_mixer(x.cuda()), ctx, i)
         if kind == "conv":
             want = torch.cat([plain_lfm3.short_conv(v, w, f"{p}conv.", s, torch.float64) for v in xs])
         else:
             want = torch.cat([plain_lfm3.attention(v, w, f"{p}self_attn.", s, kind, torch.float64)
                               for v in xs])
         _close(got, want, dtype, f"{name} layer {i} {kind}")
-        got = block.ffn.forward(x.cuda())
-        _close(got, plain_lfm3.swiglu(x.double(), w, f"{p}feed_forward.", torch.float64), dtype,
+        got = block.ffn.forward(block.pre_ffn(x.cuda()))
+        normed = plain_lfm3.rmsnorm(x.double(), w[f"{p}ffn_norm.weight"], s["eps"])
+        _close(got, plain_lfm3.swiglu(normed, w, f"{p}feed_forward.", torch.float64), dtype,
                f"{name} layer {i} ffn")
-        norm = block.pre_mixer
-        _close(norm(x.cuda()), plain_lfm3.rmsnorm(x.double(), w[f"{p}operator_norm.weight"], s["eps"]),
-               dtype, f"{name} layer {i} norm")
 
 
 def test_rope_part_matches_the_plain_tables():

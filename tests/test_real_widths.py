@@ -17,9 +17,10 @@ own engine on a real checkpoint is an argmax agreement of 0.97 and no gap over 0
 (Tokenomos tests/core/test_engine.py:98-102). Measured on a B200 over 150 rows per width and
 way of cutting: agreement 0.96 to 0.98, the worst chosen token 0.03 nats below the best, every
 row whose best two oracle logits are further apart than 0.15 nats agreed; errors of 1.1 to 1.7 %
-of the largest logit against the oracle (the largest of 65,536 errors of a row), 0.8 to 1.1 %
-between two ways of cutting. The test holds the gap to 0.08 nats, the agreement to 0.94 over
-all rows and to 1.0 over the clear ones, and the 32-bit path to full agreement.
+of the largest logit against the oracle (the largest of 65,536 errors of a row), 1.0 to 1.7 %
+between two ways of cutting (a step of a few decoded tokens and a prompt portion round at
+different places, see tests/test_replay.py). The test holds the gap to 0.08 nats, the agreement
+to 0.94 over all rows and to 1.0 over the clear ones, and the 32-bit path to full agreement.
 """
 
 from __future__ import annotations
@@ -46,9 +47,9 @@ WIDTHS = {
 }
 PAGE = 16
 # relative to the largest |logit| of the request; measured on a B200: 32-bit 3e-6 to 6e-6,
-# bfloat16 1.1 to 1.7 %; between two ways of cutting 0 (32-bit) and 0.8 to 1.1 %
+# bfloat16 1.0 to 1.5 %; between two ways of cutting 0 (32-bit) and 1.0 to 1.7 %
 TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
-TOL_SAME = {"float32": 1e-5, "bfloat16": 1.6e-2}
+TOL_SAME = {"float32": 1e-5, "bfloat16": 2.5e-2}
 GAP_NATS = 0.08
 CLEAR_NATS = 0.15
 
@@ -195,11 +196,14 @@ def test_every_route_at_real_widths_through_generate(real_folders, monkeypatch):
         routes = _count_routes(llm.model)
         assert llm.engine.stats.decode_steps > 0 and llm.engine.stats.graph_steps > 0
     assert ops.gemm_tc_status() == 0 and ops.attention_prefill_tc_status() == 0
-    for key in ("skinny head", "tc head", "library head",                 # 1..4 rows, 5..64, more
-                "skinny 2048x2048", "library 2048x2048",                  # out / o projections
-                "skinny 3104x2048", "library 3104x2048",                  # q, k, v and the gate
-                "skinny 2048x8192", "tc 2048x8192", "library 2048x8192",  # the down projection
-                "library 16384x2048", "library 6144x2048"):
+    # up to 8 decoded tokens a block's norms and residual adds run inside its products
+    # ("skinny+norm", "skinny+add"); 9 to 16 rows take the plain weight-streaming kernel
+    for key in ("skinny head", "tc head", "library head",                            # 1..4 rows, 5..64, more
+                "skinny+add 2048x2048", "skinny 2048x2048", "library 2048x2048",     # out / o
+                "skinny+norm 3104x2048", "skinny 3104x2048", "library 3104x2048",    # q, k, v, gate
+                "skinny+add 2048x8192", "tc 2048x8192", "library 2048x8192",         # down
+                "skinny+norm 16384x2048", "library 16384x2048",                      # gate / up
+                "skinny+norm 6144x2048", "library 6144x2048"):                       # conv in
         assert routes.get(key, 0) > 0, (key, routes)
     assert all(n > 0 for n in forms.values()), forms
 

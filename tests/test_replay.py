@@ -18,13 +18,18 @@ pytestmark = pytest.mark.gpu
 # Tolerances, relative to the largest |logit| of the request. 32-bit: accumulation order only
 # (measured: 4e-7 to 2e-6 against the float64 oracle, at most 1e-6 between two ways of cutting).
 # bfloat16: the 16-bit path rounds activations after every kernel, and a configuration's error
-# depends on its depth and weight scale, so each has its own bound, about 1.3 to 2 times what
-# was measured on a B200: against the oracle A 0.32 %, B 2.3 %, C 3.1 %, D 1.7 % of the scale;
-# between two bfloat16 runs that differ only in cutting A 1e-7, B 0.57 %, C 0.88 %, D 1.3 %
-# (other kernels take a portion than a single token: the tensor-core attention in D).
+# depends on its depth and weight scale, so each has its own bound, about 1.3 to 1.7 times what
+# was measured on a B200: against the oracle A 0.47 %, B 2.7 %, C 3.1 %, D 1.6 % of the scale.
+# Two bfloat16 runs that differ only in cutting do not round alike: a step of a few decoded
+# tokens takes the norm and the residual add inside its products (the normed activation is
+# never rounded to 16 bits there), a prompt portion takes the norm kernel, and the tensor-core
+# attention has a prefill and a decode form. Their difference is that of two roundings of the
+# same value, so it is held to about the bound each has against the oracle (measured: A 0.33 %,
+# B 3.4 %, C 0.88 %, D 1.4 %), not to accumulation order; the 32-bit path, where the cut changes
+# no rounding, is what holds the cache and the batch to 1e-5.
 TOL_F32, TOL_F32_SAME = 2e-5, 1e-5
-TOL_BF16 = {"A": 6e-3, "B": 3.5e-2, "C": 4e-2, "D": 2.5e-2}
-TOL_BF16_SAME = {"A": 1e-3, "B": 1e-2, "C": 1.5e-2, "D": 2e-2}
+TOL_BF16 = {"A": 8e-3, "B": 4e-2, "C": 4e-2, "D": 2.5e-2}
+TOL_BF16_SAME = {"A": 6e-3, "B": 5e-2, "C": 1.5e-2, "D": 2.2e-2}
 
 
 def tol(name: str, dtype: str, same: bool = False) -> float:

@@ -81,7 +81,7 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
             const int kk = tid >> 2, part = tid & 3;
             const int j = j0 + kk;
             if (j <= pos_last) {
-                const int page = block_table[(size_t)seq * bt_stride + j / P];
+                const int page = TK_PAGE(TK_K_ATTN_GENERIC, block_table[(size_t)seq * bt_stride + j / P]);
                 const size_t base = ((size_t)page * 2 * Hkv * P + (size_t)kvh * P + (j % P)) * D;
                 const size_t vbase = base + (size_t)Hkv * P * D;
                 for (int c = part; c < D; c += 4) {

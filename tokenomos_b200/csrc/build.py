@@ -82,9 +82,17 @@ def build_root() -> Path:
     return Path(tempfile.gettempdir()) / f"tokenomos_b200-build-{os.getuid()}"
 
 
-def library_path() -> Path:
-    """Path of the library for the current sources (it may not exist yet)."""
-    tag = source_hash()
+def checks_wanted() -> bool:
+    """``TOKENOMOS_B200_CHECKS=1``: the debug build whose kernels check every index they follow
+    into a pool (checks.cuh)."""
+    return os.environ.get("TOKENOMOS_B200_CHECKS", "0") == "1"
+
+
+def library_path(checks: bool | None = None) -> Path:
+    """Path of the library for the current sources (it may not exist yet); the build with
+    index checks lives beside the plain one."""
+    checks = checks_wanted() if checks is None else checks
+    tag = source_hash() + ("-checks" if checks else "")
     local = HERE / "_build" / tag / LIB_NAME
     if local.exists():
         return local
@@ -95,8 +103,9 @@ def _say(msg: str) -> None:
     print(f"[tokenomos_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> None:
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)]
+def _compile(nvcc: str, src: Path, obj: Path, verbose: bool, checks: bool = False) -> None:
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *(["-DTK_CHECKS"] if checks else []), "-I", str(HERE), "-c",
+           str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -107,9 +116,11 @@ def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> None:
         _say(f"{src.name}:\n{proc.stderr}")
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile if needed and return the library's path."""
-    target = library_path()
+def build(force: bool = False, verbose: bool = False, checks: bool | None = None) -> Path:
+    """Compile if needed and return the library's path. ``checks``: the debug build with index
+    checks (default: what ``TOKENOMOS_B200_CHECKS`` says)."""
+    checks = checks_wanted() if checks is None else checks
+    target = library_path(checks)
     if target.exists() and not force:
         return target
     nvcc = find_nvcc()
@@ -129,7 +140,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     try:
         objs = [work / (s.stem + ".o") for s in srcs]
         with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
-            futs = [pool.submit(_compile, nvcc, s, o, verbose) for s, o in zip(srcs, objs)]
+            futs = [pool.submit(_compile, nvcc, s, o, verbose, checks) for s, o in zip(srcs, objs)]
             for s, f in zip(srcs, futs):
                 f.result()
                 _say(f"  compiled {s.name} ({time.time() - t0:.0f} s)")
@@ -140,8 +151,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stderr[-4000:]}")
         os.replace(tmp_lib, target)
         # libraries of earlier source states are dead weight (each is a few MB)
+        current = source_hash()
         for old in target.parent.parent.iterdir():
-            if old.is_dir() and old != target.parent and (old / LIB_NAME).exists():
+            if old.is_dir() and not old.name.startswith(current) and (old / LIB_NAME).exists():
                 shutil.rmtree(old, ignore_errors=True)
     finally:
         done.set()
@@ -151,4 +163,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv,
+                checks=True if "--checks" in sys.argv else None))

@@ -10,6 +10,8 @@
 
 #define TK_API extern "C" __attribute__((visibility("default")))
 
+#include "checks.cuh"
+
 // dtype codes shared with the Python side (ops/_lib.py)
 enum TkDtype : int { TK_F32 = 0, TK_BF16 = 1 };
 

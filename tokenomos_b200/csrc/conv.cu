@@ -36,7 +36,7 @@ __global__ void conv_gated_kernel(const T* bcx, int64_t stride, int d,
     const int start = cu[s];
     const int len = cu[s + 1] - start;
     const int ctx = seq_ctx[s];
-    T* st = state + (size_t)seq_slot[s] * (W - 1) * d + c;
+    T* st = state + (size_t)TK_SLOT(TK_K_CONV, seq_slot[s]) * (W - 1) * d + c;
 
     float taps[W];
 #pragma unroll
@@ -109,7 +109,7 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
     const int start = cu[s];
     const int len = cu[s + 1] - start;
     const int ctx = seq_ctx[s];
-    T* st = state + (size_t)seq_slot[s] * (W - 1) * d + c;
+    T* st = state + (size_t)TK_SLOT(TK_K_CONV, seq_slot[s]) * (W - 1) * d + c;
 
     float taps[W][VEC], b[VEC];
 #pragma unroll

@@ -13,7 +13,7 @@ __global__ void gather_rows_kernel(const T* table, const int* ids,
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
-    int id = ids[r];
+    int id = TK_ROW(TK_K_GATHER, ids[r], rows_in_table);
     // an id outside the table would read foreign memory: clamp (callers validate on the host)
     id = id < 0 ? 0 : (id >= rows_in_table ? rows_in_table - 1 : id);
     const T* src = table + (size_t)id * width;
@@ -56,7 +56,7 @@ __global__ void gather_rows_select_kernel(const T* table, const int* ids_host, c
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
-    int id = use_prev[r] ? last_token[slot[r]] : ids_host[r];
+    int id = TK_ROW(TK_K_GATHER, use_prev[r] ? last_token[slot[r]] : ids_host[r], rows_in_table);
     id = id < 0 ? 0 : (id >= rows_in_table ? rows_in_table - 1 : id);
     const T* src = table + (size_t)id * width;
     T* dst = out + (size_t)r * width;
@@ -443,6 +443,30 @@ __global__ void head_gate_kernel(T* x, const T* g, int64_t ldg, int64_t total, i
     }
 }
 
+// The same on 16 bytes of bfloat16 at a time (head_dim a multiple of 8, x 16-byte aligned): a
+// prompt portion's gate is a pass over [tokens, heads, head_dim], bound by memory.
+__global__ void head_gate_vec_kernel(__nv_bfloat16* x, const __nv_bfloat16* g, int64_t ldg,
+                                     int64_t chunks, int heads, int chunks_per_head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (; i < chunks; i += step) {
+        const int64_t th = i / chunks_per_head;
+        const float gate = __bfloat162float(g[(th / heads) * ldg + th % heads]);
+        const float s = round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-gate)));
+        uint4 v = reinterpret_cast<uint4*>(x)[i];
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[e]));
+            const __nv_bfloat162 r = __floats2bfloat162_rn(f.x * s, f.y * s);
+            w[e] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        reinterpret_cast<uint4*>(x)[i] = v;
+    }
+}
+
 // g: [rows, heads] with rows `ldg` elements apart (a column block of a wider projection's output)
 TK_API int tk_head_gate(void* x, const void* g, int64_t ldg, int rows, int heads, int head_dim, int dtype,
                         cudaStream_t stream) {
@@ -452,7 +476,13 @@ TK_API int tk_head_gate(void* x, const void* g, int64_t ldg, int rows, int heads
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                         : 148 * 16);
-    if (dtype == TK_F32)
+    if (dtype == TK_BF16 && head_dim % 8 == 0 && (uintptr_t)x % 16 == 0) {
+        const int64_t chunks = total / 8;
+        const int vblocks = (int)((chunks + threads - 1) / threads < 148 * 16 ? (chunks + threads - 1) / threads
+                                                                             : 148 * 16);
+        tk_launch(head_gate_vec_kernel, dim3(vblocks), dim3(threads), 0, stream, (__nv_bfloat16*)x,
+                  (const __nv_bfloat16*)g, ldg, chunks, heads, head_dim / 8);
+    } else if (dtype == TK_F32)
         tk_launch(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, (const float*)g, ldg, total, heads, head_dim);
     else if (dtype == TK_BF16)
         tk_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 

@@ -59,6 +59,34 @@ struct ConvTail {
 
 enum : int { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
 
+// The two halves of a residual add + RMSNorm taken into the products on either side of it, so
+// that a decode step needs no kernel between two products:
+//   NORM (the product after the norm): x is the residual stream itself, not normed. Every CTA
+//     reads all of x anyway, so it sums the squares of what it loads, and the epilogue scales the
+//     accumulators by rstd = 1 / sqrt(mean(x^2) + eps) of each token's row. The norm's weight is
+//     folded into the matrix's columns when the model is built (W'[n, k] = W[n, k] * weight[k]),
+//     so (x * rstd * weight) . W^T = rstd * (x . W'^T).
+//   ADD (the product before the norm): the epilogue adds the product, rounded as a store would
+//     round it, to `residual` and writes the new stream, rounded once: what the norm kernel's
+//     add does.
+struct Fuse {
+    float eps;                          // NORM
+    const __nv_bfloat16* residual;      // ADD: [M, N], rows `ldr` apart
+    int64_t ldr;
+};
+
+__device__ __forceinline__ float sum_squares(const uint4& v) {
+    float acc = 0.f;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+    }
+    return acc;
+}
+
 // MT: 8 or 16 tokens (one or two n8 tiles). R8: the CTA owns 8 weight rows instead of 16 (the
 // upper half of the mma tile stays zero): twice as many CTAs for matrices with few rows.
 // EPI_SWIGLU: the weight rows come in blocks of 16, 8 gate rows then the 8 up rows of the same
@@ -68,16 +96,18 @@ enum : int { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_CONV = 2 };
 // the CTA writes C * conv(B * X) for its 8 channels and moves their state on: out is [M, N / 3].
 // A second mma per step takes the X rows (its upper half stays zero).
 // UNROLL: slices whose loads a warp has in flight together (registers: 8 per slice and row half)
-template <int MT, typename TO, bool R8, int EPI, int UNROLL>
+template <int MT, typename TO, bool R8, int EPI, int UNROLL, bool NORM = false, bool ADD = false>
 __global__ void __launch_bounds__(512)
 gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                    const __nv_bfloat16* __restrict__ w, int64_t ldw, const float* __restrict__ bias,
-                   TO* out, int64_t ldo, int M, int N, int K, ConvTail tail) {
-    extern __shared__ float red[];                 // [warps][RED_ROWS][MT]
+                   TO* out, int64_t ldo, int M, int N, int K, ConvTail tail, Fuse fuse) {
+    extern __shared__ float red[];                 // [warps][RED_ROWS][MT], NORM: + [warps][MT] + [MT]
     pdl_launch_dependents();
     constexpr bool SWIGLU = EPI == EPI_SWIGLU, CONV = EPI == EPI_CONV;
     constexpr int RED_ROWS = CONV ? 24 : ROWS;
     const int warps = blockDim.x >> 5;
+    float* ssq_s = red + (size_t)warps * RED_ROWS * MT;      // NORM: each warp's sums of squares
+    float* rstd_s = ssq_s + (size_t)warps * MT;              // NORM: 1 / rms of each token's row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     constexpr int CTA_ROWS = CONV ? 24 : (R8 ? 8 : ROWS);
@@ -112,6 +142,11 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
     float pf_state[3] = {0.f, 0.f, 0.f};
     int pf_ctx = 0;
     bool pf = false;
+    float ss[TG];                                  // NORM: this thread's share of sum(x^2)
+#pragma unroll
+    for (int i = 0; i < TG; ++i) ss[i] = 0.f;
+    float pf_res = 0.f;                            // ADD: the residual of this thread's output
+    bool pf_res_ok = false;
     for (int s0 = warp; s0 < slices; s0 += warps * UNROLL) {
         uint4 wa[UNROLL][2], wb[UNROLL][2], wc[CONV ? UNROLL : 1][2];
 #pragma unroll
@@ -131,6 +166,16 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
         if (!waited) {
             pdl_wait();
             waited = true;
+            if constexpr (ADD) {
+                // the residual this thread's output joins, asked for now instead of after the
+                // reduction (rows fastest, as the epilogue walks them)
+                constexpr int CR = R8 ? 8 : ROWS;
+                const int tok = threadIdx.x / CR, r = threadIdx.x % CR;
+                if ((int)threadIdx.x < CR * MT && tok < M && n0 + r < N) {
+                    pf_res = __bfloat162float(fuse.residual[(size_t)tok * fuse.ldr + n0 + r]);
+                    pf_res_ok = true;
+                }
+            }
             if constexpr (CONV) {
                 // what this thread's (token, channel) needs of the conv state in the epilogue is
                 // asked for now (widths up to 4): two trips to memory, one behind the other, that
@@ -138,7 +183,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                 const int tok = threadIdx.x / 8, c = blockIdx.x * 8 + threadIdx.x % 8;
                 if (threadIdx.x < 8 * MT && tok < M && c < tail.d && tail.W <= 4) {
                     pf_ctx = tail.seq_ctx[tok];
-                    const __nv_bfloat16* st = tail.state + (size_t)tail.seq_slot[tok] * (tail.W - 1) * tail.d + c;
+                    const __nv_bfloat16* st = tail.state + (size_t)TK_SLOT(TK_K_SKINNY_CONV, tail.seq_slot[tok]) * (tail.W - 1) * tail.d + c;
 #pragma unroll
                     for (int k = 0; k < 3; ++k)
                         if (k < tail.W - 1) pf_state[k] = __bfloat162float(st[(size_t)k * tail.d]);
@@ -156,6 +201,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
 #pragma unroll
                 for (int i = 0; i < TG; ++i) {
                     const uint4 xv = (ok && x_ok[i]) ? ld_activation(xr[i] + k) : zero;
+                    if constexpr (NORM) ss[i] += sum_squares(xv);
                     // elements 0..3 of the 16 bytes are one mma step, 4..7 the next
                     mma16816(acc[i], wa[u][h].x, wb[u][h].x, wa[u][h].y, wb[u][h].y, xv.x, xv.y);
                     mma16816(acc[i], wa[u][h].z, wb[u][h].z, wa[u][h].w, wb[u][h].w, xv.z, xv.w);
@@ -181,7 +227,25 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
             dst[(g + 16) * MT + 8 * i + 2 * t + 1] = accx[i][1];
         }
     }
+    if constexpr (NORM) {
+        // lanes t = 0..3 of a quad hold parts of token g's sum; the CTA's warps cover all of K
+#pragma unroll
+        for (int i = 0; i < TG; ++i) {
+            float v = ss[i];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0) ssq_s[warp * MT + 8 * i + g] = v;
+        }
+    }
     __syncthreads();
+    if constexpr (NORM) {
+        if ((int)threadIdx.x < MT) {
+            float v = 0.f;
+            for (int wv = 0; wv < warps; ++wv) v += ssq_s[wv * MT + threadIdx.x];
+            rstd_s[threadIdx.x] = rsqrtf(v / (float)K + fuse.eps);
+        }
+        __syncthreads();
+    }
     if constexpr (CONV) {
         // one thread per (token, channel): B, C, X of the channel as the unfused path stores them,
         // u = B X, the taps over the state row and u, the state moved on by one
@@ -197,6 +261,12 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                 cv += src[(j + 8) * MT];
                 xv += src[(j + 16) * MT];
             }
+            if constexpr (NORM) {
+                const float rs = rstd_s[tok];
+                bv *= rs;
+                cv *= rs;
+                xv *= rs;
+            }
             if (bias != nullptr) {
                 bv += bias[n0 + j];
                 cv += bias[n0 + 8 + j];
@@ -208,7 +278,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
             const float u = round_as<TO>(bv * xv);
             const bool have = pf && idx == (int)threadIdx.x;          // fetched at the start
             const int ctx = have ? pf_ctx : tail.seq_ctx[tok];
-            __nv_bfloat16* st = tail.state + (size_t)tail.seq_slot[tok] * (W - 1) * d + c;
+            __nv_bfloat16* st = tail.state + (size_t)TK_SLOT(TK_K_SKINNY_CONV, tail.seq_slot[tok]) * (W - 1) * d + c;
             const float* taps = tail.taps + (size_t)c * W;
             // state row k holds u of position ctx - (W - 1) + k; before position 0 it reads as 0
             float acc_c = 0.f;
@@ -244,6 +314,10 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                 gate += red[(size_t)wv * ROWS * MT + j * MT + tok];
                 up += red[(size_t)wv * ROWS * MT + (j + 8) * MT + tok];
             }
+            if constexpr (NORM) {
+                gate *= rstd_s[tok];
+                up *= rstd_s[tok];
+            }
             if (bias != nullptr) {
                 gate += bias[n0 + j];
                 up += bias[n0 + 8 + j];
@@ -260,7 +334,14 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
             if (tok >= M || n0 + r >= N) continue;
             float v = 0.f;
             for (int wv = 0; wv < warps; ++wv) v += red[(size_t)wv * ROWS * MT + r * MT + tok];
+            if constexpr (NORM) v *= rstd_s[tok];
             if (bias != nullptr) v += bias[n0 + r];
+            if constexpr (ADD) {
+                const float res = (pf_res_ok && idx == (int)threadIdx.x)
+                                      ? pf_res
+                                      : __bfloat162float(fuse.residual[(size_t)tok * fuse.ldr + n0 + r]);
+                v = res + round_as<TO>(v);
+            }
             out[(size_t)tok * ldo + n0 + r] = from_f<TO>(v);
         }
     }
@@ -289,14 +370,23 @@ TK_API int tk_gemm_skinny_tune(int unroll, int max_warps, int r8_below) {
 // bfloat16 or float (out_dtype); M <= 16; K, ldx, ldw multiples of 8 and 16-byte aligned bases.
 // swiglu != 0: w holds blocks of 8 gate rows followed by the 8 up rows of the same channels
 // (N a multiple of 16) and out is [M, N / 2] = silu(gate) * up.
+// norm_eps > 0 (at most 8 rows, bfloat16 out): x is an un-normed stream and the result is scaled
+// by each row's 1 / sqrt(mean(x^2) + norm_eps) (see Fuse; the norm's weight is in w's columns).
+// residual != null (at most 8 rows, bfloat16 out, no swiglu): out = residual + product, the
+// product rounded first, the sum rounded once; residual: [M, N] bfloat16, rows `ldr` apart.
 TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                           void* out, int64_t ldo, int M, int N, int K, int out_dtype, int swiglu,
-                          cudaStream_t stream) {
+                          float norm_eps, const void* residual, int64_t ldr, cudaStream_t stream) {
     TK_CHECK_ARG(M >= 0 && M <= 16 && N > 0 && K > 0, "gemm_skinny: M=%d (at most 16) N=%d K=%d", M, N, K);
     TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_skinny: K and the leading dimensions "
                  "must be multiples of 8 (K=%d)", K);
     TK_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_skinny: operands must be 16-byte aligned");
     TK_CHECK_ARG(!swiglu || N % 16 == 0, "gemm_skinny: the fused SwiGLU needs N (%d) in blocks of 16", N);
+    const bool norm = norm_eps > 0.f, add = residual != nullptr;
+    TK_CHECK_ARG(!(norm || add) || (M <= 8 && out_dtype == TK_BF16),
+                 "gemm_skinny: the fused norm and the fused residual add take at most 8 rows and a "
+                 "bfloat16 output (M=%d)", M);
+    TK_CHECK_ARG(!(norm && add) && !(add && swiglu), "gemm_skinny: the residual add goes with a plain product only");
     if (M == 0) return 0;
     const int slices = (K + KSLICE - 1) / KSLICE;
     const int ctas16 = (N + ROWS - 1) / ROWS;
@@ -312,29 +402,39 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
     const bool r8 = !swiglu && (g_r8_below >= 0 ? ctas16 < g_r8_below : (mid || ctas16 < 74));
     const int blocks = r8 ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
     const int MT = M <= 8 ? 8 : 16;
-    const size_t smem = (size_t)warps * ROWS * MT * sizeof(float);
+    const size_t smem = ((size_t)warps * ROWS * MT + (norm ? (size_t)warps * MT + MT : 0)) * sizeof(float);
     auto x_ = (const __nv_bfloat16*)x;
     auto w_ = (const __nv_bfloat16*)w;
-#define TK_SKINNY(MT_, TO_, R8_, SW_)                                                              \
+    const Fuse fuse{norm_eps, (const __nv_bfloat16*)residual, ldr};
+#define TK_SKINNY_F(MT_, TO_, R8_, SW_, NORM_, ADD_)                                               \
     do {                                                                                           \
         if (unroll == 2)                                                                           \
-            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 2>, dim3(blocks), dim3(threads), smem, stream, \
-                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{});                \
+            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 2, NORM_, ADD_>, dim3(blocks), dim3(threads), smem, \
+                      stream, x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{}, fuse);   \
         else                                                                                       \
-            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 4>, dim3(blocks), dim3(threads), smem, stream, \
-                      x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{});                \
+            tk_launch(gemm_skinny_kernel<MT_, TO_, R8_, SW_, 4, NORM_, ADD_>, dim3(blocks), dim3(threads), smem, \
+                      stream, x_, ldx, w_, ldw, bias, (TO_*)out, ldo, M, N, K, ConvTail{}, fuse);   \
     } while (0)
+#define TK_SKINNY(MT_, TO_, R8_, SW_) TK_SKINNY_F(MT_, TO_, R8_, SW_, false, false)
 #define TK_SKINNY_T(TO_)                                                                           \
     do {                                                                                           \
         if (swiglu) { if (MT == 8) TK_SKINNY(8, TO_, false, EPI_SWIGLU); else TK_SKINNY(16, TO_, false, EPI_SWIGLU); } \
         else if (r8) { if (MT == 8) TK_SKINNY(8, TO_, true, EPI_NONE); else TK_SKINNY(16, TO_, true, EPI_NONE); } \
         else { if (MT == 8) TK_SKINNY(8, TO_, false, EPI_NONE); else TK_SKINNY(16, TO_, false, EPI_NONE); }  \
     } while (0)
-    if (out_dtype == TK_BF16) TK_SKINNY_T(__nv_bfloat16);
+    if (norm) {
+        if (swiglu) TK_SKINNY_F(8, __nv_bfloat16, false, EPI_SWIGLU, true, false);
+        else if (r8) TK_SKINNY_F(8, __nv_bfloat16, true, EPI_NONE, true, false);
+        else TK_SKINNY_F(8, __nv_bfloat16, false, EPI_NONE, true, false);
+    } else if (add) {
+        if (r8) TK_SKINNY_F(8, __nv_bfloat16, true, EPI_NONE, false, true);
+        else TK_SKINNY_F(8, __nv_bfloat16, false, EPI_NONE, false, true);
+    } else if (out_dtype == TK_BF16) TK_SKINNY_T(__nv_bfloat16);
     else if (out_dtype == TK_F32) TK_SKINNY_T(float);
     else TK_CHECK_ARG(false, "gemm_skinny: output dtype %d", out_dtype);
 #undef TK_SKINNY_T
 #undef TK_SKINNY
+#undef TK_SKINNY_F
     TK_CHECK_LAUNCH("gemm_skinny");
     return 0;
 }
@@ -344,17 +444,20 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
 // w: [3 d, K] bfloat16 whose rows come in blocks of 24: 8 rows of B, of C and of X of the same 8
 // channels (d a multiple of 8); bias: [3 d] in the same order, or null. taps: [d, W] float32,
 // conv_bias: [d] or null; state: [slots, W - 1, d] bfloat16, moved on by one token per request;
-// seq_ctx, seq_slot: [M]. out: [M, d] bfloat16 = C * conv(B * X).
+// seq_ctx, seq_slot: [M]. out: [M, d] bfloat16 = C * conv(B * X). norm_eps > 0: x is an un-normed
+// stream and B, C, X are scaled by each row's 1 / rms first (see tk_gemm_skinny).
 TK_API int tk_gemm_skinny_conv(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                                void* out, int64_t ldo, int M, int d, int K, const float* taps,
                                const float* conv_bias, void* state, const int* seq_ctx,
-                               const int* seq_slot, int W, cudaStream_t stream) {
+                               const int* seq_slot, int W, float norm_eps, cudaStream_t stream) {
     TK_CHECK_ARG(M >= 0 && M <= 16 && d > 0 && K > 0, "gemm_skinny_conv: M=%d (at most 16) d=%d K=%d", M, d, K);
     TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_skinny_conv: K and the leading "
                  "dimensions must be multiples of 8 (K=%d)", K);
     TK_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_skinny_conv: operands must be 16-byte aligned");
     TK_CHECK_ARG(d % 8 == 0, "gemm_skinny_conv: the channel count (%d) must come in blocks of 8", d);
     TK_CHECK_ARG(W >= 2 && W <= 8, "gemm_skinny_conv: width %d outside 2..8", W);
+    const bool norm = norm_eps > 0.f;
+    TK_CHECK_ARG(!norm || M <= 8, "gemm_skinny_conv: the fused norm takes at most 8 rows (M=%d)", M);
     if (M == 0) return 0;
     const int N = 3 * d;
     const int slices = (K + KSLICE - 1) / KSLICE;
@@ -366,16 +469,18 @@ TK_API int tk_gemm_skinny_conv(const void* x, int64_t ldx, const void* w, int64_
     int warps = (slices + unroll - 1) / unroll;
     warps = warps < 1 ? 1 : (warps > max_warps ? max_warps : warps);
     const int MT = M <= 8 ? 8 : 16;
-    const size_t smem = (size_t)warps * 24 * MT * sizeof(float);
+    const size_t smem = ((size_t)warps * 24 * MT + (norm ? (size_t)warps * MT + MT : 0)) * sizeof(float);
     const ConvTail tail{taps, conv_bias, (__nv_bfloat16*)state, seq_ctx, seq_slot, W, d};
+    const Fuse fuse{norm_eps, nullptr, 0};
     auto x_ = (const __nv_bfloat16*)x;
     auto w_ = (const __nv_bfloat16*)w;
     auto o_ = (__nv_bfloat16*)out;
-#define TK_SKINNY_CONV(MT_, U_)                                                                    \
-    tk_launch(gemm_skinny_kernel<MT_, __nv_bfloat16, false, EPI_CONV, U_>, dim3(blocks), dim3(warps * 32), \
-              smem, stream, x_, ldx, w_, ldw, bias, o_, ldo, M, N, K, tail)
-    if (MT == 8) TK_SKINNY_CONV(8, 2);
-    else TK_SKINNY_CONV(16, 2);
+#define TK_SKINNY_CONV(MT_, U_, NORM_)                                                             \
+    tk_launch(gemm_skinny_kernel<MT_, __nv_bfloat16, false, EPI_CONV, U_, NORM_, false>, dim3(blocks),    \
+              dim3(warps * 32), smem, stream, x_, ldx, w_, ldw, bias, o_, ldo, M, N, K, tail, fuse)
+    if (norm) TK_SKINNY_CONV(8, 2, true);
+    else if (MT == 8) TK_SKINNY_CONV(8, 2, false);
+    else TK_SKINNY_CONV(16, 2, false);
 #undef TK_SKINNY_CONV
     TK_CHECK_LAUNCH("gemm_skinny_conv");
     return 0;

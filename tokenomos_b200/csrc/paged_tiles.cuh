@@ -40,7 +40,7 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* po
         const bool valid = j >= j_first && j <= j_last;
         const __nv_bfloat16* src = pool;
         if (valid) {
-            const int page = bt_row[j / P];
+            const int page = TK_PAGE(TK_K_ATTN_TILES, bt_row[j / P]);
             src = pool + (((size_t)page * 2 + which) * Hkv + kvh) * (size_t)P * D +
                   (size_t)(j % P) * D + c * 8;
         }
@@ -82,7 +82,7 @@ struct PagedLoader {
             const bool valid = j >= j_first && j <= j_last;
             const __nv_bfloat16* src = pool;
             if (valid) {
-                const int page = bt_row[j >> p_shift];
+                const int page = TK_PAGE(TK_K_ATTN_TILES, bt_row[j >> p_shift]);
                 src = pool + (size_t)page * page_stride + head_off + (size_t)(j & p_mask) * D;
             }
             cp_async16(ktile + dst[k], src, valid);
@@ -99,7 +99,7 @@ struct PagedLoader {
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
             const int j = min(max(j0 + r0 + k * STEP, j_first), j_last);     // always a held position
-            page[k] = bt_row[j >> p_shift];
+            page[k] = TK_PAGE(TK_K_ATTN_TILES, bt_row[j >> p_shift]);
         }
     }
 

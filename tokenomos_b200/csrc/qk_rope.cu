@@ -37,7 +37,7 @@ __global__ void qk_norm_rope_write_kernel(
     size_t cache_row = 0;
     if (Hkv > 0) {
         const int s = tok_seq[t];
-        const int page = block_table[(size_t)s * bt_stride + pos / P];
+        const int page = TK_PAGE(TK_K_QK_ROPE, block_table[(size_t)s * bt_stride + pos / P]);
         cache_row = (size_t)page * 2 * Hkv * P + (pos % P);  // + (kv*Hkv + kh)*P rows
     }
     const T* row = qkv + (size_t)t * qkv_stride;
@@ -116,7 +116,7 @@ __global__ void qk_norm_rope_write_vec_kernel(
     const int pos = positions[t];
     const int seq_of_t = Hkv > 0 ? tok_seq[t] : 0;
     // (the page is looked up before the angles are computed, not after: its trip runs beside them)
-    const int page = Hkv > 0 ? block_table[(size_t)seq_of_t * bt_stride + pos / P] : 0;
+    const int page = Hkv > 0 ? TK_PAGE(TK_K_QK_ROPE, block_table[(size_t)seq_of_t * bt_stride + pos / P]) : 0;
     const int half = R >> 1;
     float* cs = smem;
     float* sn = smem + half;

@@ -28,6 +28,18 @@ from tokenomos_b200.engine.step import StepEntry, StepFunction
 from tokenomos_b200.sampling import sampler
 
 
+def _nvtx_push(name: str) -> None:
+    """An NVTX range around a phase of the host loop (``plan``, ``launch``, ``wait``, ``deliver``,
+    ``idle``; the reference marks ``admit / decode / wait / idle``, Tokenomos
+    core/engine.py:692,752,763,794), so that a timeline shows which side a step waited on.
+    Without a profiler attached a range costs a fraction of a microsecond."""
+    torch.cuda.nvtx.range_push(name)
+
+
+def _nvtx_pop() -> None:
+    torch.cuda.nvtx.range_pop()
+
+
 @dataclass
 class Result:
     tokens: list[int]
@@ -91,8 +103,84 @@ class Engine:
         self.inbox: queue.Queue[Request] = queue.Queue()
         self.stats = Stats()
         self.prefill_budget, self.slots = prefill_budget, slots
+        # ``trace_on()``: one record per step from then on (``trace_take`` hands them over)
+        self.trace: list[dict] | None = None
+        self._trace_lock = threading.Lock()
+        self._wait_s = 0.0
+        self._nvtx = self.device.type == "cuda"
         if warmup:
             self.warmup()
+
+    # ---- tracing ----
+
+    def trace_on(self) -> None:
+        """Record every step from now on: its kind (``decode``, ``mixed``: a captured mixed step,
+        ``eager``), rows, tokens, the captured bucket it replayed, the host's milliseconds to
+        plan it, to launch it and waiting for older steps' tokens, and (from two CUDA events
+        around the step) its milliseconds on the device. Opt-in, as the reference's per-iteration
+        records are (Tokenomos core/engine.py:270-298): the two events cost a few microseconds
+        a step."""
+        with self._trace_lock:
+            self.trace = []
+
+    def trace_take(self) -> list[dict]:
+        """The records of the steps finished since the last take, device times filled in (waits
+        for their events). Any thread."""
+        with self._trace_lock:
+            if self.trace is None:
+                return []
+            records, self.trace = self.trace, []
+        out = []
+        for rec in records:
+            start, end = rec.pop("_events")
+            end.synchronize()
+            rec["gpu_ms"] = round(start.elapsed_time(end), 4)
+            out.append(rec)
+        return out
+
+    def _trace_begin(self, t0: float, kind: str, rows: int, tokens: int, bucket) -> dict | None:
+        if self._nvtx:
+            _nvtx_push("launch")
+        if self.trace is None:
+            return None
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        now = time.perf_counter()
+        return {"step": self.stats.steps, "kind": kind, "rows": rows, "tokens": tokens, "bucket": bucket,
+                "captured": kind != "eager", "plan_ms": round((now - t0) * 1e3, 4), "_t": now,
+                "_events": (start, None)}
+
+    def _trace_end(self, rec: dict | None) -> None:
+        if self._nvtx:
+            _nvtx_pop()
+        if rec is None:
+            return
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        rec["_events"] = (rec["_events"][0], end)
+        rec["launch_ms"] = round((time.perf_counter() - rec.pop("_t")) * 1e3, 4)
+        rec["wait_ms"] = round(self._wait_s * 1e3, 4)        # waiting for older steps, since the last record
+        self._wait_s = 0.0
+        with self._trace_lock:
+            if self.trace is not None:
+                self.trace.append(rec)
+
+    def _deliver_older(self, finished: list[Request]) -> None:
+        """Read the tokens of every step in flight beyond ``depth`` (waits for them) and let the
+        scheduler take them."""
+        while len(self._inflight) > self.depth:
+            old_planned, old_handle = self._inflight.popleft()
+            if self._nvtx:
+                _nvtx_push("wait")
+            t = time.perf_counter()
+            tokens = old_handle.tokens()
+            self._wait_s += time.perf_counter() - t
+            if self._nvtx:
+                _nvtx_pop()
+                _nvtx_push("deliver")
+            finished += self.scheduler.deliver(old_planned, tokens)
+            if self._nvtx:
+                _nvtx_pop()
 
     def warmup(self) -> tuple[int, int]:
         """Touch every kernel variant and record every step shape serving will meet, before the
@@ -155,6 +243,10 @@ class Engine:
             if where:
                 raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
                                    "the tokens of the steps since the last check are not to be trusted")
+        if ops.checks_enabled():
+            found = ops.checks_status()
+            if found:
+                raise RuntimeError(f"index check: {found}")
         row = ops.sample_status()
         if row:
             raise RuntimeError(f"the sampler met a row of logits without a finite value (row {row - 1} of "
@@ -183,7 +275,7 @@ class Engine:
         self._check_kernels()
         return finished
 
-    def _decode_step(self, planned, finished: list[Request]) -> list[Request]:
+    def _decode_step(self, planned, finished: list[Request], t0: float = 0.0) -> list[Request]:
         """Every request decodes one token: the captured decode graph, queued without waiting
         for the step before it. One pass over the plan builds what the graph's layout needs."""
         rids, tokens, rows, fed = [], [], [], []
@@ -201,13 +293,14 @@ class Engine:
         self.stats.stamps.append((time.perf_counter(), n, n))
         self.stats.steps += 1
         self.stats.decode_steps += 1
+        bucket = self.step_fn.decode_graph(n).rows if self.trace is not None else None
+        rec = self._trace_begin(t0, "decode", n, n, bucket)
         handle = self.step_fn.launch_decode_ids(rids, tokens, rows, fed)
+        self._trace_end(rec)
         self.scheduler.launch(planned)
         self._inflight.append((planned, handle))
         self.stats.generated += n
-        while len(self._inflight) > self.depth:
-            old_planned, old_handle = self._inflight.popleft()
-            finished += self.scheduler.deliver(old_planned, old_handle.tokens())
+        self._deliver_older(finished)
         self.stats.preemptions = self.scheduler.stats["preemptions"]
         return self._finish(finished)
 
@@ -220,15 +313,22 @@ class Engine:
         ends therefore decodes one token too many, which is dropped. Any other step (prompt
         portions, a preemption) first reads what is in flight and then runs synchronously."""
         finished: list[Request] = []
+        t0 = time.perf_counter()
         if self.stats.steps - self._checked_at >= self.CHECK_EVERY:
             self._check_kernels()
+        if self._nvtx:
+            _nvtx_push("plan")
         try:
-            planned = self.scheduler.plan()
-        except NeedsDrain:
-            finished += self._drain()
-            if self.scheduler.idle():
-                return self._finish(finished)
-            planned = self.scheduler.plan()
+            try:
+                planned = self.scheduler.plan()
+            except NeedsDrain:
+                finished += self._drain()
+                if self.scheduler.idle():
+                    return self._finish(finished)
+                planned = self.scheduler.plan()
+        finally:
+            if self._nvtx:
+                _nvtx_pop()
         if not planned:
             return self._finish(finished + self._drain())
         def entries_of(planned):
@@ -244,7 +344,7 @@ class Engine:
 
         decode_only = all(p.count == 1 and p.sample for p in planned)
         if self.graphs and decode_only:
-            return self._decode_step(planned, finished)
+            return self._decode_step(planned, finished, t0)
         entries, rows = entries_of(planned)
         # a captured step (decode-only, or a mixed one whose bucket has been captured) is queued
         # without waiting for the step before it; anything else runs eagerly and needs every
@@ -272,23 +372,29 @@ class Engine:
         if self.graphs and (decode_only or graph is not None):
             fed = [p.fed_on_device for p in planned]
             if decode_only:
+                bucket = self.step_fn.decode_graph(len(planned)).rows if self.trace is not None else None
+                rec = self._trace_begin(t0, "decode", len(planned), tokens_in_step, bucket)
                 handle = self.step_fn.launch_decode_graph(entries, rows, fed, reserved=True)
             else:
+                rec = self._trace_begin(t0, "mixed", len(planned), tokens_in_step,
+                                        [graph.tokens_cap, graph.seqs_cap])
                 handle = self.step_fn.launch_step_graph(graph, entries, rows, fed, reserved=True)
                 self.stats.graph_steps += 1
+            self._trace_end(rec)
             self.scheduler.launch(planned)
             self._inflight.append((planned, handle))
             self.stats.generated += len(rows)
-            while len(self._inflight) > self.depth:
-                old_planned, old_handle = self._inflight.popleft()
-                finished += self.scheduler.deliver(old_planned, old_handle.tokens())
+            self._deliver_older(finished)
         else:
+            rec = self._trace_begin(t0, "eager", len(planned), tokens_in_step, None)
             logits = self.step_fn.run(entries, commit=False)
-            sampled: list[int] = []
+            sampled_dev = None
             if rows:
                 packed = self.step_fn._upload(sampler.pack_rows(rows))
                 slots = self.step_fn._upload([self.cache.slot(p.req.rid) for p in planned if p.sample])
-                sampled = sampler.sample_packed(logits, packed, scatter=(slots, self.step_fn.last_token)).tolist()
+                sampled_dev = sampler.sample_packed(logits, packed, scatter=(slots, self.step_fn.last_token))
+            self._trace_end(rec)
+            sampled: list[int] = sampled_dev.tolist() if sampled_dev is not None else []
             self.stats.generated += len(sampled)
             finished += self.scheduler.commit(planned, sampled)
         self.stats.preemptions = self.scheduler.stats["preemptions"]
@@ -305,10 +411,15 @@ class Engine:
                 self.drain()
                 if stop is None or stop.is_set():
                     break
+                if self._nvtx:
+                    _nvtx_push("idle")
                 try:
                     self.scheduler.add(self.inbox.get(timeout=0.02))
                 except queue.Empty:
                     continue
+                finally:
+                    if self._nvtx:
+                        _nvtx_pop()
             self.step()
         self.stats.wall_s += time.perf_counter() - start
 

@@ -430,6 +430,10 @@ class StepFunction:
         self._ring_events = [None] * len(self._ring)
         self._ring_pos = 0
         self.steps = 0
+        if self.device.type == "cuda":
+            from tokenomos_b200 import ops
+            if ops.checks_enabled():         # the debug build: tell the kernels the pools' sizes
+                ops.set_check_bounds(cache.num_pages, cache.max_requests + 1)
 
     def _upload(self, values) -> torch.Tensor:
         """Host ints (a list, or a numpy int32 array) -> device int32 tensor through pinned

@@ -62,13 +62,15 @@ def configure(path: str | Path, work: str | torch.dtype | None = None) -> Config
     return Configured(arch, arch.config_class.from_dict(raw), work or torch.bfloat16)
 
 
-def load(path: str | Path, device: torch.device | str = "cuda", arch: Configured | None = None):
+def load(path: str | Path, device: torch.device | str = "cuda", arch: Configured | None = None,
+         tuning: Tuning | None = None):
     """The model in folder ``path`` (config.json + safetensors), chosen by its ``architectures``
-    name unless ``arch`` (from ``configure``) is given."""
+    name unless ``arch`` (from ``configure``) is given. ``tuning``: the kernel-choice thresholds
+    (default: the device's)."""
     conf = arch or configure(path)
     ckpt = Checkpoint(path)
     spec = conf.arch.declare(conf.config, ckpt.names())
-    rt = Runtime(conf.work, torch.device(device), Tuning.for_device(device))
+    rt = Runtime(conf.work, torch.device(device), tuning or Tuning.for_device(device))
     tensors = load_tensors(ckpt, spec.tensor_decls(), rt.dtype, rt.device, spec.scope)
     model = build_model(spec, tensors, rt)
     model.config = conf.config

@@ -14,7 +14,7 @@ from tokenomos_b200.ops import _lib
 from tokenomos_b200.ops._lib import BF16, F32, KernelError
 
 __all__ = [
-    "KernelError", "available", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
+    "KernelError", "available", "checks_enabled", "set_check_bounds", "checks_status", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
     "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
@@ -35,6 +35,36 @@ ATTENTION_MAX_HEAD_DIM = 256
 def available() -> None:
     """Raise unless the library loads and the current device can run it."""
     _lib.call("tk_check_device")
+
+
+def checks_enabled() -> bool:
+    """Whether the loaded library is the debug build whose kernels check the indices they follow
+    (``TOKENOMOS_B200_CHECKS=1`` at first use; csrc/checks.cuh)."""
+    return bool(_lib.call("tk_checks_enabled"))
+
+
+def set_check_bounds(pages: int, slots: int) -> None:
+    """What the index checks compare against: pages per paged pool, rows per state tensor."""
+    _lib.call("tk_checks_set_bounds", int(pages), int(slots))
+
+
+CHECKED_KERNELS = {1: "row gather", 2: "q/k norm + rope + cache write", 3: "attention (generic)",
+                   4: "attention (tensor cores)", 5: "gated short conv", 6: "projection with the conv inside"}
+CHECKED_INDICES = {1: "page", 2: "state row", 3: "table row"}
+
+
+def checks_status() -> str | None:
+    """None, or what the first index was that a kernel found outside its pool since the last call
+    (the kernel went on with the null page or row instead of following it)."""
+    import ctypes
+
+    word = (ctypes.c_int * 2)()
+    _lib.call("tk_checks_status", ctypes.cast(word, ctypes.c_void_p))
+    if word[0] == 0:
+        return None
+    kernel, what = divmod(word[0], 8)
+    return (f"{CHECKED_KERNELS.get(kernel, f'kernel {kernel}')}: {CHECKED_INDICES.get(what, 'index')} "
+            f"{word[1]} is outside its pool")
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -336,12 +366,13 @@ def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 
 def gemm_skinny_conv(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, taps: torch.Tensor,
                      conv_bias: torch.Tensor | None, state: torch.Tensor, seq_ctx: torch.Tensor,
-                     seq_slot: torch.Tensor) -> torch.Tensor:
+                     seq_slot: torch.Tensor, norm_eps: float = 0.0) -> torch.Tensor:
     """A gated short conv's in-projection with the conv in its epilogue, for a step whose tokens
     are one new token of a sequence each (decoding): ``x`` [M <= 16, K] bfloat16, ``w`` [3d, K]
     with rows in blocks of 24 (8 rows of B, of C and of X of the same 8 channels), ``bias`` in the
     same order; returns ``C * conv(B * X)`` [M, d] and moves each request's row of ``state``
-    [slots, W-1, d] on by its token. ``seq_ctx``, ``seq_slot``: [M]."""
+    [slots, W-1, d] on by its token. ``seq_ctx``, ``seq_slot``: [M]. ``norm_eps`` > 0 (at most 8
+    rows): ``x`` is an un-normed stream; see ``gemm_skinny``."""
     _cuda(x, w, bias, taps, conv_bias, state, seq_ctx, seq_slot)
     M, K = x.shape
     d, W = taps.shape
@@ -357,7 +388,7 @@ def gemm_skinny_conv(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None
     _lib.call("tk_gemm_skinny_conv", _ptr(x), x.stride(0), _ptr(w), w.stride(0),
               _ptr(_f32vec(bias, "bias", 3 * d)), _ptr(out), d, M, d, K, _ptr(taps),
               _ptr(_f32vec(conv_bias, "conv bias", d)), _ptr(state), _ptr(_i32(seq_ctx, "seq_ctx")),
-              _ptr(_i32(seq_slot, "seq_slot")), W, _stream())
+              _ptr(_i32(seq_slot, "seq_slot")), W, float(norm_eps), _stream())
     return out
 
 
@@ -389,20 +420,33 @@ def gemm_skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+SKINNY_FUSED_ROWS = 8
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-                out_dtype: torch.dtype | None = None, swiglu: bool = False) -> torch.Tensor:
+                out_dtype: torch.dtype | None = None, swiglu: bool = False, norm_eps: float = 0.0,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)`` for at most 16 rows of ``x`` (decode): a weight-streaming kernel.
     ``swiglu``: the rows of ``w`` alternate in runs of 8 (8 gate rows, the 8 up rows of the same
-    channels) and the result is ``silu(gate) * up`` of width ``N / 2``."""
-    _cuda(x, w, bias)
+    channels) and the result is ``silu(gate) * up`` of width ``N / 2``.
+    The two halves of a residual add + RMSNorm, for at most 8 rows: ``norm_eps`` > 0: ``x`` is the
+    un-normed stream and row r of the product is scaled by ``1 / sqrt(mean(x[r]^2) + norm_eps)``
+    (the norm's weight is expected in ``w``'s columns); ``residual`` [M, N]: the result is
+    ``residual + product`` (the product rounded to 16 bits first, the sum once)."""
+    _cuda(x, w, bias, residual)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)} against w {tuple(w.shape)}")
     width = N // 2 if swiglu else N
+    if residual is not None and (tuple(residual.shape) != (M, N) or residual.dtype != torch.bfloat16
+                                 or residual.stride(1) != 1):
+        raise KernelError(f"gemm_skinny: residual {tuple(residual.shape)} {residual.dtype} for a "
+                          f"[{M}, {N}] bfloat16 result")
     out = torch.empty(M, width, dtype=out_dtype or x.dtype, device=x.device)
     _lib.call("tk_gemm_skinny", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
-              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), _stream())
+              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), float(norm_eps), _ptr(residual),
+              residual.stride(0) if residual is not None else 0, _stream())
     return out
 
 

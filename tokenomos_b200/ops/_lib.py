@@ -25,6 +25,9 @@ _SIGNATURES = {
     "tk_check_device": [],
     "tk_built_for": [],
     "tk_set_pdl": [I],
+    "tk_checks_enabled": [],
+    "tk_checks_set_bounds": [I, I],
+    "tk_checks_status": [P],
     "tk_gather_rows": [P, P, P, I, I, I, I, P],
     "tk_gather_rows_select": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_add_rmsnorm": [P, L, P, P, F, P, F, P, P, I, I, I, P],
@@ -43,9 +46,9 @@ _SIGNATURES = {
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
-    "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, P],
+    "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, F, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
-    "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, P],
+    "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, F, P, L, P],
     "tk_gemm_skinny_tune": [I, I, I],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_gemm_tc_status": [],
@@ -99,7 +102,7 @@ def calls() -> int:
     return _calls
 
 
-_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
+_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled", "tk_checks_set_bounds", "tk_checks_status", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
 

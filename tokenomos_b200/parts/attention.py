@@ -53,6 +53,7 @@ class Attention:
             raise ValueError("attention: the gate is either fused into qkv or a projection of its own")
         if qkv.out_features != self.qkv_width + (-(-heads // 8) * 8 if gate_fused else 0):
             raise ValueError("attention: the fused projection does not match the head counts")
+        self.norm_folded = False
         self.head_layout = HeadLayout(heads, own_kv, head_dim, self.q_norm,
                                       self.k_norm if own_kv else None, self.eps)
 
@@ -75,6 +76,31 @@ class Attention:
             if self.gate is not None:
                 ops.head_gate(out, self.gate(x), self.heads, self.head_dim)
         return self.o(out.view(T, self.heads * self.head_dim))
+
+    # ---- the block's norm and residual add taken into the two products (parts.contract) ----
+
+    def fold_norm(self, weight: torch.Tensor) -> bool:
+        if self.qkv.weight.dtype != torch.bfloat16 or not self.tuning.fuse_norms or self.gate is not None:
+            return False
+        self.qkv.fold_columns(weight)
+        self.norm_folded = True
+        return True
+
+    def can_stream(self, rows: int, ctx: StepContext) -> bool:
+        return (self.norm_folded and rows <= ops.SKINNY_FUSED_ROWS and self.qkv.in_features % 8 == 0
+                and self.qkv.out_features % 8 == 0 and self.o.in_features % 8 == 0)
+
+    def forward_stream(self, stream: torch.Tensor, eps: float, ctx: StepContext, call: int) -> torch.Tensor:
+        self.qkv.note("skinny+norm")
+        self.o.note("skinny+add")
+        T = stream.shape[0]
+        proj = ops.gemm_skinny(stream, self.qkv.weight, self.qkv.bias, norm_eps=eps)
+        n = self.qkv_width
+        out = self._core(proj[:, :n] if self.gate_fused else proj, ctx, call)
+        if self.gate_fused:
+            ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
+        return ops.gemm_skinny(out.view(T, self.heads * self.head_dim), self.o.weight, self.o.bias,
+                               residual=stream)
 
     def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
               out: torch.Tensor | None = None) -> torch.Tensor:

@@ -29,13 +29,51 @@ class PreNormBlock:
         self.capture_safe = all(getattr(part, "capture_safe", False)
                                 for part in (mixer, ffn, pre_mixer, pre_ffn, post_mixer, post_ffn)
                                 if part is not None)
+        # A sublayer whose part offers it runs without a norm kernel when the step is small:
+        # the pre-norm's weight moves into the part's first projection now (``fold_norm``), the
+        # norm that stays has weight one, and ``forward_stream`` takes the un-normed stream and
+        # returns stream + part(norm(stream)) with both the statistics and the add inside its
+        # own kernels. Without post-norms only: they sit between the part and the add.
+        self.eps_mixer = self.eps_ffn = None
+        if post_mixer is None and post_ffn is None:
+            self.pre_mixer, self.eps_mixer = self._fold(pre_mixer, mixer)
+            self.pre_ffn, self.eps_ffn = self._fold(pre_ffn, ffn)
+
+    @staticmethod
+    def _fold(norm, part):
+        """(the norm that is left, eps if ``part`` took the weight else None)."""
+        if not (hasattr(norm, "folded") and hasattr(part, "fold_norm") and hasattr(part, "forward_stream")):
+            return norm, None
+        weight, eps, unit = norm.folded()
+        return (unit, eps) if part.fold_norm(weight) else (norm, None)
+
+    @staticmethod
+    def _stream(h, residual):
+        """The residual stream with ``h`` (a part's output not yet added, or None) in it."""
+        if h is None:
+            return residual
+        if residual is None:
+            return h if h.is_contiguous() else h.contiguous()
+        return ops.add_rmsnorm(h, residual, None, 0.0)[1]
 
     def forward(self, h, residual, pending, ctx: StepContext, call: int):
-        """``pending``: the previous block's post-norm still to apply to ``h`` before it joins
-        the stream. Returns this block's output, the stream and its own pending post-norm."""
-        x, residual = self.pre_mixer.add_norm(h, residual, pending)
-        m = self.mixer.forward(x, ctx, call)
-        x, residual = self.pre_ffn.add_norm(m, residual, self.post_mixer)
+        """``h``: the block before's output still to be added to ``residual`` (None: it is in the
+        stream already); ``pending``: that block's post-norm still to apply to ``h``. Returns this
+        block's output (or None), the stream and its own pending post-norm."""
+        rows = (h if h is not None else residual).shape[0]
+        if self.eps_mixer is not None and pending is None and self.mixer.can_stream(rows, ctx):
+            residual = self.mixer.forward_stream(self._stream(h, residual), self.eps_mixer, ctx, call)
+            h = None
+        else:
+            if h is None:
+                h, residual = residual, None
+            x, residual = self.pre_mixer.add_norm(h, residual, pending)
+            h = self.mixer.forward(x, ctx, call)
+        if self.eps_ffn is not None and self.ffn.can_stream(rows):
+            return None, self.ffn.forward_stream(self._stream(h, residual), self.eps_ffn), None
+        if h is None:
+            h, residual = residual, None
+        x, residual = self.pre_ffn.add_norm(h, residual, self.post_mixer)
         return self.ffn.forward(x), residual, self.post_ffn
 
 
@@ -112,6 +150,8 @@ class Stack:
         """Float32 logits [len(rows), vocab] at token rows ``rows`` (int32) of the step; None:
         at every row, in order."""
         h, residual, pending = out
+        if h is None:                    # the last block's output is in the stream already
+            h, residual = residual, None
         if rows is not None:
             h = ops.gather_rows(h, rows)
             if residual is not None:

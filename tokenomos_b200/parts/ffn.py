@@ -24,6 +24,7 @@ class SwiGLU:
         if gate_up.out_features != 2 * down.in_features:
             raise ValueError("SwiGLU: gate_up must be twice as wide as down's input")
         self.gate_up, self.down, self.run = gate_up, down, run
+        self.norm_folded = False
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w = self.gate_up.weight
@@ -35,6 +36,27 @@ class SwiGLU:
         else:
             act = ops.swiglu(self.gate_up(x), self.run)
         return self.down(act)
+
+
+    # ---- the block's norm and residual add taken into the two products (parts.contract) ----
+
+    def fold_norm(self, weight: torch.Tensor) -> bool:
+        if self.gate_up.weight.dtype != torch.bfloat16 or not self.gate_up.tuning.fuse_norms:
+            return False
+        self.gate_up.fold_columns(weight)
+        self.norm_folded = True
+        return True
+
+    def can_stream(self, rows: int) -> bool:
+        t = self.gate_up.tuning
+        return (self.norm_folded and self.run == RUN and rows <= min(ops.SKINNY_FUSED_ROWS, t.swiglu_fused_rows)
+                and self.gate_up.in_features % 8 == 0 and self.down.in_features % 8 == 0)
+
+    def forward_stream(self, stream: torch.Tensor, eps: float) -> torch.Tensor:
+        self.gate_up.note("skinny+norm")
+        self.down.note("skinny+add")
+        act = ops.gemm_skinny(stream, self.gate_up.weight, self.gate_up.bias, swiglu=True, norm_eps=eps)
+        return ops.gemm_skinny(act, self.down.weight, self.down.bias, residual=stream)
 
 
 def interleave_rows(gate: torch.Tensor, up: torch.Tensor, run: int) -> torch.Tensor:

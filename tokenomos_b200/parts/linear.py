@@ -45,6 +45,16 @@ class Linear:
         bias = torch.cat(biases) if biases[0] is not None else None
         return cls(torch.cat(weights, dim=0), bias, tuning)
 
+    def note(self, route: str) -> None:
+        """Count a product a part ran through a kernel of its own choice instead of ``route``."""
+        self.routed[route] = self.routed.get(route, 0) + 1
+
+    def fold_columns(self, scale: torch.Tensor) -> None:
+        """``weight[n, k] *= scale[k]`` (the product formed in 32-bit, rounded once): a norm's
+        weight taken into the projection that follows the norm."""
+        w = self.weight
+        self.weight = (w.float() * scale.float().to(w.device)[None, :]).to(w.dtype).contiguous()
+
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         w = self.weight
         if x.dtype != w.dtype:

@@ -33,6 +33,11 @@ class RMSNorm:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         return self.add_norm(x, None)[0]
 
+    def folded(self) -> tuple[torch.Tensor, float, "RMSNorm"]:
+        """For a block that takes this norm's weight into the projection after it: the weight,
+        eps, and the norm that is left (the same statistics, weight one)."""
+        return self.weight, self.eps, RMSNorm(torch.ones_like(self.weight), self.eps)
+
 
 @register("norm", "rmsnorm")
 def build_rmsnorm(params: dict, tensors: dict, rt: Runtime) -> RMSNorm:

@@ -7,6 +7,7 @@ kind is all it takes to use it in a ``ModelSpec``; the framework's files do not 
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable
 
@@ -35,7 +36,11 @@ class Tuning:
     ``decode_ctas_per_sm`` CTAs per SM (three fit by shared memory, and a few waves of them even
     out the last, partial one).
     ``conv_tile``: tokens a conv tile walks in order (a 2,048-token portion of 2,048 channels:
-    18 us at 8, 33 us at 32)."""
+    18 us at 8, 33 us at 32).
+    ``fuse_norms``: 16-bit models fold each pre-norm's weight into the columns of the projection
+    that follows it when they are built, and steps of at most ``ops.SKINNY_FUSED_ROWS`` decoded
+    tokens then run without norm kernels (``parts.block.PreNormBlock``); the environment variable
+    ``TOKENOMOS_B200_FUSE_NORMS=0`` turns it off for a whole process."""
 
     sm_count: int = 148
     skinny_rows: int = 8
@@ -52,13 +57,16 @@ class Tuning:
     decode_min_keys: int = 128
     decode_ctas_per_sm: int = 12
     conv_tile: int = 8
+    fuse_norms: bool = True
 
     @classmethod
     def for_device(cls, device) -> "Tuning":
         device = torch.device(device)
+        fuse = os.environ.get("TOKENOMOS_B200_FUSE_NORMS", "1") != "0"
         if device.type == "cuda" and torch.cuda.is_available():
-            return cls(sm_count=torch.cuda.get_device_properties(device).multi_processor_count)
-        return cls()
+            return cls(sm_count=torch.cuda.get_device_properties(device).multi_processor_count,
+                       fuse_norms=fuse)
+        return cls(fuse_norms=fuse)
 
 
 DEFAULT_TUNING = Tuning()

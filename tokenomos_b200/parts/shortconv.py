@@ -35,6 +35,7 @@ class ShortConv:
             raise ValueError(f"short conv: {self.width} taps; the conv kernels take {lo} to {hi}")
         if in_proj.out_features != 3 * self.dim or out_proj.in_features != self.dim:
             raise ValueError("short conv: projections do not match the conv's channel count")
+        self.norm_folded = False
         # tokens a conv tile walks in order; any value >= width - 1 is correct
         self.tile = max(in_proj.tuning.conv_tile, self.width - 1)
 
@@ -54,6 +55,29 @@ class ShortConv:
         y = ops.conv_gated(bcx, self.conv, self.conv_bias, state,
                            ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run)
         return self.out_proj(y)
+
+
+    # ---- the block's norm and residual add taken into the two products (parts.contract) ----
+
+    def fold_norm(self, weight: torch.Tensor) -> bool:
+        if self.in_proj.weight.dtype != torch.bfloat16 or not self.in_proj.tuning.fuse_norms:
+            return False
+        self.in_proj.fold_columns(weight)
+        self.norm_folded = True
+        return True
+
+    def can_stream(self, rows: int, ctx: StepContext) -> bool:
+        return (self.norm_folded and self.run == RUN and ctx.host.decode_only
+                and rows <= ops.SKINNY_FUSED_ROWS and self.in_proj.in_features % 8 == 0
+                and self.dim % 8 == 0)
+
+    def forward_stream(self, stream: torch.Tensor, eps: float, ctx: StepContext, call: int) -> torch.Tensor:
+        self.in_proj.note("skinny+norm")
+        self.out_proj.note("skinny+add")
+        state = ctx.states[(call, "conv")]
+        y = ops.gemm_skinny_conv(stream, self.in_proj.weight, self.in_proj.bias, self.conv, self.conv_bias,
+                                 state, ctx.seq_ctx, ctx.seq_slot, norm_eps=eps)
+        return ops.gemm_skinny(y, self.out_proj.weight, self.out_proj.bias, residual=stream)
 
 
 def interleave_bcx(w: torch.Tensor, run: int) -> torch.Tensor:
