@@ -337,8 +337,13 @@ def conv_ref(bcx, taps, bias, prev):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("W, d, with_bias", [(2, 100, True), (3, 64, False), (4, 96, True), (7, 300, False)])
-def test_conv_gated_mixed_batch_and_state(dtype, W, d, with_bias):
+@pytest.mark.parametrize("tile", [32, 16, 7])
+@pytest.mark.parametrize("W, d, with_bias", [(2, 100, True), (3, 64, False), (4, 96, True), (7, 300, False),
+                                             (8, 2048, True), (3, 136, False)])
+def test_conv_gated_mixed_batch_and_state(dtype, W, d, with_bias, tile):
+    """Tiles of 32 tokens take the kernel that walks a tile's tokens in order; tiles of at most 16
+    (given as ``tile_cap``) the tiled kernel: one thread per token and 16 bytes of channels, inputs
+    through shared memory. Channel counts that are and are not whole 16-byte chunks."""
     from tokenomos_b200 import ops
     slots = 6
     taps = torch.randn(d, W)
@@ -352,14 +357,15 @@ def test_conv_gated_mixed_batch_and_state(dtype, W, d, with_bias):
     cu = [0]
     for _, _, n in seqs:
         cu.append(cu[-1] + n)
-    tile = 32
-    tseq, toff, tn = [], [], []
+    tseq, toff, tn, ttok0 = [], [], [], []
     for s, (_, _, n) in enumerate(seqs):
         for o in range(0, n, tile):
-            tseq.append(s), toff.append(o), tn.append(min(tile, n - o))
+            tseq.append(s), toff.append(o), tn.append(min(tile, n - o)), ttok0.append(cu[s] + o)
+    # (each tile's first token in the batch is optional: given for the tile of 16, left out for 7)
     out = ops.conv_gated(dev(bcx), dev(taps), dev(bias) if with_bias else None, state, i32(cu),
                          i32([c for _, c, _ in seqs]), i32([s for s, _, _ in seqs]),
-                         i32(tseq), i32(toff), i32(tn))
+                         i32(tseq), i32(toff), i32(tn), 0, tile if tile <= 16 else 0,
+                         i32(ttok0) if tile == 16 else None)
     new_state = state.cpu()
     touched = set()
     for s, (slot, ctx, n) in enumerate(seqs):
@@ -379,9 +385,11 @@ def test_conv_gated_mixed_batch_and_state(dtype, W, d, with_bias):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_conv_gated_cut_anywhere_equals_whole(dtype):
+@pytest.mark.parametrize("tile", [32, 16, 5])
+def test_conv_gated_cut_anywhere_equals_whole(dtype, tile):
     """A sequence fed in portions (down to one token) through its state row gives what the whole
-    sequence gives: bit for bit, since every output sums the same values in the same order."""
+    sequence gives: bit for bit, since every output sums the same values in the same order; in
+    both forms of the kernel (tiles of 32: the walking one; up to 16: the tiled one)."""
     from tokenomos_b200 import ops
     W, d, T = 4, 72, 57
     taps, bcx = torch.randn(d, W), torch.randn(T, 3 * d).to(dtype)
@@ -391,10 +399,10 @@ def test_conv_gated_cut_anywhere_equals_whole(dtype):
         outs = []
         for a, b in zip(cuts[:-1], cuts[1:]):
             n = b - a
-            tiles = [(0, o, min(32, n - o)) for o in range(0, n, 32)]
+            tiles = [(0, o, min(tile, n - o)) for o in range(0, n, tile)]
             outs.append(ops.conv_gated(dev(bcx[a:b]), dev(taps), None, state, i32([0, n]), i32([a]),
                                        i32([1]), i32([t[0] for t in tiles]), i32([t[1] for t in tiles]),
-                                       i32([t[2] for t in tiles])))
+                                       i32([t[2] for t in tiles]), 0, tile if tile <= 16 else 0))
         return torch.cat(outs)
 
     whole = run([0, T])
@@ -421,14 +429,14 @@ def test_conv_gated_blocked_columns_equal_plain_columns():
         tiles = [(s, o, min(8, n - o)) for s, (_, _, n) in enumerate(seqs) for o in range(0, n, 8)]
         state0 = torch.randn(slots, W - 1, d).to(dtype)
         outs, states = [], []
-        for rows, block in ((bcx, 0), (blocked, 8)):
+        for rows, block, cap in ((bcx, 0, 0), (blocked, 8, 0), (bcx, 0, 8), (blocked, 8, 8)):
             state = dev(state0).clone()
             outs.append(ops.conv_gated(dev(rows), dev(taps), dev(bias), state, i32(cu),
                                        i32([c for _, c, _ in seqs]), i32([s for s, _, _ in seqs]),
                                        i32([t[0] for t in tiles]), i32([t[1] for t in tiles]),
-                                       i32([t[2] for t in tiles]), block))
+                                       i32([t[2] for t in tiles]), block, cap))
             states.append(state)
-        assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
+        assert all(torch.equal(o, outs[0]) for o in outs) and all(torch.equal(st, states[0]) for st in states)
 
 
 @pytest.mark.parametrize("W, d, K, M, with_bias", [(3, 64, 128, 8, False), (2, 40, 72, 5, True),

@@ -108,11 +108,15 @@ __global__ void qk_norm_rope_write_vec_kernel(
     const int hpw = 32 / lph;                      // heads a warp takes per pass
     const int sub = lane / lph, c = (lane % lph) * VEC;
     const T* row = qkv + (size_t)t * qkv_stride;
-    // this thread's share of the first pass is asked for before anything else: its trip to
-    // memory runs beside those for the position, the sequence and the page
+    // this thread's share of the first two passes is asked for before anything else: its trips
+    // to memory run beside those for the position, the sequence and the page (a prompt portion's
+    // block takes all heads of a token in two passes: no load then waits for another)
     const int h_first = (blockIdx.y * nwarp + warp) * hpw;
-    uint4 raw_first = make_uint4(0u, 0u, 0u, 0u);
+    const int h_step = gridDim.y * nwarp * hpw;
+    uint4 raw_first = make_uint4(0u, 0u, 0u, 0u), raw_second = make_uint4(0u, 0u, 0u, 0u);
     if (h_first + sub < heads) raw_first = *reinterpret_cast<const uint4*>(row + (size_t)(h_first + sub) * D + c);
+    if (h_first + h_step + sub < heads)
+        raw_second = *reinterpret_cast<const uint4*>(row + (size_t)(h_first + h_step + sub) * D + c);
     const int pos = positions[t];
     const int seq_of_t = Hkv > 0 ? tok_seq[t] : 0;
     // (the page is looked up before the angles are computed, not after: its trip runs beside them)
@@ -131,11 +135,11 @@ __global__ void qk_norm_rope_write_vec_kernel(
     const int half_lanes = half / VEC;
     // the lane that holds this chunk's partner in the rotation (itself beyond the rotary width)
     const int partner = c < half ? lane + half_lanes : (c < R ? lane - half_lanes : lane);
-    for (int h0 = h_first; h0 < heads; h0 += gridDim.y * nwarp * hpw) {
+    for (int h0 = h_first; h0 < heads; h0 += h_step) {
         const int hh = h0 + sub;
         const bool live = hh < heads;
-        uint4 raw = raw_first;
-        if (h0 != h_first) {
+        uint4 raw = h0 == h_first ? raw_first : raw_second;
+        if (h0 > h_first + h_step) {
             raw = make_uint4(0u, 0u, 0u, 0u);
             if (live) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * D + c);
         }

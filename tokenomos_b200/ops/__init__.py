@@ -341,10 +341,14 @@ def conv_min_tile(width: int) -> int:
 def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
                state: torch.Tensor, cu: torch.Tensor, seq_ctx: torch.Tensor,
                seq_slot: torch.Tensor, tile_seq: torch.Tensor, tile_off: torch.Tensor,
-               tile_n: torch.Tensor, block: int = 0) -> torch.Tensor:
+               tile_n: torch.Tensor, block: int = 0, tile_cap: int = 0,
+               tile_tok0: torch.Tensor | None = None) -> torch.Tensor:
     """Gated short conv of ``bcx`` [T, 3d] = (B | C | X): returns ``C * conv(B * X)`` [T, d] and
     replaces each sequence's row of ``state`` [slots, W-1, d]. ``weight`` [d, W] float32.
-    ``block`` b > 0: a row of ``bcx`` holds runs of b channels of B, of C and of X in turn."""
+    ``block`` b > 0: a row of ``bcx`` holds runs of b channels of B, of C and of X in turn.
+    ``tile_cap``: the most tokens a tile has, if the caller knows (up to 16 a faster kernel takes
+    the call); every tile but a portion's last has at least W - 1 tokens. ``tile_tok0``: each
+    tile's first token in the batch, if the caller has it (it spares that kernel a lookup)."""
     _cuda(bcx, weight, bias, state, cu, seq_ctx, seq_slot, tile_seq, tile_off, tile_n)
     T, three_d = bcx.shape
     d = three_d // 3
@@ -359,8 +363,9 @@ def conv_gated(bcx: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
     _lib.call("tk_conv_gated", _ptr(bcx), bcx.stride(0), d, _ptr(weight), _ptr(_f32vec(bias, "conv bias", d)),
               _ptr(state), _ptr(out), _ptr(_i32(cu, "cu")), _ptr(_i32(seq_ctx, "seq_ctx")),
               _ptr(_i32(seq_slot, "seq_slot")), _ptr(_i32(tile_seq, "tile_seq")),
-              _ptr(_i32(tile_off, "tile_off")), _ptr(_i32(tile_n, "tile_n")), tile_seq.numel(), W,
-              int(block), _dtype_code(bcx), _stream())
+              _ptr(_i32(tile_off, "tile_off")), _ptr(_i32(tile_n, "tile_n")),
+              _ptr(_i32(tile_tok0, "tile_tok0")) if tile_tok0 is not None else None, tile_seq.numel(), W,
+              int(block), int(tile_cap), _dtype_code(bcx), _stream())
     return out
 
 

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
     "tk_conv_min_tile": [I],
-    "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, F, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, F, P, L, P],

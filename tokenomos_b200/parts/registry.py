@@ -35,8 +35,8 @@ class Tuning:
     on the GPU (never below ``decode_min_keys`` keys each); never more than
     ``decode_ctas_per_sm`` CTAs per SM (three fit by shared memory, and a few waves of them even
     out the last, partial one).
-    ``conv_tile``: tokens a conv tile walks in order (a 2,048-token portion of 2,048 channels:
-    18 us at 8, 33 us at 32).
+    ``conv_tile``: tokens of a conv tile; up to 16 the tiled kernel takes them (one thread per
+    token and 8 channels, a 2,048-token portion of 2,048 channels at memory speed).
     ``fuse_norms``: 16-bit models fold each pre-norm's weight into the columns of the projection
     that follows it when they are built, and steps of at most ``ops.SKINNY_FUSED_ROWS`` decoded
     tokens then run without norm kernels (``parts.block.PreNormBlock``); the environment variable
@@ -56,7 +56,7 @@ class Tuning:
     decode_fill: int = 256
     decode_min_keys: int = 128
     decode_ctas_per_sm: int = 12
-    conv_tile: int = 8
+    conv_tile: int = 16
     fuse_norms: bool = True
 
     @classmethod

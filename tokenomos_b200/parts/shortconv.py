@@ -51,9 +51,9 @@ class ShortConv:
                                      state, ctx.seq_ctx, ctx.seq_slot)
             return self.out_proj(y)
         bcx = self.in_proj(x)
-        seq, _, off, n = ctx.tiles(self.tile)
+        seq, tok0, off, n = ctx.tiles(self.tile)
         y = ops.conv_gated(bcx, self.conv, self.conv_bias, state,
-                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run)
+                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run, self.tile, tok0)
         return self.out_proj(y)
 
 
