@@ -312,7 +312,8 @@ def device_prefill(model, cfg, page: int, reps: int = 3, tokens: int = PROMPT) -
 
     eager_ms = timed(eager)
     step_fn.capture_after = 0            # as after Engine.warmup(): the shape is captured
-    ms = timed(captured) if eng.graphs else eager_ms
+    fits = eng.graphs and step_fn.step_graph_for([StepEntry("probe", ids, [tokens - 1])]) is not None
+    ms = timed(captured) if fits else eager_ms       # (no captured shape beyond 16,384 tokens)
     flops = prefill_flops(cfg.to_dict(), tokens)
     del eng
     torch.cuda.empty_cache()

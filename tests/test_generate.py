@@ -133,6 +133,10 @@ def test_warmup_records_every_step_shape_before_the_first_request(model_folders)
         assert decode == {1, 2, 4, 5}                          # buckets up to the 5 slots
         assert mixed == {(32, 4), (32, 16)}                    # 24 tokens at most, 5 + 1 sequences
         assert llm.engine.stats.steps == 0
+        # the runs that warm a shape up work on an empty layout; what the sampler made of their
+        # logits must not be held against the first real step
+        from tokenomos_b200 import ops
+        assert ops.sample_status() == 0
         warm = llm.generate(prompts, p)
         assert set(step_fn._graphs) == decode and set(step_fn._step_graphs) == mixed
         assert llm.engine.stats.graph_steps > 0

@@ -49,6 +49,16 @@ def _no_collection():
             gc.enable()
 
 
+def _forget_capture_run() -> None:
+    """The run that warms a step up before it is captured works on an all-zero layout: no tile,
+    every token of the dummy sequence, outputs that no kernel wrote. What the sampler made of
+    such logits (a row without a finite value is reported) says nothing about a real step."""
+    from tokenomos_b200 import ops
+
+    torch.cuda.synchronize()
+    ops.sample_status()
+
+
 class _Tiles:
     """Cuts the step's sequences into runs of at most ``size`` tokens, on demand, once per size."""
 
@@ -199,6 +209,7 @@ class _DecodeGraph:
             self.body(model)
         self.launches = _lib.calls() - before
         self.graph = graph
+        _forget_capture_run()
 
 
 class DecodeHandle:
@@ -327,6 +338,7 @@ class _StepGraph:
             self.body(model)
         self.launches = _lib.calls() - before
         self.graph = graph
+        _forget_capture_run()
 
     def fill(self, turn: int, entries: list[StepEntry], states: list, sampling_rows: list[tuple],
              fed_on_device: list[bool]) -> int:
