@@ -390,6 +390,124 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
     print(f"profile case done: {mode} layers={layers} batch={batch} ctx={ctx} steps={steps}")
 
 
+def ingraph_table(layers: int, batch: int, ctx: int, page: int) -> None:
+    """What each kind of kernel costs *inside* the captured decode step, where launches overlap
+    through programmatic dependent launch and a kernel's cold, serialised time under a profiler
+    says little: the step is captured once whole and once per kind with that kind's launches
+    left out (their outputs stay unwritten, which changes no launch that follows), each graph is
+    replayed and timed with CUDA events, and the difference is the kind's cost in the step.
+    Prints one line per kind: launches, microseconds, microseconds per launch, share, and for
+    matrix products the bytes of the matrix over that time."""
+    import tempfile
+
+    import torch
+    import torch.nn.functional as F
+
+    import tokenomos_b200.parts.linear as linear_part
+    from tokenomos_b200 import models
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.engine.step import StepFunction
+    from tokenomos_b200.ops import _lib
+    from tokenomos_b200.sampling import sampler
+
+    with tempfile.TemporaryDirectory(prefix="tokenomos_b200_profile_") as tmp:
+        folder = Path(tmp) / "model"
+        write_folder(folder, layers)
+        model = models.load(folder, "cuda", models.configure(folder, work="bf16"))
+    pages = batch * (-(-(ctx + 64) // page)) + 2
+    cache = CacheManager(model.state_specs(), page, pages, batch, torch.bfloat16, "cuda", max_len=ctx + 64)
+    for r in range(batch):
+        cache.admit(r)
+        cache.extend(r, ctx + 1)
+        cache.commit(r, ctx)
+    real_call, real_linear, real_mm = _lib.call, F.linear, torch.mm
+    seen: dict[str, int] = {}
+    sizes: dict[str, int] = {}
+
+    def key_of(name, args):
+        if name in ("tk_gemm_skinny", "tk_gemm_tc_decode", "tk_gemm_skinny_conv"):
+            extra = ""
+            if name == "tk_gemm_skinny":
+                extra = (" swiglu" if args[11] else "") + (" +norm" if args[12] > 0 else "") + (" +add" if args[13] else "")
+            k = f"{name[3:]}[{args[8]}x{args[9]}]{extra}"
+            sizes[k] = 2 * args[8] * args[9]
+            return k
+        return name[3:]
+
+    def timed_step(skip=None, record=False) -> float:
+        def call(name, *args):
+            k = key_of(name, args)
+            if record and name not in _lib._QUERIES:
+                seen[k] = seen.get(k, 0) + 1
+            return 0 if k == skip else real_call(name, *args)
+
+        def lin(x, w, b=None):
+            k = f"library[{w.shape[0]}x{w.shape[1]}]"
+            sizes[k] = 2 * w.shape[0] * w.shape[1]
+            if record:
+                seen[k] = seen.get(k, 0) + 1
+            if k == skip:
+                return torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+            return real_linear(x, w, b)
+
+        def mm(a, b, out_dtype=None):
+            k = f"library[{b.shape[1]}x{b.shape[0]}]"
+            sizes[k] = 2 * b.shape[0] * b.shape[1]
+            if record:
+                seen[k] = seen.get(k, 0) + 1
+            if k == skip:
+                return torch.empty(a.shape[0], b.shape[1], dtype=out_dtype or a.dtype, device=a.device)
+            return real_mm(a, b, out_dtype=out_dtype) if out_dtype else real_mm(a, b)
+
+        _lib.call, linear_part.F.linear, torch.mm = call, lin, mm
+        try:
+            graph = StepFunction(model, cache).decode_graph(batch)
+        finally:
+            _lib.call, linear_part.F.linear, torch.mm = real_call, real_linear, real_mm
+        h = graph.host_np[0]
+        states = [cache.requests[r] for r in range(batch)]
+        for name, values in (("positions", [st.length for st in states]), ("seq_ctx", [st.length for st in states]),
+                             ("seq_slot", [st.slot for st in states]), ("ids_host", [5] * batch),
+                             ("use_prev", [0] * batch)):
+            o, _ = graph.off[name]
+            h[o:o + batch] = values
+        o, _ = graph.off["sampling"]
+        sampler.pack_rows_into(h[o:o + 6 * graph.rows], [(0.0, 1.0, 0, 0.0, 0, 0)] * batch, graph.rows)
+        for grp in graph.groups:
+            o, _ = graph.off[("table", grp)]
+            for i, st in enumerate(states):
+                row = st.tables[grp]
+                h[o + i * graph.width:o + i * graph.width + len(row)] = row
+        graph.dev.copy_(graph.host[0])
+        torch.cuda.synchronize()
+        for _ in range(5):
+            graph.graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(20):
+                graph.graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end) / 20 * 1e3)
+        return statistics.median(times)
+
+    whole = timed_step(record=True)
+    # the step is run once to warm up and once to be captured: every kind was counted twice
+    print(f"decode step, batch {batch}, {ctx} cached positions, {layers} layers: {whole:.1f} us, "
+          f"{sum(seen.values()) // 2} launches")
+    rows = []
+    for k, n in seen.items():
+        rows.append((whole - timed_step(skip=k), k, n // 2))
+    print(f"  {'kind':46s} launches      us   us each   share   matrix GB/s")
+    for cost, k, n in sorted(rows, reverse=True):
+        rate = f"{sizes[k] * n / cost / 1e3:10.0f}" if k in sizes and cost > 0 else ""
+        print(f"  {k:46s} {n:6d} {cost:9.1f} {cost / max(n, 1):8.2f} {100 * cost / whole:6.1f}%  {rate}")
+    print(f"  the kinds sum to {sum(r[0] for r in rows):.1f} us of the step's {whole:.1f}")
+
+
 def run_sweep(model, cfg, page: int, pk: dict) -> int:
     """Decode at other batch sizes and context lengths, prefill at other lengths: one JSON line
     of points, each with its fraction of the roofline (decode: bytes the step must read over the
@@ -658,8 +776,9 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run a whole serving workload of BASELINE.json (configs[3] / configs[4]) instead")
-    ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill"],
-                    help="run only a small case for a profiler (see profile_case) and exit")
+    ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill", "ingraph"],
+                    help="run only a small case for a profiler (see profile_case) and exit; ingraph: "
+                         "the cost of each kind of kernel inside the captured decode step (ingraph_table)")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -687,6 +806,9 @@ def main() -> int:
 
     torch.cuda.set_device(0)
     ops.available()
+    if args.profile == "ingraph":
+        ingraph_table(args.layers, args.batch, args.ctx, args.page)
+        return 0
     if args.profile:
         profile_case(args.profile, args.layers, args.batch, args.ctx, args.steps, args.page)
         return 0
