@@ -349,23 +349,11 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
 
 }  // namespace
 
-// Tuning knobs (tk_gemm_skinny_tune; 0 = choose by shape): slices in flight per warp (2 or 4), the
-// most warps a CTA may have, and the number of 16-row CTAs below which a matrix is cut into
-// 8-row CTAs instead. Measured on a B200 in CUDA graphs at 1 and 8 tokens (2048- and 8192-wide K):
-// two slices in flight beat four (75 instead of 126 registers: three CTAs of 8 warps per SM
-// instead of two, whose load, compute and reduce phases overlap); a tall matrix (300 or more CTAs) wants 8 warps per CTA, a
-// short one 16 (more of K in flight per CTA); 8-row CTAs only pay below half a wave.
-static int g_unroll = 0, g_max_warps = 0, g_r8_below = -1;
-
-TK_API int tk_gemm_skinny_tune(int unroll, int max_warps, int r8_below) {
-    TK_CHECK_ARG((unroll == 0 || unroll == 2 || unroll == 4) && max_warps >= 0 && max_warps <= 16,
-                 "gemm_skinny_tune: unroll 0, 2 or 4; 0..16 warps");
-    g_unroll = unroll;
-    g_max_warps = max_warps;
-    g_r8_below = r8_below;
-    return 0;
-}
-
+// How the launch is shaped, measured on a B200 in CUDA graphs at 1 and 8 tokens (2048- and
+// 8192-wide K): two slices in flight per warp beat four (75 instead of 126 registers: three CTAs
+// of 8 warps per SM instead of two, whose load, compute and reduce phases overlap); a tall matrix
+// (300 or more CTAs) wants 8 warps per CTA, a short one 16 (more of K in flight per CTA); 8-row
+// CTAs only pay below half a wave.
 // x: [M, K] bfloat16, rows `ldx` apart; w: [N, K] bfloat16, rows `ldw` apart; out: [M, N]
 // bfloat16 or float (out_dtype); M <= 16; K, ldx, ldw multiples of 8 and 16-byte aligned bases.
 // swiglu != 0: w holds blocks of 8 gate rows followed by the 8 up rows of the same channels
@@ -393,13 +381,13 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
     // between one and two waves of 16-row CTAs, and a short K: 8-row CTAs with four slices in
     // flight (the 3072 x 2048 qkv projection: 3.5 us against 4.9)
     const bool mid = !swiglu && ctas16 >= 160 && ctas16 < 296 && K <= 4096;
-    const int unroll = g_unroll ? g_unroll : (mid ? 4 : 2);
-    const int max_warps = g_max_warps ? g_max_warps : (ctas16 >= 296 || mid ? 8 : 16);
+    const int unroll = mid ? 4 : 2;
+    const int max_warps = ctas16 >= 296 || mid ? 8 : 16;
     int warps = (slices + unroll - 1) / unroll;      // every slice of a warp in flight at once
     warps = warps < 1 ? 1 : (warps > max_warps ? max_warps : warps);
     const int threads = warps * 32;
     // very few rows: 8 per CTA so that the grid still covers the GPU
-    const bool r8 = !swiglu && (g_r8_below >= 0 ? ctas16 < g_r8_below : (mid || ctas16 < 74));
+    const bool r8 = !swiglu && (mid || ctas16 < 74);
     const int blocks = r8 ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
     const int MT = M <= 8 ? 8 : 16;
     const size_t smem = ((size_t)warps * ROWS * MT + (norm ? (size_t)warps * MT + MT : 0)) * sizeof(float);
@@ -465,7 +453,7 @@ TK_API int tk_gemm_skinny_conv(const void* x, int64_t ldx, const void* w, int64_
     const int unroll = 2;
     // (90 registers: two CTAs of 8 warps per SM. Bounding it to 80 for three made the decode step
     // slower, 0.842 ms against 0.816 ms.)
-    const int max_warps = g_max_warps ? g_max_warps : (blocks >= 200 ? 8 : 16);
+    const int max_warps = blocks >= 200 ? 8 : 16;
     int warps = (slices + unroll - 1) / unroll;
     warps = warps < 1 ? 1 : (warps > max_warps ? max_warps : warps);
     const int MT = M <= 8 ? 8 : 16;

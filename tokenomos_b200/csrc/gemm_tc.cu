@@ -8,9 +8,9 @@
 // Decode ("weights as A"): A = W [N, K], B = x [tokens, K]; the 128-row MMA tile is filled with
 // weight rows and the few tokens are the MMA's N (16..256), so no tensor-core row is wasted on
 // padding the batch; D is stored transposed into out[token, n]. Matrices with few rows are split
-// along K over several CTAs; partial tiles are added into a zeroed 32-bit scratch with
-// red.global.add and the last CTA of a tile (a counter decides) applies the epilogue, writes the
-// 16-bit result and zeroes its scratch entries and counter again, so one kernel does it all.
+// along K over the CTAs of a thread-block cluster (up to 8); every CTA leaves its partial tile in
+// its own shared memory and each sums a share of the rows over all of them through distributed
+// shared memory, so one kernel does it all without scratch memory or atomics.
 // Prefill ("tokens as A"): A = x, B = W, D is stored as it is.
 //
 // Warp roles in a CTA of 192 threads: warp 0 produces (one lane issues TMA), warp 1 allocates
@@ -57,7 +57,7 @@ template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                TO* out, int64_t ldo, const float* __restrict__ bias, int rows_a, int rows_b, int K,
-               int stages, int splitk, float* scratch, int* counters, int cluster_k) {
+               int stages, int splitk, int cluster_k) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int B_TILE_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
@@ -156,18 +156,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         pdl_wait();
         const int lane_group = warp & 3;
         const int epi_tid = (warp - 2) * 32 + lane;
-        __shared__ int s_last;
         ok = n_kb > 0 ? mbar_wait(tmem_full_bar, 0, 3) : true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int i_row = a_row0 + lane_group * 32 + lane;          // row of A / D
         const bool row_ok = i_row < rows_a;
         float bias_i = 0.f;
         if (TRANSPOSED && bias != nullptr && row_ok) bias_i = bias[i_row];
-        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-        // the scratch is [rows_b][rows_a] (decode) or [rows_a][rows_b] floats, zero between calls
-        auto scratch_at = [&](int jj) -> float* {
-            return TRANSPOSED ? scratch + (size_t)jj * rows_a + i_row : scratch + (size_t)i_row * rows_b + jj;
-        };
         // columns c .. c + 15 of this thread's row, finished: bias, activation, store
         auto finalize = [&](int c, float (&part)[16]) {
             if (TRANSPOSED && SWIGLU) {
@@ -214,47 +208,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int e = 0; e < 16; ++e) mine[(c + e) * BM + row_local] = part[e];
             }
-        } else if (splitk == 1) {
-            for (int c = 0; c < BN; c += 16) {
-                float part[16];
-                if (have) {
-                    tmem_ld16(tmem_d + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c, part);
-                    finalize(c, part);
-                }
-            }
         } else {
-            // partial sums into the scratch; the tile's last CTA (a counter decides) finishes it
             for (int c = 0; c < BN; c += 16) {
                 float part[16];
                 if (have) {
                     tmem_ld16(tmem_d + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c, part);
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int jj = b_row0 + c + e;
-                        if (row_ok && jj < rows_b) atomicAdd(scratch_at(jj), part[e]);
-                    }
-                }
-            }
-            __threadfence();
-            epi_bar_sync();
-            if (epi_tid == 0) s_last = atomicAdd(&counters[tile_id], 1) == splitk - 1;
-            epi_bar_sync();
-            if (s_last != 0) {
-                __threadfence();
-                for (int c = 0; c < BN; c += 16) {
-                    float part[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int jj = b_row0 + c + e;
-                        part[e] = 0.f;
-                        if (row_ok && jj < rows_b) {
-                            part[e] = __ldcg(scratch_at(jj));
-                            __stcg(scratch_at(jj), 0.f);     // leave the scratch zero for the next call
-                        }
-                    }
                     finalize(c, part);
                 }
-                if (epi_tid == 0) counters[tile_id] = 0;
             }
         }
     }
@@ -366,8 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 template <int BN, bool TRANSPOSED, bool SWIGLU, typename TO>
 cudaError_t launch_tc(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& ma,
                       const CUtensorMap& mb, TO* out, int64_t ldo, const float* bias, int rows_a,
-                      int rows_b, int K, int stages, int splitk, float* scratch, int* counters,
-                      int cluster_k) {
+                      int rows_b, int K, int stages, int splitk, int cluster_k) {
     auto kernel = gemm_tc_kernel<BN, TRANSPOSED, SWIGLU, TO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -392,32 +351,10 @@ cudaError_t launch_tc(dim3 grid, size_t smem, cudaStream_t stream, const CUtenso
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, out, ldo, bias, rows_a, rows_b, K, stages, splitk, scratch,
-                              counters, cluster_k);
+    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, out, ldo, bias, rows_a, rows_b, K, stages, splitk, cluster_k);
 }
 
 }  // namespace
-
-// How K is split: 0 = by cluster when it fits (default), 1 = always through the scratch
-// (atomics), 2 = never split. For measurements.
-static int g_tc_split_mode = 0;
-TK_API int tk_gemm_tc_split_mode(int mode) {
-    g_tc_split_mode = mode;
-    return 0;
-}
-
-// Split heuristic, for measurements: K is split further while the grid has fewer than
-// `target_ctas` CTAs and a slice keeps at least `min_kb` K blocks of 64; the pipeline's stages
-// take at most `stage_kb` KB of shared memory. 0 keeps a value, a negative target restores the
-// default by batch size.
-static int g_tc_target_ctas = 0, g_tc_min_kb = 4, g_tc_stage_kb = 100;
-TK_API int tk_gemm_tc_tune(int target_ctas, int min_kb, int stage_kb) {
-    if (target_ctas > 0) g_tc_target_ctas = target_ctas;
-    if (target_ctas < 0) g_tc_target_ctas = 0;
-    if (min_kb > 0) g_tc_min_kb = min_kb;
-    if (stage_kb > 0) g_tc_stage_kb = stage_kb;
-    return 0;
-}
 
 // 0 if no tensor-core GEMM on the current device has given up on a barrier since the last call;
 // else the place it gave up (1 producer, 2 MMA issuer, 3 epilogue). Resets the word.
@@ -428,18 +365,12 @@ TK_API int tk_gemm_tc_status() {
     return v;
 }
 
-// Scratch the split-K path needs, in bytes: floats [tokens][n] then int counters (one per tile).
-TK_API int64_t tk_gemm_tc_scratch_bytes(int tokens, int n) {
-    return (int64_t)tokens * n * 4 + ((int64_t)(n + BM - 1) / BM) * ((tokens + 15) / 16) * 4 + 256;
-}
-
 // Decode form: out[tokens, N] = x[tokens, K] . w[N, K]^T (+ bias[N]); tokens <= 256.
 // swiglu: see gemm_skinny (rows of w in runs of 8 gate / 8 up; out is [tokens, N / 2]).
-// scratch: zeroed memory of tk_gemm_tc_scratch_bytes(tokens, N) bytes (kept zero by the kernel),
-// or null to forbid splitting K. out_dtype: bfloat16 or float.
+// split_k: whether K may be split over a cluster. out_dtype: bfloat16 or float.
 TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
                              void* out, int64_t ldo, int tokens, int N, int K, int out_dtype, int swiglu,
-                             void* scratch, cudaStream_t stream) {
+                             int split_k, cudaStream_t stream) {
     TK_CHECK_ARG(tokens > 0 && tokens <= 256 && N > 0 && K > 0, "gemm_tc_decode: tokens=%d (1..256) N=%d K=%d",
                  tokens, N, K);
     TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0,
@@ -451,37 +382,28 @@ TK_API int tk_gemm_tc_decode(const void* x, int64_t ldx, const void* w, int64_t 
                  "gemm_tc_decode: cuTensorMapEncodeTiled failed (N=%d K=%d ldw=%lld)", N, K, (long long)ldw);
     const int a_tiles = (N + BM - 1) / BM;
     const int kb_total = (K + BK - 1) / BK;
-    // split K until there are about two CTAs per SM or slices of 4 k-blocks. Up to 8 ways the
-    // partial tiles are reduced inside a cluster (distributed shared memory: no scratch, no
-    // atomics); beyond that, through the scratch.
+    // split K until there are about two CTAs per SM's worth of slices (up to 16 tokens; one for
+    // wider token tiles) or slices of 4 k-blocks, at most 8 ways: the partial tiles are reduced
+    // inside a cluster. Measured on a B200 (2048- to 8192-wide matrices, CUDA graphs). The
+    // pipeline takes at most ~100 KB so that two CTAs share an SM: one CTA's prologue and epilogue
+    // hide behind the other's loads (head at 64 tokens: 64.8 us with one CTA per SM, 49.1 us
+    // with two).
+    constexpr int MIN_KB = 4, STAGE_KB = 100;
     int splitk = 1;
-    const int max_split = (g_tc_split_mode == 1 && scratch != nullptr) ? 64 : 8;
-    // Measured on a B200 (2048- to 8192-wide matrices, CUDA graphs): up to 16 tokens two CTAs per
-    // SM's worth of slices is best; wider token tiles do better with one. The pipeline takes at
-    // most ~100 KB so that two CTAs share an SM: one CTA's prologue and epilogue hide behind the
-    // other's loads (head at 64 tokens: 64.8 us with one CTA per SM, 49.1 us with two).
-    const int target = g_tc_target_ctas > 0 ? g_tc_target_ctas : (BN <= 16 ? 2 * 148 : 148);
-    while (splitk < max_split && a_tiles * splitk < target && kb_total / (splitk * 2) >= g_tc_min_kb)
-        splitk *= 2;
-    int cluster_k = (splitk > 1 && g_tc_split_mode != 1) ? splitk : 0;
-    if (cluster_k == 0 && scratch == nullptr) splitk = 1;
-    if (g_tc_split_mode == 2) {
-        splitk = 1;
-        cluster_k = 0;
-    }
+    const int target = BN <= 16 ? 2 * 148 : 148;
+    while (split_k && splitk < 8 && a_tiles * splitk < target && kb_total / (splitk * 2) >= MIN_KB) splitk *= 2;
+    const int cluster_k = splitk > 1 ? splitk : 0;
     const int kb_per = (kb_total + splitk - 1) / splitk;
     const int stage_bytes = A_TILE_BYTES + BN * BK * 2;
     int stages = kb_per < 6 ? kb_per : 6;
-    while (stages > 2 && (size_t)stages * stage_bytes > (size_t)g_tc_stage_kb * 1024) --stages;
+    while (stages > 2 && (size_t)stages * stage_bytes > (size_t)STAGE_KB * 1024) --stages;
     size_t smem = (size_t)stages * stage_bytes + (2 * stages + 2) * 8 + 1024 + 64;
     if (smem < (size_t)BN * BM * 4 + 1024 + 256) smem = (size_t)BN * BM * 4 + 1024 + 256;
     const dim3 grid(a_tiles, 1, splitk);
-    float* sc = (float*)scratch;
-    int* counters = scratch ? (int*)((char*)scratch + (size_t)tokens * N * 4) : nullptr;
     cudaError_t err = cudaSuccess;
 #define TK_TC(BN_, SW_, TO_)                                                                        \
     err = launch_tc<BN_, true, SW_, TO_>(grid, smem, stream, ma, mb, (TO_*)out, ldo, bias, N, tokens, K, \
-                                         stages, splitk, sc, counters, splitk == 1 ? 0 : cluster_k)
+                                         stages, splitk, cluster_k)
 #define TK_TC_BN(SW_, TO_)                                                                          \
     switch (BN) {                                                                                   \
         case 16: TK_TC(16, SW_, TO_); break;                                                        \

@@ -456,21 +456,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
 
 
 TC_MAX_TOKENS = 256
-_TC_SCRATCH_BYTES = 40 << 20
-_tc_scratch: dict = {}
-
-
-def _scratch_for(device: torch.device, tokens: int, n: int) -> torch.Tensor | None:
-    """The zeroed scratch the split-K path of ``gemm_tc`` adds partial tiles into (the kernel
-    leaves it zero again). One buffer per device, made at first use; a product too large for it
-    runs without splitting K."""
-    need = tokens * n * 4 + ((n + 127) // 128) * ((tokens + 15) // 16) * 4 + 256
-    if need > _TC_SCRATCH_BYTES:
-        return None
-    buf = _tc_scratch.get(device)
-    if buf is None:
-        buf = _tc_scratch[device] = torch.zeros(_TC_SCRATCH_BYTES, dtype=torch.uint8, device=device)
-    return buf
 
 
 def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -486,7 +471,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
             out_dtype: torch.dtype | None = None, swiglu: bool = False,
             split_k: bool = True) -> torch.Tensor:
     """``x @ w.T (+ bias)`` through TMA, tcgen05.mma and tensor memory, the weight rows on the
-    MMA's M axis (decode: up to 256 rows of ``x``). ``swiglu`` as in ``gemm_skinny``."""
+    MMA's M axis (decode: up to 256 rows of ``x``). ``swiglu`` as in ``gemm_skinny``. ``split_k``:
+    matrices with few rows may be split along K over a thread-block cluster."""
     _cuda(x, w, bias)
     M, K = x.shape
     N = w.shape[0]
@@ -494,9 +480,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         raise KernelError(f"gemm_tc: x {tuple(x.shape)} against w {tuple(w.shape)}")
     width = N // 2 if swiglu else N
     out = torch.empty(M, width, dtype=out_dtype or x.dtype, device=x.device)
-    scratch = _scratch_for(x.device, M, N) if split_k else None
     _lib.call("tk_gemm_tc_decode", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
-              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), _ptr(scratch), _stream())
+              _ptr(out), width, M, N, K, _dtype_code(out), int(swiglu), int(split_k), _stream())
     return out
 
 

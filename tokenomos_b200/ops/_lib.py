@@ -49,13 +49,10 @@ _SIGNATURES = {
     "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, F, P],
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, F, P, L, P],
-    "tk_gemm_skinny_tune": [I, I, I],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_gemm_tc_status": [],
     "tk_sample_status": [],
-    "tk_gemm_tc_split_mode": [I],
-    "tk_gemm_tc_tune": [I, I, I],
-    "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, P, P],
+    "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, I, P],
 }
 
 
@@ -102,9 +99,9 @@ def calls() -> int:
     return _calls
 
 
-_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled", "tk_checks_set_bounds", "tk_checks_status", "tk_gemm_skinny_tune", "tk_attn_generic_rows", "tk_conv_min_tile",
+_QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled", "tk_checks_set_bounds", "tk_checks_status", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
-            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status", "tk_gemm_tc_split_mode", "tk_gemm_tc_tune"}
+            "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status"}
 
 
 _fns: dict = {}

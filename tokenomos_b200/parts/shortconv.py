@@ -52,8 +52,11 @@ class ShortConv:
             return self.out_proj(y)
         bcx = self.in_proj(x)
         seq, tok0, off, n = ctx.tiles(self.tile)
+        # (a step of single tokens has one-token tiles: the tiled kernel's blocks of 16 tokens
+        # would be all but empty, the walking form takes them)
+        cap = 0 if ctx.host.decode_only else self.tile
         y = ops.conv_gated(bcx, self.conv, self.conv_bias, state,
-                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run, self.tile, tok0)
+                           ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot, seq, off, n, self.run, cap, tok0)
         return self.out_proj(y)
 
 
