@@ -390,6 +390,54 @@ def profile_case(mode: str, layers: int, batch: int, ctx: int, steps: int, page:
     print(f"profile case done: {mode} layers={layers} batch={batch} ctx={ctx} steps={steps}")
 
 
+def kernel_case(name: str) -> None:
+    """One kernel alone for a profiler, over operands that rotate through more than the L2 holds:
+    ``gemm_tc64``: the tcgen05 product of 64 rows with a [6144, 2048] matrix, 16 launches;
+    ``conv_tile``: the tiled gated short conv over a 2,048-token portion of 2,048 channels (width 3,
+    tiles of 16 tokens), 20 launches in a CUDA graph that is replayed five times."""
+    import torch
+
+    from tokenomos_b200 import ops
+
+    ops.available()
+    dev, bf16 = "cuda", torch.bfloat16
+    if name == "gemm_tc64":
+        ws = [torch.randn(6144, 2048, device=dev, dtype=bf16) * 0.02 for _ in range(8)]
+        x = torch.randn(64, 2048, device=dev, dtype=bf16)
+        for i in range(16):
+            ops.gemm_tc(x, ws[i % 8])
+        torch.cuda.synchronize()
+        if ops.gemm_tc_status():
+            raise RuntimeError("the tcgen05 product reported an error")
+    else:
+        tokens, width, taps, tile = 2048, 2048, 3, 16
+        ins = [torch.randn(tokens, 3 * width, device=dev, dtype=bf16) for _ in range(10)]
+        w = torch.randn(width, taps, device=dev)
+        state = torch.zeros(4, taps - 1, width, device=dev, dtype=bf16)
+        i32 = dict(dtype=torch.int32, device=dev)
+        cu, ctx0, slot = torch.tensor([0, tokens], **i32), torch.zeros(1, **i32), torch.ones(1, **i32)
+        seq, off = torch.zeros(tokens // tile, **i32), torch.arange(0, tokens, tile, **i32)
+        n = torch.full((tokens // tile,), tile, **i32)
+
+        def calls():
+            for i in range(20):
+                ops.conv_gated(ins[i % 10], w, None, state, cu, ctx0, slot, seq, off, n, 0, tile, off)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            calls()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            calls()
+        for _ in range(5):
+            graph.replay()
+        torch.cuda.synchronize()
+    print(f"kernel case done: {name}")
+
+
 def ingraph_table(layers: int, batch: int, ctx: int, page: int) -> None:
     """What each kind of kernel costs *inside* the captured decode step, where launches overlap
     through programmatic dependent launch and a kernel's cold, serialised time under a profiler
@@ -779,6 +827,8 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill", "ingraph"],
                     help="run only a small case for a profiler (see profile_case) and exit; ingraph: "
                          "the cost of each kind of kernel inside the captured decode step (ingraph_table)")
+    ap.add_argument("--kernel", default=None, choices=["gemm_tc64", "conv_tile"],
+                    help="run only one kernel over rotating operands for a profiler (see kernel_case) and exit")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -806,6 +856,9 @@ def main() -> int:
 
     torch.cuda.set_device(0)
     ops.available()
+    if args.kernel:
+        kernel_case(args.kernel)
+        return 0
     if args.profile == "ingraph":
         ingraph_table(args.layers, args.batch, args.ctx, args.page)
         return 0
