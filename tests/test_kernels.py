@@ -647,6 +647,129 @@ def test_attention_mma_mixed_batches(H, Hkv, D, P, nsplit):
     close(got, want, torch.bfloat16, f"mma attention H{H} Hkv{Hkv} D{D} P{P} split {nsplit}")
 
 
+def decode_fused_case(H, Hkv, D, P, angles, window, nsplit, gated, normed, ctxs, write_kv=True):
+    """One decode step's attention for sequences holding ``ctxs`` positions, through the one-kernel
+    form and through the chain it replaces (norm + rotation + cache write, split attention + merge,
+    gate), on two copies of the same NaN-poisoned cache, and in float64 from the same inputs."""
+    from tokenomos_b200 import ops
+    dtype, eps = torch.bfloat16, 1e-5
+    G, n = H // Hkv, len(ctxs)
+    own = Hkv if write_kv else 0
+    blocks = [-(-(c + 1) // P) for c in ctxs]
+    pages = sum(blocks) + 1
+    perm = (torch.randperm(pages - 1) + 1).tolist()
+    pool = torch.full((pages, 2, Hkv, P, D), float("nan"), dtype=torch.float64)
+    table = torch.zeros(n, max(blocks), dtype=torch.int32)
+    ks, vs = [], []
+    for s_, c in enumerate(ctxs):
+        held = c + (0 if write_kv else 1)           # without keys of its own the cache holds this step's already
+        k = torch.randn(held, Hkv, D).to(dtype).double()
+        v = torch.randn(held, Hkv, D).to(dtype).double()
+        for b in range(blocks[s_]):
+            page = perm.pop()
+            table[s_, b] = page
+            rows = max(0, min(P, held - b * P))
+            pool[page, 0, :, :rows] = k[b * P:b * P + rows].transpose(0, 1)
+            pool[page, 1, :, :rows] = v[b * P:b * P + rows].transpose(0, 1)
+        ks.append(k), vs.append(v)
+    width = (H + 2 * own) * D
+    pad = -(-H // 8) * 8 if gated else 0
+    proj = (torch.randn(n, width + pad) * 1.5).to(dtype)
+    wq = (1 + 0.3 * torch.randn(D)) if normed else None
+    wk = (1 + 0.3 * torch.randn(D)) if normed else None
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 2 * angles, 2, dtype=torch.float32) / (2 * angles)))
+    rot = 2 * angles
+    positions, tok_seq = i32(ctxs), i32(list(range(n)))
+    proj_d, table_d, inv_d = dev(proj), dev(table), dev(inv)
+    wq_d, wk_d = (dev(wq), dev(wk)) if normed else (None, None)
+    gate = proj_d[:, width:width + H] if gated else None
+    scale = D ** -0.5
+
+    pool_a = dev(pool, dtype)
+    got = ops.attention_decode_fused(proj_d, pool_a, wq_d, wk_d if own else None, eps, inv_d, gate, positions,
+                                     tok_seq, table_d, H, Hkv, window, scale, nsplit, write_kv=write_kv)
+    pool_b = dev(pool, dtype)
+    q = ops.qk_norm_rope_write(proj_d[:, :width], pool_b if own else None, wq_d, wk_d if own else None, eps,
+                               inv_d, positions, tok_seq, table_d if own else None, H, own, D, P)
+    chain = torch.empty_like(q)
+    ops.attention_decode_mma(q, pool_b, chain, positions, tok_seq, table_d, None, window, scale, nsplit)
+    if gated:
+        ops.head_gate(chain, gate, H, D)
+
+    x = proj.double()[:, :width].view(n, H + 2 * own, D)
+
+    def norm(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.double() if w is not None else v
+
+    pos = torch.tensor(ctxs)
+    inv_full = torch.cat((inv, torch.zeros(0)))
+    want_q = rope_ref(norm(x[:, :H], wq), pos, inv_full, rot)
+    want = []
+    for s_, c in enumerate(ctxs):
+        k, v = ks[s_], vs[s_]
+        if write_kv:
+            k = torch.cat((k, rope_ref(norm(x[s_:s_ + 1, H:H + Hkv], wk), pos[s_:s_ + 1], inv_full, rot)
+                           .to(dtype).double()))
+            v = torch.cat((v, x[s_:s_ + 1, H + Hkv:]))
+        k, v = k.repeat_interleave(G, 1), v.repeat_interleave(G, 1)
+        sc = torch.einsum("hd,jhd->hj", want_q[s_].to(dtype).double(), k) * scale
+        j = torch.arange(c + 1)
+        vis = j <= c
+        if window:
+            vis &= (c - j) < window
+        sc = sc.masked_fill(~vis[None], float("-inf"))
+        o = torch.einsum("hj,jhd->hd", sc.softmax(-1), v)
+        if gated:
+            o = o * torch.sigmoid(proj.double()[s_, width:width + H])[:, None]
+        want.append(o)
+    tickets = ops._tickets.get(got.device)
+    return got, chain, torch.stack(want), pool_a, pool_b, tickets
+
+
+@pytest.mark.parametrize("H, Hkv, D, P, angles", [(32, 8, 64, 16, 32), (8, 8, 64, 64, 16), (4, 2, 128, 32, 64),
+                                                  (16, 1, 64, 8, 32), (6, 3, 64, 7, 8), (8, 1, 128, 16, 24),
+                                                  (2, 2, 64, 16, 0)])
+@pytest.mark.parametrize("nsplit, window, gated, normed", [(1, None, True, True), (3, None, True, True),
+                                                           (16, None, False, True), (5, 40, True, False),
+                                                           (2, 1, False, False)])
+def test_attention_decode_fused_equals_the_chain_it_replaces(H, Hkv, D, P, angles, nsplit, window, gated, normed):
+    ctxs = [0, 1, 31, 32, 33, 100, 1000, 333, 64, 95]
+    got, chain, want, pool_a, pool_b, tickets = decode_fused_case(H, Hkv, D, P, angles, window, nsplit, gated,
+                                                                   normed, ctxs)
+    what = f"fused decode attention H{H} Hkv{Hkv} D{D} P{P} R{2 * angles} split {nsplit} window {window}"
+    close(got, want, torch.bfloat16, what)
+    # the same bits as norm + rotation + write, split attention + merge, gate: outputs and cache
+    assert torch.equal(got.view(torch.int16), chain.view(torch.int16)), what
+    assert torch.equal(pool_a.view(torch.int16), pool_b.view(torch.int16)), what + ": cache"
+    assert tickets is None or int(tickets.abs().sum()) == 0, "tickets are zero again"
+
+
+def test_attention_decode_fused_without_keys_of_its_own_and_twice_in_a_row():
+    """A layer that reads another layer's cache (queries only, nothing written), and the same
+    launch repeated: the tickets of the first leave the second alone."""
+    ctxs = [5, 700, 31, 32]
+    for _ in range(2):
+        got, chain, want, pool_a, pool_b, tickets = decode_fused_case(8, 2, 64, 16, 32, None, 4, False, True, ctxs,
+                                                                       write_kv=False)
+        close(got, want, torch.bfloat16, "fused decode attention over a shared cache")
+        assert torch.equal(got.view(torch.int16), chain.view(torch.int16))
+        assert torch.equal(pool_a.view(torch.int16), pool_b.view(torch.int16))
+        assert int(tickets.abs().sum()) == 0
+
+
+def test_attention_decode_fused_refuses_what_it_cannot_take():
+    from tokenomos_b200 import ops
+    assert not ops.attention_decode_fused_supported(8, 2, 48, 32, torch.bfloat16)      # head size
+    assert not ops.attention_decode_fused_supported(8, 2, 64, 24, torch.bfloat16)      # rotary halves of 12
+    assert not ops.attention_decode_fused_supported(8, 2, 64, 64, torch.float32)
+    assert ops.attention_decode_fused_supported(8, 2, 64, 0, torch.bfloat16)
+    pool = torch.zeros(4, 2, 2, 16, 48, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="not taken"):
+        ops.attention_decode_fused(torch.zeros(1, 12 * 48, dtype=torch.bfloat16, device="cuda"), pool, None, None,
+                                   1e-5, torch.ones(16, device="cuda"), None, i32([0]), i32([0]),
+                                   torch.ones(1, 1, dtype=torch.int32, device="cuda"), 8, 2, None, 0.1, 1)
+
+
 @pytest.mark.parametrize("H, Hkv, P", [(32, 8, 16), (8, 8, 64), (16, 1, 8), (6, 3, 7), (4, 4, 32)])
 def test_attention_tc_prefill(H, Hkv, P):
     """The tcgen05 prefill kernel (head size 64): portions of every length beside cached

@@ -434,6 +434,361 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
     out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode, a layer's whole attention core in one kernel: the q/k norm, the rotation and the cache
+// write of the new key and value (qk_rope.cu's formulas, to the bit), the split attention above,
+// the merge of the splits by whichever CTA of a (token, KV head) finishes last, and the per-head
+// output gate  out = round(round(o) * round(sigmoid(g))).
+//   - Everything a CTA can know before the kernel in front of it has finished is asked for ahead
+//     of the dependency wait: the page numbers, the first key/value tiles (earlier steps wrote
+//     them; the tile that holds this step's position is never among them) and the angles.
+//   - The new key and value never make the trip through memory: the CTA whose range holds the
+//     position writes them to the cache for later steps, and every CTA that needs them patches
+//     them into its shared-memory tile.
+//   - `tickets` [n * Hkv] are zero between launches: each CTA adds one after its partial result is
+//     visible, the one that draws the last number merges and puts the zero back.
+// ---------------------------------------------------------------------------------------------
+struct DecodeFused {
+    const __nv_bfloat16* qkv;       // [n, >= (H + 2 Hkv) D] raw projection rows (q heads only if !write_kv)
+    int64_t ldq;
+    __nv_bfloat16* pool;
+    __nv_bfloat16* out;             // [n, H, D]
+    const float* wq;                // null: no q/k norm
+    const float* wk;
+    float eps;
+    const float* inv_freq;          // [R / 2]
+    int R;
+    const __nv_bfloat16* gate;      // [n, >= H] rows ldg apart; null: no gate
+    int64_t ldg;
+    const int* positions;
+    const int* tok_seq;
+    const int* block_table;
+    int bt_stride;
+    int H, Hkv, P, window;
+    float scale;
+    int nsplit;
+    float* part_o;
+    float* part_ml;
+    int* tickets;
+    int p_shift;
+    int write_kv;                   // 0: the layer reads another layer's cache, which holds this step's key already
+};
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFused a) {
+    pdl_launch_dependents();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_last;
+    constexpr int TILE_BYTES = 32 * D * 2;                   // one warp's 32 keys
+    constexpr int STAGING = 4 * 2 * 2 * TILE_BYTES;          // [warp][stage][K|V]; later the warps' merge
+    constexpr int QS = D + 8;                                // row stride of the query tile (no bank conflicts)
+    __nv_bfloat16* sm_q = reinterpret_cast<__nv_bfloat16*>(smem_raw + STAGING);     // [G][QS]
+    __nv_bfloat16* sm_new = sm_q + 16 * QS;                                        // the new key, the new value
+    float* sm_cs = reinterpret_cast<float*>(sm_new + 2 * D);                       // [D/2] cos, [D/2] sin
+    float* sm_sn = sm_cs + D / 2;
+    const int H = a.H, Hkv = a.Hkv, P = a.P, window = a.window, nsplit = a.nsplit;
+    const int G = H / Hkv;
+    const int i = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tok = i;
+    const int seq = a.tok_seq[tok];
+    const int pos = a.positions[tok];
+    const int* bt_row = a.block_table + (size_t)seq * a.bt_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int j_begin = (lo / 32) * 32;
+    const int tiles = (pos - j_begin) / 32 + 1;
+    const int per_split = (tiles + nsplit - 1) / nsplit;
+    const int t_begin = split * per_split, t_end = min(tiles, t_begin + per_split);
+    const int last_tile = tiles - 1;                         // the tile that holds position `pos`
+    const int j_last = a.write_kv ? pos - 1 : pos;           // the last key that comes from the cache
+    const bool owner = a.write_kv && t_begin <= last_tile && last_tile < t_end;
+    size_t cache_row = 0;
+    if (owner) {
+        const int page = TK_PAGE(TK_K_QK_ROPE, bt_row[a.p_shift >= 0 ? pos >> a.p_shift : pos / P]);
+        cache_row = (size_t)page * 2 * Hkv * P + (a.p_shift >= 0 ? pos & (P - 1) : pos % P);
+    }
+    const int half = a.R >> 1;
+    for (int k = tid; k < half; k += 128) {
+        float s_, c_;
+        sincosf((float)pos * a.inv_freq[k], &s_, &c_);
+        sm_cs[k] = round_as<__nv_bfloat16>(c_);
+        sm_sn[k] = round_as<__nv_bfloat16>(s_);
+    }
+
+    // the warp's private double buffer: [stage][K|V][32][D]
+    const uint32_t wbase = smem_u32(smem_raw) + (uint32_t)warp * 4 * TILE_BYTES;
+    PagedLoader<D, 32, 32> loader;
+    loader.init(lane, kvh, Hkv, P, a.p_shift);
+    auto issue = [&](int tile, int stage) {
+        const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
+        const int j0 = j_begin + tile * 32;
+        if (a.p_shift >= 0) {
+            loader.issue_looked_up(base, base + TILE_BYTES, a.pool, j0, lo, j_last);
+            if (tile + 4 < t_end) loader.lookup(bt_row, j0 + 4 * 32, lo, pos);
+        } else {
+            load_tile<D>(base, a.pool, bt_row, j0, 32, lo, j_last, kvh, Hkv, P, 0, lane, 32);
+            load_tile<D>(base + TILE_BYTES, a.pool, bt_row, j0, 32, lo, j_last, kvh, Hkv, P, 1, lane, 32);
+        }
+        cp_async_commit();
+    };
+    const int first = t_begin + warp;
+    const bool deferred = first == last_tile;                // this step writes into that tile
+    if (first < t_end && !deferred) {
+        if (a.p_shift >= 0) loader.lookup(bt_row, j_begin + first * 32, lo, pos);
+        issue(first, 0);
+    }
+    pdl_wait();
+    __syncthreads();                                         // the angles are in place
+
+    // the group's query heads, then the new key, then the new value: a head over LPH lanes
+    {
+        constexpr int LPH = D / 8, HPP = 32 / LPH;
+        const int sub = lane / LPH, c = (lane % LPH) * 8;
+        const int jobs = G + (a.write_kv ? 2 : 0);
+        const int half_lanes = half / 8;
+        const int partner = c < half ? lane + half_lanes : (c < a.R ? lane - half_lanes : lane);
+        const __nv_bfloat16* row = a.qkv + (size_t)tok * a.ldq;
+        for (int j0 = warp * HPP; j0 < jobs; j0 += 4 * HPP) {
+            const int job = j0 + sub;
+            const bool live = job < jobs;
+            const __nv_bfloat16* src = row;
+            const float* w = nullptr;
+            bool rotate = true;
+            if (job < G) {
+                src = row + (size_t)(kvh * G + job) * D;
+                w = a.wq;
+            } else if (job == G) {
+                src = row + (size_t)(H + kvh) * D;
+                w = a.wk;
+            } else {
+                src = row + (size_t)(H + Hkv + kvh) * D;
+                rotate = false;
+            }
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (live) raw = *reinterpret_cast<const uint4*>(src + c);
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+            float v[8];
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                v[k] = __bfloat162float(e[k]);
+                ss += v[k] * v[k];
+            }
+            for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (rotate && w != nullptr) {
+                const float rstd = 1.0f / sqrtf(ss / (float)D + a.eps);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    v[k] = round_as<__nv_bfloat16>(round_as<__nv_bfloat16>(v[k] * rstd) * w[c + k]);
+            }
+            float pv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pv[k] = __shfl_sync(0xffffffffu, v[k], partner);
+            if (!live) continue;
+            uint4 packed = raw;
+            if (rotate) {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+                const int i0 = c < half ? c : c - half;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float r = v[k];
+                    if (c < a.R) r = r * sm_cs[i0 + k] + (c < half ? -pv[k] : pv[k]) * sm_sn[i0 + k];
+                    o[k] = __float2bfloat16_rn(r);
+                }
+            }
+            if (job < G) {
+                *reinterpret_cast<uint4*>(sm_q + job * QS + c) = packed;
+            } else {
+                *reinterpret_cast<uint4*>(sm_new + (job - G) * D + c) = packed;
+                if (owner)
+                    *reinterpret_cast<uint4*>(a.pool + (cache_row + (size_t)((job - G) * Hkv + kvh) * P) * D + c) = packed;
+            }
+        }
+    }
+    __syncthreads();
+
+    uint32_t qf[D / 16][4];                                  // rows 0..G-1 are the group's heads
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const int r = g + 8 * hf;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t ql = 0u, qh = 0u;
+            if (r < G) {
+                ql = *reinterpret_cast<const uint32_t*>(sm_q + r * QS + ks * 16 + 2 * t);
+                qh = *reinterpret_cast<const uint32_t*>(sm_q + r * QS + ks * 16 + 8 + 2 * t);
+            }
+            qf[ks][hf] = ql;
+            qf[ks][hf + 2] = qh;
+        }
+    }
+    const int pos_lo = g < G ? pos : -1, pos_hi = g + 8 < G ? pos : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    const float scale_log2 = a.scale * LOG2E;
+
+    if (first < t_end && deferred) {
+        if (a.p_shift >= 0) loader.lookup(bt_row, j_begin + first * 32, lo, pos);
+        issue(first, 0);
+    }
+    int stage = 0;
+    for (int tile = first; tile < t_end; tile += 4) {
+        const bool more = tile + 4 < t_end;
+        if (more) issue(tile + 4, stage ^ 1);
+        if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncwarp();
+        const int j0 = j_begin + tile * 32;
+        const uint32_t off = (uint32_t)warp * 4 * TILE_BYTES + (uint32_t)stage * 2 * TILE_BYTES;
+        if (a.write_kv && tile == last_tile) {
+            // this step's key and value: into their row of the tile (the copies left it zero)
+            constexpr int LPH = D / 8;
+            if (lane < 2 * LPH) {
+                const int which = lane / LPH, ch = lane % LPH;
+                const uint4 nv = *reinterpret_cast<const uint4*>(sm_new + which * D + ch * 8);
+                *reinterpret_cast<uint4*>(smem_raw + off + which * TILE_BYTES + tile_off<D>(pos - j0, ch)) = nv;
+            }
+            __syncwarp();
+        }
+        const uint32_t base = smem_u32(smem_raw) + off;
+        warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2, true, m, l, o);
+        __syncwarp();
+        stage ^= 1;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    // merge the four warps through shared memory (the K/V buffers are done with)
+    __syncthreads();
+    float* sm_o = reinterpret_cast<float*>(smem_raw);              // [4][16][D]
+    float* sm_ml = sm_o + 4 * 16 * D;                              // [4][16][2]
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const int r = g + 8 * hf;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            sm_o[(warp * 16 + r) * D + n * 8 + 2 * t] = o[n][hf * 2];
+            sm_o[(warp * 16 + r) * D + n * 8 + 2 * t + 1] = o[n][hf * 2 + 1];
+        }
+        if (t == 0) {
+            sm_ml[(warp * 16 + r) * 2] = m[hf];
+            sm_ml[(warp * 16 + r) * 2 + 1] = l[hf];
+        }
+    }
+    __syncthreads();
+    // one finished element: rounded as the attention's output, gated, rounded again
+    auto finish = [&](int head, int c, float val) {
+        float y = round_as<__nv_bfloat16>(val);
+        if (a.gate != nullptr) {
+            const float gv = __bfloat162float(a.gate[(size_t)tok * a.ldg + head]);
+            y *= round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-gv)));
+        }
+        a.out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(y);
+    };
+    for (int idx = tid; idx < G * D; idx += 128) {
+        const int r = idx / D, c = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_ml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : fast_exp2((mw - M) * scale_log2);
+            L += sm_ml[(w * 16 + r) * 2 + 1] * f;
+            acc += sm_o[(w * 16 + r) * D + c] * f;
+        }
+        const int head = kvh * G + r;
+        if (nsplit == 1) {
+            finish(head, c, L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t slot = ((size_t)i * H + head) * nsplit + split;
+            a.part_o[slot * D + c] = acc;
+            if (c == 0) {
+                a.part_ml[slot * 2] = M;
+                a.part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+    if (nsplit == 1) return;
+    // the last CTA of this (token, KV head) to get here merges the splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&a.tickets[i * Hkv + kvh], 1) == nsplit - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // every split's (maximum, sum) of the group's heads in one trip, then each head's weights
+    float* sm_f = reinterpret_cast<float*>(smem_raw);            // [G][nsplit] maxima, then weights
+    float* sm_l = sm_f + G * nsplit;                             // [G][nsplit] sums
+    float* sm_inv = sm_l + G * nsplit;                           // [G] 1 / total, 0 for an empty row
+    for (int idx = tid; idx < G * nsplit; idx += 128) {
+        const int r = idx / nsplit, s = idx % nsplit;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + ((size_t)i * H + kvh * G + r) * nsplit + s);
+        sm_f[idx] = ml.x;
+        sm_l[idx] = ml.y;
+    }
+    __syncthreads();
+    for (int r = warp; r < G; r += 4) {
+        float M = -INFINITY;
+        for (int s = lane; s < nsplit; s += 32) M = fmaxf(M, sm_f[r * nsplit + s]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        for (int s = lane; s < nsplit; s += 32) {
+            const float ms = sm_f[r * nsplit + s];
+            sm_f[r * nsplit + s] = ms == -INFINITY ? 0.f : fast_exp2((ms - M) * scale_log2);
+        }
+        // the sum runs over the splits in order, as the element loop below and the merge kernel do
+        __syncwarp();
+        if (lane == 0) {
+            float tot = 0.f;
+            for (int s = 0; s < nsplit; ++s) tot += sm_l[r * nsplit + s] * sm_f[r * nsplit + s];
+            sm_inv[r] = tot;
+        }
+    }
+    __syncthreads();
+    constexpr int PER = 16 * D / 128;                            // elements a thread may own (G <= 16)
+    float acc[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) acc[k] = 0.f;
+    for (int s0 = 0; s0 < nsplit; s0 += 4) {
+        float got[PER][4];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int idx = tid + k * 128;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                got[k][u] = 0.f;
+                if (idx < G * D && s0 + u < nsplit)
+                    got[k][u] = __ldcg(&a.part_o[(((size_t)i * H + kvh * G + idx / D) * nsplit + s0 + u) * D + idx % D]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int idx = tid + k * 128;
+            if (idx >= G * D) continue;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (s0 + u < nsplit) acc[k] += got[k][u] * sm_f[(idx / D) * nsplit + s0 + u];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int idx = tid + k * 128;
+        if (idx >= G * D) continue;
+        const int r = idx / D;
+        const float L = sm_inv[r];
+        finish(kvh * G + r, idx % D, L > 0.f ? acc[k] / L : 0.f);
+    }
+    if (tid == 0) a.tickets[i * Hkv + kvh] = 0;
+}
+
 // log2 of a power-of-two page size, else -1 (the kernels then divide per 16-byte request)
 int page_shift(int P) {
     if (P <= 0 || (P & (P - 1))) return -1;
@@ -525,6 +880,98 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
             tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
     }
     TK_CHECK_LAUNCH("attn_decode_merge");
+    return 0;
+}
+
+// 1 when tk_attn_decode_fused takes this shape: what the tensor-core kernels take, and a rotation
+// whose halves are whole 16-byte chunks.
+TK_API int tk_attn_decode_fused_supported(int H, int Hkv, int D, int R) {
+    return mma_shape_ok(H, Hkv, D) && R >= 0 && R <= D && R % 16 == 0 ? 1 : 0;
+}
+
+// The most splits tk_attn_decode_fused takes: the merging CTA holds every split's maximum and sum
+// of the group's heads in the shared memory its key/value tiles left.
+TK_API int tk_attn_decode_fused_max_splits(int H, int Hkv, int D) {
+    if (!mma_shape_ok(H, Hkv, D)) return 0;
+    const int G = H / Hkv;
+    const int floats = 4 * 2 * 2 * 32 * D * 2 / 4;
+    const int most = (floats - G) / (2 * G);
+    return most < 65535 ? most : 65535;
+}
+
+// A decode step's attention for `n` sequences of one token each, from the raw projection rows
+// `qkv` [n, (H + 2 Hkv) D] (rows `ldq` elements apart) to the gated heads' outputs `out`
+// [n, H, D]: q/k norm (wq, wk null: none), rotate-half rotation of the first R columns by
+// position x inv_freq, the new key and value into the cache (write_kv 0: the layer has none of
+// its own and `qkv` holds queries only), attention split `nsplit` ways, merge, gate (null: none).
+// `scratch`: tk_attn_decode_mma_scratch floats (nsplit > 1); `tickets`: n * Hkv ints that are zero
+// and are zero again when the kernel has finished. `carveout`: the share of the SM's memory (in
+// percent of the most it can give) this launch would like as shared memory, -1 for the driver's
+// choice. It matters to the kernels around this one more than to this one: an SM changes its
+// split between shared memory and L1 only when it is empty, so a kernel that asks for another
+// split than its neighbours cannot start under them, and the split it leaves behind is the L1 the
+// next kernels' loads find.
+TK_API int tk_attn_decode_fused(const void* qkv, int64_t ldq, void* kv_pool, void* out, const float* wq,
+                                const float* wk, float eps, const float* inv_freq, int R,
+                                const void* gate, int64_t ldg, const int* positions, const int* tok_seq,
+                                const int* block_table, int bt_stride, int n, int H, int Hkv, int D, int P,
+                                int window, float scale, int nsplit, float* scratch, int* tickets,
+                                int write_kv, int carveout, cudaStream_t stream) {
+    TK_CHECK_ARG(tk_attn_decode_fused_supported(H, Hkv, D, R),
+                 "attn_decode_fused: shape H=%d Hkv=%d D=%d rotary %d is not taken (head size 64 or 128, "
+                 "group a power of two up to 16, rotary width a multiple of 16)", H, Hkv, D, R);
+    TK_CHECK_ARG(P > 0 && n >= 0 && nsplit >= 1, "attn_decode_fused: bad sizes");
+    TK_CHECK_ARG(nsplit <= tk_attn_decode_fused_max_splits(H, Hkv, D), "attn_decode_fused: %d splits, at most %d",
+                 nsplit, tk_attn_decode_fused_max_splits(H, Hkv, D));
+    TK_CHECK_ARG(ldq % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kv_pool % 16 == 0,
+                 "attn_decode_fused: projection rows and the cache must be 16-byte aligned");
+    TK_CHECK_ARG((wq == nullptr) == (wk == nullptr) || !write_kv, "attn_decode_fused: q and k norms come together");
+    TK_CHECK_ARG(inv_freq != nullptr || R == 0, "attn_decode_fused: a rotation needs its frequencies");
+    if (n == 0) return 0;
+    TK_CHECK_ARG(nsplit == 1 || (scratch != nullptr && tickets != nullptr),
+                 "attn_decode_fused: %d splits need scratch memory and tickets", nsplit);
+    DecodeFused a;
+    a.qkv = (const __nv_bfloat16*)qkv;
+    a.ldq = ldq;
+    a.pool = (__nv_bfloat16*)kv_pool;
+    a.out = (__nv_bfloat16*)out;
+    a.wq = wq;
+    a.wk = wk;
+    a.eps = eps;
+    a.inv_freq = inv_freq;
+    a.R = R;
+    a.gate = (const __nv_bfloat16*)gate;
+    a.ldg = ldg;
+    a.positions = positions;
+    a.tok_seq = tok_seq;
+    a.block_table = block_table;
+    a.bt_stride = bt_stride;
+    a.H = H;
+    a.Hkv = Hkv;
+    a.P = P;
+    a.window = window;
+    a.scale = scale;
+    a.nsplit = nsplit;
+    a.part_o = scratch;
+    a.part_ml = scratch ? scratch + (size_t)n * H * nsplit * D : nullptr;
+    a.tickets = tickets;
+    a.p_shift = page_shift(P);
+    a.write_kv = write_kv ? 1 : 0;
+    dim3 grid(n, Hkv, nsplit);
+    // K/V staging (the warps' merge reuses it), the query tile, the new key and value, cos and sin
+    const size_t smem = 4 * 2 * 2 * 32 * (size_t)D * 2 + 16 * ((size_t)D + 8) * 2 + 2 * (size_t)D * 2 +
+                        (size_t)D * sizeof(float);
+    const int prefer = carveout >= 0 && carveout <= 100 ? carveout : (int)cudaSharedmemCarveoutDefault;
+    if (D == 64) {
+        cudaFuncSetAttribute(attn_decode_fused_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, prefer);
+        cudaFuncSetAttribute(attn_decode_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_fused_kernel<64>, dim3(grid), dim3(128), smem, stream, a);
+    } else {
+        cudaFuncSetAttribute(attn_decode_fused_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, prefer);
+        cudaFuncSetAttribute(attn_decode_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_fused_kernel<128>, dim3(grid), dim3(128), smem, stream, a);
+    }
+    TK_CHECK_LAUNCH("attn_decode_fused");
     return 0;
 }
 

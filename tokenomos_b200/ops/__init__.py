@@ -334,6 +334,71 @@ def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tens
               n, H, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), _stream())
 
 
+def attention_decode_fused_supported(heads: int, kv_heads: int, head_dim: int, rotary: int,
+                                     dtype: torch.dtype) -> bool:
+    """Whether ``attention_decode_fused`` takes this shape and rotary width."""
+    return dtype == torch.bfloat16 and bool(
+        _lib.call("tk_attn_decode_fused_supported", heads, kv_heads, head_dim, rotary))
+
+
+# per device: [n * kv_heads] zeros the fused decode kernel counts finished splits in and zeroes
+# again; a buffer that a captured step may point at is never freed, only outgrown
+_tickets: dict = {}
+_tickets_outgrown: list = []
+
+
+def _decode_tickets(n: int, device: torch.device) -> torch.Tensor:
+    have = _tickets.get(device)
+    if have is None or have.numel() < n:
+        if have is not None:
+            _tickets_outgrown.append(have)
+        have = _tickets[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return have
+
+
+def attention_decode_fused(qkv: torch.Tensor, kv_pool: torch.Tensor, q_norm: torch.Tensor | None,
+                           k_norm: torch.Tensor | None, eps: float, inv_freq: torch.Tensor,
+                           gate: torch.Tensor | None, positions: torch.Tensor, tok_seq: torch.Tensor,
+                           block_table: torch.Tensor, heads: int, kv_heads: int, window: int | None,
+                           scale: float, nsplit: int, write_kv: bool = True,
+                           carveout: int = -1) -> torch.Tensor:
+    """A decode step's attention in one kernel, for sequences that bring one token each (row i of
+    ``qkv`` is sequence i's): from the raw projection rows ``qkv`` [T, >= (H + 2 Hkv) D] (q heads,
+    k heads, v heads; rows may be strided) through q/k norm, the rotate-half rotation by
+    ``position * inv_freq`` [R / 2], the write of the new keys and values into ``kv_pool``
+    [pages, 2, Hkv, P, D], attention over the cache split ``nsplit`` ways, the merge of the splits
+    and the per-head gate ``gate`` [T, H] (a strided view; None: no gate) to the heads' outputs
+    [T, H, D]. ``write_kv`` False: the layer reads a cache that another layer wrote this step and
+    ``qkv`` holds queries only. ``carveout``: the share of an SM's memory, in percent of the most,
+    that the launch prefers as shared memory (-1: the driver's choice). ``nsplit`` is cut to what
+    the kernel's merge can hold."""
+    _cuda(qkv, kv_pool, q_norm, k_norm, inv_freq, gate, positions, tok_seq, block_table)
+    T = qkv.shape[0]
+    _, two, Hkv, P, D = kv_pool.shape
+    need = (heads + (2 * Hkv if write_kv else 0)) * D
+    if (two != 2 or Hkv != kv_heads or qkv.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16
+            or qkv.stride(1) != 1 or qkv.shape[1] < need or not kv_pool.is_contiguous()):
+        raise KernelError("attention_decode_fused: qkv [T, >= (H + 2 Hkv) D] with contiguous rows and "
+                          "kv_pool [pages, 2, Hkv, P, D], both bfloat16")
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape != (T, heads) or gate.stride(1) != 1):
+        raise KernelError("attention_decode_fused: gate must be a bfloat16 [T, H] view with unit column stride")
+    R = 2 * inv_freq.numel()
+    out = torch.empty(T, heads, D, dtype=torch.bfloat16, device=qkv.device)
+    nsplit = max(1, min(int(nsplit), _lib.call("tk_attn_decode_fused_max_splits", heads, Hkv, D)))
+    scratch = tickets = None
+    if nsplit > 1:
+        scratch = torch.empty(T * heads * nsplit * (D + 2), dtype=torch.float32, device=qkv.device)
+        tickets = _decode_tickets(T * Hkv, qkv.device)
+    _lib.call("tk_attn_decode_fused", _ptr(qkv), qkv.stride(0), _ptr(kv_pool), _ptr(out),
+              _ptr(_f32vec(q_norm, "q_norm", D)), _ptr(_f32vec(k_norm, "k_norm", D)), float(eps),
+              _ptr(_f32vec(inv_freq, "inv_freq", R // 2)), R, _ptr(gate),
+              gate.stride(0) if gate is not None else 0, _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+              T, heads, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), _ptr(tickets),
+              1 if write_kv else 0, int(carveout), _stream())
+    return out
+
+
 def conv_min_tile(width: int) -> int:
     return _lib.call("tk_conv_min_tile", width)
 

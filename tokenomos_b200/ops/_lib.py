@@ -44,6 +44,9 @@ _SIGNATURES = {
     "tk_attn_prefill_tc_status": [],
     "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
+    "tk_attn_decode_fused_supported": [I, I, I, I],
+    "tk_attn_decode_fused_max_splits": [I, I, I],
+    "tk_attn_decode_fused": [P, L, P, P, P, P, F, P, I, P, L, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "tk_gemm_skinny_conv": [P, L, P, L, P, P, L, I, I, I, P, P, P, P, P, I, F, P],
@@ -100,7 +103,7 @@ def calls() -> int:
 
 
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled", "tk_checks_set_bounds", "tk_checks_status", "tk_attn_generic_rows", "tk_conv_min_tile",
-            "tk_attn_mma_supported", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
+            "tk_attn_mma_supported", "tk_attn_decode_fused_supported", "tk_attn_decode_fused_max_splits", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status"}
 
 

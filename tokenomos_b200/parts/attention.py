@@ -54,6 +54,7 @@ class Attention:
         if qkv.out_features != self.qkv_width + (-(-heads // 8) * 8 if gate_fused else 0):
             raise ValueError("attention: the fused projection does not match the head counts")
         self.norm_folded = False
+        self._fused_freqs = None        # the rotation's frequencies once asked for; False: not fusable
         self.head_layout = HeadLayout(heads, own_kv, head_dim, self.q_norm,
                                       self.k_norm if own_kv else None, self.eps)
 
@@ -67,7 +68,9 @@ class Attention:
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
         proj = self.qkv(x)
-        if self.gate_fused:
+        if self._fused_decode(ctx):
+            out = self._decode_fused(proj, ctx, call)
+        elif self.gate_fused:
             n = self.qkv_width
             out = self._core(proj[:, :n], ctx, call)
             ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
@@ -96,11 +99,48 @@ class Attention:
         T = stream.shape[0]
         proj = ops.gemm_skinny(stream, self.qkv.weight, self.qkv.bias, norm_eps=eps)
         n = self.qkv_width
-        out = self._core(proj[:, :n] if self.gate_fused else proj, ctx, call)
-        if self.gate_fused:
-            ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
+        if self._fused_decode(ctx):
+            out = self._decode_fused(proj, ctx, call)
+        else:
+            out = self._core(proj[:, :n] if self.gate_fused else proj, ctx, call)
+            if self.gate_fused:
+                ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
         return ops.gemm_skinny(out.view(T, self.heads * self.head_dim), self.o.weight, self.o.bias,
                                residual=stream)
+
+    # whether decode steps may take the one-kernel form (TOKENOMOS_B200_ATTN_FUSED=0: never)
+    decode_fused = os.environ.get("TOKENOMOS_B200_ATTN_FUSED", "1") != "0"
+
+    def _fused_decode(self, ctx: StepContext) -> bool:
+        """Whether this step's attention runs as one kernel: every sequence brings one token, the
+        position encoding is a plain rotation that says so, and the kernel takes the shape."""
+        if not (self.decode_fused and ctx.host.decode_only and self.gate is None
+                and ctx.n_tokens <= self.tuning.decode_fused_rows):
+            return False
+        if self._fused_freqs is None:
+            offer = getattr(self.rope, "rotate_half_frequencies", None)
+            freqs = offer() if offer is not None else None
+            self._fused_freqs = freqs if freqs is not None and ops.attention_decode_fused_supported(
+                self.heads, self.kv_heads, self.head_dim, 2 * freqs.numel(), self.qkv.weight.dtype) else False
+        return self._fused_freqs is not False
+
+    def _decode_fused(self, proj: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
+        """From the fused projection's rows (q, k, v and the gate's columns) to the gated heads'
+        outputs [T, H, D] in one kernel."""
+        pool = ctx.states[(call, "kv")]
+        table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
+        layout = self.head_layout
+        longest = ctx.host.longest
+        if self.window is not None:
+            longest = min(longest, self.window)
+        nsplit = self.decode_splits(ctx.n_tokens, self.kv_heads, longest, self.tuning)
+        n = self.qkv_width
+        gate = proj[:, n:n + self.heads] if self.gate_fused else None
+        return ops.attention_decode_fused(
+            proj, pool, layout.q_norm, layout.k_norm if layout.kv_heads else None, layout.eps,
+            self._fused_freqs, gate, ctx.positions, ctx.tok_seq, table, self.heads, self.kv_heads,
+            self.window, self.scale, nsplit, write_kv=bool(layout.kv_heads),
+            carveout=self.tuning.decode_fused_carveout if ctx.n_tokens <= self.tuning.skinny_rows else -1)
 
     def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
               out: torch.Tensor | None = None) -> torch.Tensor:

@@ -237,3 +237,13 @@ class PositionEncoding(Protocol):
         through ``table`` (the block table of the layer's cache group); ``pool`` None: the layer
         has no keys of its own."""
         ...
+
+    # Optional. An encoding that is nothing but a rotate-half rotation of the first R columns of
+    # every q and k head by ``position * frequency`` may say so:
+    #
+    #     def rotate_half_frequencies(self) -> torch.Tensor      # [R / 2] float32, on the device
+    #
+    # A mixer is then free to apply norm, rotation and cache write inside a kernel of its own
+    # (attention does, in steps where every sequence brings one token) instead of calling
+    # ``encode_qk``; both ways give the same bits. Encodings without the method are always
+    # called through ``encode_qk``.

@@ -35,6 +35,15 @@ class Tuning:
     on the GPU (never below ``decode_min_keys`` keys each); never more than
     ``decode_ctas_per_sm`` CTAs per SM (three fit by shared memory, and a few waves of them even
     out the last, partial one).
+    ``decode_fused_rows``: up to that many decoded tokens a layer's norm + rotation + cache write,
+    split attention, merge and gate are one kernel (``ops.attention_decode_fused``); beyond, the
+    separate kernels overlap better (measured: -2.7 % of the step at 1 row, -5 % at 8, +1 % at 16,
+    +5 % at 64). ``decode_fused_carveout``: the share of shared memory that
+    kernel asks for (percent) while the products around it are the weight-streaming kernels (up to
+    ``skinny_rows`` rows): an SM changes its split between shared memory and L1 only when empty,
+    so a kernel that asks for another split than its neighbours cannot start under them, and the
+    L1 it leaves is what their activation loads find; -1 leaves the choice to the driver, which
+    it always is above ``skinny_rows`` rows.
     ``conv_tile``: tokens of a conv tile; up to 16 the tiled kernel takes them (one thread per
     token and 8 channels, a 2,048-token portion of 2,048 channels at memory speed).
     ``fuse_norms``: 16-bit models fold each pre-norm's weight into the columns of the projection
@@ -56,6 +65,8 @@ class Tuning:
     decode_fill: int = 256
     decode_min_keys: int = 128
     decode_ctas_per_sm: int = 12
+    decode_fused_rows: int = 8
+    decode_fused_carveout: int = 62
     conv_tile: int = 16
     fuse_norms: bool = True
 

@@ -32,6 +32,9 @@ class Rope:
         self.inv_freq = inv.to(device).contiguous()
         self.dim = dim
 
+    def rotate_half_frequencies(self) -> torch.Tensor:
+        return self.inv_freq
+
     def encode_qk(self, qkv: torch.Tensor, ctx: StepContext, heads: HeadLayout,
                   pool: torch.Tensor | None, table: torch.Tensor | None) -> torch.Tensor:
         if self.dim > heads.head_dim:
