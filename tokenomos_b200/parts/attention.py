@@ -133,7 +133,7 @@ class Attention:
         longest = ctx.host.longest
         if self.window is not None:
             longest = min(longest, self.window)
-        nsplit = self.decode_splits(ctx.n_tokens, self.kv_heads, longest, self.tuning)
+        nsplit = self.fused_splits(ctx.n_tokens, self.kv_heads, longest, self.tuning)
         n = self.qkv_width
         gate = proj[:, n:n + self.heads] if self.gate_fused else None
         return ops.attention_decode_fused(
@@ -178,6 +178,18 @@ class Attention:
         to_fill = min(-(-tuning.decode_fill // per_split), -(-longest // tuning.decode_min_keys))
         most = tuning.decode_ctas_per_sm * tuning.sm_count
         return max(1, min(-(-most // per_split), max(by_keys, to_fill)))
+
+    @staticmethod
+    def fused_splits(rows: int, kv_heads: int, longest: int, tuning: Tuning = DEFAULT_TUNING) -> int:
+        """The same for the one-kernel form: as many splits as keep every CTA resident at once
+        (``decode_fused_ctas_per_sm`` fit an SM by shared memory; one CTA more than that and the
+        kernel runs in two waves: 0.82 ms a step against 0.76 at 8 rows and 4,000 positions),
+        never fewer than ``decode_min_keys`` keys each. The CTA that merges the splits does so
+        alone, so fewer and longer splits beat the other kernel's rule at every length measured
+        (2,048 to 32,000 positions)."""
+        per_split = max(1, rows * kv_heads)
+        resident = tuning.decode_fused_ctas_per_sm * tuning.sm_count // per_split
+        return max(1, min(resident, -(-longest // tuning.decode_min_keys)))
 
     def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split

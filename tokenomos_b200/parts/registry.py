@@ -38,7 +38,8 @@ class Tuning:
     ``decode_fused_rows``: up to that many decoded tokens a layer's norm + rotation + cache write,
     split attention, merge and gate are one kernel (``ops.attention_decode_fused``); beyond, the
     separate kernels overlap better (measured: -2.7 % of the step at 1 row, -5 % at 8, +1 % at 16,
-    +5 % at 64). ``decode_fused_carveout``: the share of shared memory that
+    +5 % at 64). ``decode_fused_ctas_per_sm``: how many of its CTAs an SM holds (``Attention.fused_splits``).
+    ``decode_fused_carveout``: the share of shared memory that
     kernel asks for (percent) while the products around it are the weight-streaming kernels (up to
     ``skinny_rows`` rows): an SM changes its split between shared memory and L1 only when empty,
     so a kernel that asks for another split than its neighbours cannot start under them, and the
@@ -66,6 +67,7 @@ class Tuning:
     decode_min_keys: int = 128
     decode_ctas_per_sm: int = 12
     decode_fused_rows: int = 8
+    decode_fused_ctas_per_sm: int = 2
     decode_fused_carveout: int = 62
     conv_tile: int = 16
     fuse_norms: bool = True
