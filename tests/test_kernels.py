@@ -571,10 +571,11 @@ def test_sample_is_batch_invariant_and_step_dependent():
 
 # ---- tensor-core attention (bfloat16, head sizes 64 and 128) -------------------------------------
 
-def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None, tc=False):
+def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None, tc=False, gate=None):
     """Like ``attention_case`` but through the tensor-core kernels: multi-token sequences go to
     the prefill kernel (``tc``: the tcgen05 one), single-token ones to the decode kernel (split
-    ``nsplit`` ways)."""
+    ``nsplit`` ways). ``gate`` [T, H] (on the device): the kernels apply the per-head output gate
+    as they write (the reference returned stays ungated)."""
     from tokenomos_b200 import ops
     dtype = torch.bfloat16
     assert ops.attention_mma_supported(H, Hkv, D, dtype)
@@ -617,12 +618,12 @@ def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None,
     if tok0:
         prefill = ops.attention_prefill_tc if tc else ops.attention_prefill_mma
         prefill(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table), i32(tok0), i32(ntok),
-                window, D ** -0.5)
+                window, D ** -0.5, gate)
         if tc:
             assert ops.attention_prefill_tc_status() == 0
     if singles:
         ops.attention_decode_mma(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table),
-                                 i32(singles), window, D ** -0.5, nsplit or 1)
+                                 i32(singles), window, D ** -0.5, nsplit or 1, gate)
     want = []
     for s, (c, n) in enumerate(seqs):
         k = ks[s].repeat_interleave(G, 1)
@@ -768,6 +769,25 @@ def test_attention_decode_fused_refuses_what_it_cannot_take():
         ops.attention_decode_fused(torch.zeros(1, 12 * 48, dtype=torch.bfloat16, device="cuda"), pool, None, None,
                                    1e-5, torch.ones(16, device="cuda"), None, i32([0]), i32([0]),
                                    torch.ones(1, 1, dtype=torch.int32, device="cuda"), 8, 2, None, 0.1, 1)
+
+
+@pytest.mark.parametrize("tc, H, Hkv, D, nsplit", [(True, 32, 8, 64, 1), (False, 32, 8, 64, 5), (False, 4, 2, 128, 2),
+                                                   (True, 6, 3, 64, 3)])
+def test_attention_gate_in_the_epilogue_equals_the_gate_kernel(tc, H, Hkv, D, nsplit):
+    """The per-head output gate applied by the attention kernels as they write gives the bits that
+    the same kernels followed by the gate kernel give (one seed, two runs)."""
+    from tokenomos_b200 import ops
+    seqs = [(0, 1), (17, 3), (0, 40), (40, 100), (333, 1), (5, 2), (64, 64), (1000, 1), (0, 130)]
+    T = sum(n for _, n in seqs)
+    wide = torch.randn(T, H + 11, device="cuda").to(torch.bfloat16)
+    gate = wide[:, 3:3 + H]                                  # a strided view, as the fused projection gives
+    torch.manual_seed(7)
+    plain, want = attention_mma_case(H, Hkv, D, 16, seqs, nsplit=nsplit, tc=tc)
+    torch.manual_seed(7)
+    gated, _ = attention_mma_case(H, Hkv, D, 16, seqs, nsplit=nsplit, tc=tc, gate=gate)
+    ops.head_gate(plain, gate, H, D)
+    assert torch.equal(plain.view(torch.int16), gated.view(torch.int16))
+    close(gated, want * torch.sigmoid(gate.double().cpu())[:, :, None], torch.bfloat16, "gated attention")
 
 
 @pytest.mark.parametrize("H, Hkv, P", [(32, 8, 16), (8, 8, 64), (16, 1, 8), (6, 3, 7), (4, 4, 32)])

@@ -50,6 +50,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// The per-head output gate of (token, head): round(sigmoid(g)), or 1 without a gate. A gated
+// output element is round(round(o) * gate), as the separate gate kernel computes it.
+__device__ __forceinline__ float head_gate_of(const __nv_bfloat16* gate, int64_t ldg, int tok, int head) {
+    if (gate == nullptr) return 1.0f;
+    const float g = __bfloat162float(gate[(size_t)tok * ldg + head]);
+    return round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-g)));
+}
+
 // One 16-row x NK-key block of the online softmax for a warp: S = Q K^T from `ktile`, mask,
 // update (m, l, O) with V from `vtile`. NK is 64 (prefill) or 32 (decode).
 template <int D, int NK>
@@ -186,7 +194,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                         const int* tok_seq, const int* block_table,
                         int bt_stride, const int* tile_tok0,
                         const int* tile_ntok, int H, int Hkv, int P, int window,
-                        float scale, int p_shift) {
+                        float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -273,9 +281,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         if (r >= rows) continue;
         const float inv = l[half] > 0.f ? 1.0f / l[half] : 0.f;
         __nv_bfloat16* dst = out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * D;
+        const float gs = head_gate_of(gate, ldg, tok0 + r / G, kvh * G + r % G);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
-            const uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+            uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+            if (gate != nullptr) {
+                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+                v = pack_bf16(f.x * gs, f.y * gs);
+            }
             *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = v;
         }
     }
@@ -291,7 +304,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                        const int* tok_seq, const int* block_table,
                        int bt_stride, const int* tok_index, int H, int Hkv, int P,
                        int window, float scale, int nsplit, float* part_o,
-                       float* part_ml, int p_shift) {
+                       float* part_ml, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -397,7 +410,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         }
         const int head = kvh * G + r;
         if (nsplit == 1) {
-            out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            float y = round_as<__nv_bfloat16>(L > 0.f ? acc / L : 0.f);
+            if (gate != nullptr) y *= head_gate_of(gate, ldg, tok, head);
+            out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(y);
         } else {
             const size_t slot = ((size_t)i * H + head) * nsplit + split;
             part_o[slot * D + c] = acc;
@@ -414,7 +429,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
                                          const float* part_ml,
                                          __nv_bfloat16* out,
                                          const int* tok_index, int H, int nsplit,
-                                         float scale) {
+                                         float scale, const __nv_bfloat16* gate, int64_t ldg) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
@@ -431,7 +446,9 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
         L += part_ml[(base + s) * 2 + 1] * f;
         acc += part_o[(base + s) * D + c] * f;
     }
-    out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    float y = round_as<__nv_bfloat16>(L > 0.f ? acc / L : 0.f);
+    if (gate != nullptr) y *= head_gate_of(gate, ldg, tok, head);
+    out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(y);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -815,8 +832,8 @@ TK_API int tk_attn_prefill_mma_tokens(int H, int Hkv) { return 64 / (H / Hkv); }
 TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, const int* positions,
                                const int* tok_seq, const int* block_table, int bt_stride,
                                const int* tile_tok0, const int* tile_ntok, int n_tiles, int H,
-                               int Hkv, int D, int P, int window, float scale,
-                               cudaStream_t stream) {
+                               int Hkv, int D, int P, int window, float scale, const void* gate,
+                               int64_t ldg, cudaStream_t stream) {
     TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_prefill_mma: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_mma: bad page size or tile count");
@@ -826,14 +843,15 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
     auto q_ = (const __nv_bfloat16*)q;
     auto p_ = (const __nv_bfloat16*)kv_pool;
     auto o_ = (__nv_bfloat16*)out;
+    auto g_ = (const __nv_bfloat16*)gate;
     if (D == 64) {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P));
+                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg);
     } else {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P));
+                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg);
     }
     TK_CHECK_LAUNCH("attn_prefill_mma");
     return 0;
@@ -848,7 +866,8 @@ TK_API int64_t tk_attn_decode_mma_scratch(int n, int H, int D, int nsplit) {
 TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, const int* positions,
                               const int* tok_seq, const int* block_table, int bt_stride,
                               const int* tok_index, int n, int H, int Hkv, int D, int P, int window,
-                              float scale, int nsplit, float* scratch, cudaStream_t stream) {
+                              float scale, int nsplit, float* scratch, const void* gate, int64_t ldg,
+                              cudaStream_t stream) {
     TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_decode_mma: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n >= 0 && nsplit >= 1 && nsplit <= 65535, "attn_decode_mma: bad sizes");
@@ -864,20 +883,21 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
     auto q_ = (const __nv_bfloat16*)q;
     auto p_ = (const __nv_bfloat16*)kv_pool;
     auto o_ = (__nv_bfloat16*)out;
+    auto g_ = (const __nv_bfloat16*)gate;
     if (D == 64) {
         cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
+                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
+            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg);
     } else {
         cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P));
+                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale);
+            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg);
     }
     TK_CHECK_LAUNCH("attn_decode_merge");
     return 0;
@@ -1019,5 +1039,5 @@ TK_API int tk_attn_decode_mma_static(const void* q, const void* kv_pool, void* o
         g_decode_scratch_ptr[dev] = p;
     }
     return tk_attn_decode_mma(q, kv_pool, out, positions, tok_seq, block_table, bt_stride, tok_index, n, H,
-                              Hkv, D, P, window, scale, nsplit, g_decode_scratch_ptr[dev], stream);
+                              Hkv, D, P, window, scale, nsplit, g_decode_scratch_ptr[dev], nullptr, 0, stream);
 }

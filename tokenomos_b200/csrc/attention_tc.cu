@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_bfloat16* out,
                        const int* positions, const int* tok_seq, const int* block_table, int bt_stride,
                        const int* tile_tok0, const int* tile_ntok, int H, int Hkv, int P, int window,
-                       float scale, int p_shift) {
+                       float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -380,6 +380,12 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             const float l_row = (l_run.x + l_run.y) + (l_alt.x + l_alt.y);
             const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
             __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
+            // the per-head output gate, if the layer has one: round(round(o) * round(sigmoid(g)))
+            float gs = 1.0f;
+            if (gate != nullptr && dst != nullptr) {
+                const float gv = __bfloat162float(gate[(size_t)(tok0 + r / G) * ldg + kvh * G + r % G]);
+                gs = round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-gv)));
+            }
 #pragma unroll
             for (int c = 0; c < AT_D; c += 16) {
                 float part[16];
@@ -387,8 +393,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                 if (dst != nullptr) {
                     uint32_t packed[8];
 #pragma unroll
-                    for (int e = 0; e < 16; e += 2)
+                    for (int e = 0; e < 16; e += 2) {
                         packed[e >> 1] = pack_bf16_pair(part[e] * inv, part[e + 1] * inv);
+                        if (gate != nullptr) {
+                            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&packed[e >> 1]));
+                            packed[e >> 1] = pack_bf16_pair(f.x * gs, f.y * gs);
+                        }
+                    }
                     *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
@@ -427,10 +438,13 @@ TK_API int tk_attn_prefill_tc_status() {
 
 // q: [T, H, 64] bfloat16; kv_pool: [pages, 2, Hkv, P, 64]; out: [T, H, 64]; tiles of at most
 // tk_attn_prefill_tc_tokens tokens of one sequence with consecutive positions; window 0 = none.
+// gate: [T, >= H] bfloat16 with rows ldg apart, the per-head output gate applied to what is
+// written (null: none).
 TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, const int* positions,
                               const int* tok_seq, const int* block_table, int bt_stride,
                               const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
-                              int P, int window, float scale, cudaStream_t stream) {
+                              int P, int window, float scale, const void* gate, int64_t ldg,
+                              cudaStream_t stream) {
     TK_CHECK_ARG(tk_attn_prefill_tc_supported(H, Hkv, D), "attn_prefill_tc: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64, a group that divides 128)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_tc: bad page size or tile count");
@@ -445,7 +459,8 @@ TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, con
     if (e == cudaSuccess)
         e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv), dim3(AT_THREADS), smem, stream,
                       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions, tok_seq,
-                      block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, shift);
+                      block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, shift,
+                      (const __nv_bfloat16*)gate, ldg);
     if (e != cudaSuccess) {
         tk_set_error("attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         cudaGetLastError();

@@ -268,19 +268,32 @@ def _check_attention(q, kv_pool, name):
     return T, H, D, Hkv, P
 
 
+def _gate_view(gate: torch.Tensor | None, T: int, H: int, name: str):
+    """(pointer, row stride) of a per-head output gate [T, H] (a bfloat16 view with unit column
+    stride), or (None, 0)."""
+    if gate is None:
+        return None, 0
+    if not gate.is_cuda or gate.dtype != torch.bfloat16 or tuple(gate.shape) != (T, H) or gate.stride(1) != 1:
+        raise KernelError(f"{name}: gate must be a bfloat16 [T, H] CUDA view with unit column stride")
+    return gate.data_ptr(), gate.stride(0)
+
+
 def attention_prefill_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                           positions: torch.Tensor, tok_seq: torch.Tensor,
                           block_table: torch.Tensor, tile_tok0: torch.Tensor,
-                          tile_ntok: torch.Tensor, window: int | None, scale: float) -> None:
+                          tile_ntok: torch.Tensor, window: int | None, scale: float,
+                          gate: torch.Tensor | None = None) -> None:
     """Tensor-core attention for tiles of ``attention_prefill_mma_tokens`` tokens of one
-    sequence; writes the tiles' rows of ``out`` [T, H, D]."""
+    sequence; writes the tiles' rows of ``out`` [T, H, D], times the per-head output gate
+    ``round(sigmoid(gate))`` [T, H] if one is given."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_mma")
+    g_ptr, ldg = _gate_view(gate, T, H, "attention_prefill_mma")
     _lib.call("tk_attn_prefill_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
               _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
-              float(scale), _stream())
+              float(scale), g_ptr, ldg, _stream())
 
 
 def attention_prefill_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -297,16 +310,18 @@ def attention_prefill_tc_tokens(heads: int, kv_heads: int) -> int:
 def attention_prefill_tc(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                          positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                          tile_tok0: torch.Tensor, tile_ntok: torch.Tensor, window: int | None,
-                         scale: float) -> None:
+                         scale: float, gate: torch.Tensor | None = None) -> None:
     """``attention_prefill_mma`` on tcgen05.mma with the accumulators in tensor memory, for tiles
-    of ``attention_prefill_tc_tokens`` tokens of one sequence; writes the tiles' rows of ``out``."""
+    of ``attention_prefill_tc_tokens`` tokens of one sequence; writes the tiles' rows of ``out``
+    (gated like ``attention_prefill_mma``'s)."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_tc")
+    g_ptr, ldg = _gate_view(gate, T, H, "attention_prefill_tc")
     _lib.call("tk_attn_prefill_tc", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
               _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
-              float(scale), _stream())
+              float(scale), g_ptr, ldg, _stream())
 
 
 def attention_prefill_tc_status() -> int:
@@ -317,13 +332,15 @@ def attention_prefill_tc_status() -> int:
 def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                          positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                          tok_index: torch.Tensor | None, window: int | None, scale: float,
-                         nsplit: int) -> None:
+                         nsplit: int, gate: torch.Tensor | None = None) -> None:
     """Tensor-core attention for sequences that bring one token (``tok_index``: their rows in
     the packed batch; None: every row of ``q`` is one, in order, which spares the kernel a
     lookup), each split ``nsplit`` ways over its keys; partial results go through scratch memory
-    that this function allocates and a merge kernel. Writes those rows of ``out`` [T, H, D]."""
+    that this function allocates and a merge kernel. Writes those rows of ``out`` [T, H, D]
+    (gated like ``attention_prefill_mma``'s)."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tok_index)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_decode_mma")
+    g_ptr, ldg = _gate_view(gate, T, H, "attention_decode_mma")
     n = tok_index.numel() if tok_index is not None else T
     scratch = None
     if nsplit > 1:
@@ -331,7 +348,8 @@ def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tens
     _lib.call("tk_attn_decode_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tok_index, "tok_index") if tok_index is not None else None),
-              n, H, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), _stream())
+              n, H, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), g_ptr, ldg,
+              _stream())
 
 
 def attention_decode_fused_supported(heads: int, kv_heads: int, head_dim: int, rotary: int,

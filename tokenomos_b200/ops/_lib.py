@@ -38,12 +38,12 @@ _SIGNATURES = {
     "tk_attn_generic": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P],
     "tk_attn_mma_supported": [I, I, I],
     "tk_attn_prefill_mma_tokens": [I, I],
-    "tk_attn_prefill_mma": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
+    "tk_attn_prefill_mma": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, P],
     "tk_attn_prefill_tc_supported": [I, I, I],
     "tk_attn_prefill_tc_tokens": [I, I],
     "tk_attn_prefill_tc_status": [],
-    "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P],
-    "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P],
+    "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, P],
+    "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P, L, P],
     "tk_attn_decode_fused_supported": [I, I, I, I],
     "tk_attn_decode_fused_max_splits": [I, I, I],
     "tk_attn_decode_fused": [P, L, P, P, P, P, F, P, I, P, L, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],

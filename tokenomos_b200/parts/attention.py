@@ -67,18 +67,17 @@ class Attention:
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
-        proj = self.qkv(x)
-        if self._fused_decode(ctx):
-            out = self._decode_fused(proj, ctx, call)
-        elif self.gate_fused:
-            n = self.qkv_width
-            out = self._core(proj[:, :n], ctx, call)
-            ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
-        else:
-            out = self._core(proj, ctx, call)
-            if self.gate is not None:
-                ops.head_gate(out, self.gate(x), self.heads, self.head_dim)
+        out = self._heads(self.qkv(x), x, ctx, call)
         return self.o(out.view(T, self.heads * self.head_dim))
+
+    def _heads(self, proj: torch.Tensor, x: torch.Tensor | None, ctx: StepContext, call: int) -> torch.Tensor:
+        """From the fused projection's rows to the gated heads' outputs [T, H, D]."""
+        if self._fused_decode(ctx):
+            return self._decode_fused(proj, ctx, call)
+        n = self.qkv_width
+        if self.gate_fused:
+            return self._core(proj[:, :n], ctx, call, proj[:, n:n + self.heads])
+        return self._core(proj, ctx, call, self.gate(x) if self.gate is not None else None)
 
     # ---- the block's norm and residual add taken into the two products (parts.contract) ----
 
@@ -98,13 +97,7 @@ class Attention:
         self.o.note("skinny+add")
         T = stream.shape[0]
         proj = ops.gemm_skinny(stream, self.qkv.weight, self.qkv.bias, norm_eps=eps)
-        n = self.qkv_width
-        if self._fused_decode(ctx):
-            out = self._decode_fused(proj, ctx, call)
-        else:
-            out = self._core(proj[:, :n] if self.gate_fused else proj, ctx, call)
-            if self.gate_fused:
-                ops.head_gate(out, proj[:, n:n + self.heads], self.heads, self.head_dim)
+        out = self._heads(proj, None, ctx, call)
         return ops.gemm_skinny(out.view(T, self.heads * self.head_dim), self.o.weight, self.o.bias,
                                residual=stream)
 
@@ -143,25 +136,25 @@ class Attention:
             carveout=self.tuning.decode_fused_carveout if ctx.n_tokens <= self.tuning.skinny_rows else -1)
 
     def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
-              out: torch.Tensor | None = None) -> torch.Tensor:
-        """From the fused projection's output to the heads' outputs [T, H, D] (into ``out`` if
-        given): q/k norm, rotation, cache write, attention over the cache."""
+              gate: torch.Tensor | None = None) -> torch.Tensor:
+        """From q, k, v to the heads' outputs [T, H, D]: q/k norm, rotation, cache write, attention
+        over the cache, the per-head output gate ``gate`` [T, H] if the layer has one (the
+        tensor-core kernels apply it as they write, the generic one is followed by a kernel)."""
         pool = ctx.states[(call, "kv")]
         table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
         own_kv = self.head_layout.kv_heads
         q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
                                 table if own_kv else None)
         if ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
-            return self._attend_mma(q, pool, table, ctx, out)
+            return self._attend_mma(q, pool, table, ctx, gate)
         rows = ops.attention_rows()
         group = self.heads // self.kv_heads
         per_tile = max(1, rows // group)
         _, tok0, _, ntok = ctx.tiles(per_tile)
-        res = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
+        out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
                             self.window, self.scale)
-        if out is None:
-            return res
-        out.copy_(res.view_as(out))
+        if gate is not None:
+            ops.head_gate(out, gate, self.heads, self.head_dim)
         return out
 
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
@@ -191,11 +184,10 @@ class Attention:
         resident = tuning.decode_fused_ctas_per_sm * tuning.sm_count // per_split
         return max(1, min(resident, -(-longest // tuning.decode_min_keys)))
 
-    def _attend_mma(self, q, pool, table, ctx: StepContext, out=None) -> torch.Tensor:
+    def _attend_mma(self, q, pool, table, ctx: StepContext, gate=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
         over their keys so that a small batch still fills the GPU."""
-        if out is None:
-            out = torch.empty_like(q)
+        out = torch.empty_like(q)
         # prompt portions: the tcgen05 kernel (tiles of 128 rows) where it takes the shape, else
         # the mma.sync one (tiles of 64 rows)
         tc = self.prefill_tc and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim,
@@ -205,7 +197,7 @@ class Attention:
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
         if tok0.numel():
             (ops.attention_prefill_tc if tc else ops.attention_prefill_mma)(
-                q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window, self.scale)
+                q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window, self.scale, gate)
         # every sequence brings one token: row i is sequence i's, no list of rows needed
         decode_only = ctx.host.decode_only
         singles = None if decode_only else ctx.singles()
@@ -216,7 +208,7 @@ class Attention:
             rows = ctx.n_tokens if decode_only else singles.numel()
             nsplit = self.decode_splits(rows, self.kv_heads, longest, self.tuning)
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
-                                     self.window, self.scale, nsplit)
+                                     self.window, self.scale, nsplit, gate)
         return out
 
 
