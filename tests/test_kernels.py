@@ -155,6 +155,29 @@ def test_gemm_float32_is_not_tf32():
     assert (want - 64.0).abs().min().item() > 1e-2   # TF32 inputs would give exactly 64
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_scale_rows_and_logit_options(dtype):
+    from tokenomos_b200 import ops
+    x = torch.randn(7, 301).to(dtype)
+    got = ops.scale_rows(dev(x.clone()), 3.3)
+    s = torch.tensor(3.3).to(dtype).double()                  # the scale is rounded to the storage type first
+    assert torch.equal(got.cpu(), (x.double() * s).to(dtype))
+    logits = torch.randn(5, 1003) * 30
+    strided = dev(torch.cat((logits, torch.zeros(5, 13)), 1))[:, :1003]       # rows 1016 apart
+    ids = [0, 17, 1002]
+    ops.logit_options(strided, 12.5, i32(ids))
+    want = 12.5 * torch.tanh(logits.double() / 12.5)
+    keep = [c for c in range(1003) if c not in ids]
+    assert torch.isneginf(strided[:, ids]).all()
+    assert (strided.double().cpu()[:, keep] - want[:, keep]).abs().max().item() < 1e-5
+    only_suppress = dev(logits.clone())
+    ops.logit_options(only_suppress, None, i32([5]))
+    assert torch.isneginf(only_suppress[:, 5]).all() and torch.equal(only_suppress[:, 6:].cpu(), logits[:, 6:])
+    untouched = dev(logits.clone())
+    ops.logit_options(untouched, None, None)
+    assert torch.equal(untouched.cpu(), logits)
+
+
 # ---- q/k norm + rotary + cache write -----------------------------------------------------------
 
 def rope_ref(x, pos, inv_freq, rot):

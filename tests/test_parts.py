@@ -264,6 +264,57 @@ def test_toy_architectures_generate_through_the_entry_point_with_and_without_gra
             assert row.max().item() - row[tok].item() <= 1e-4, (mixer, i, tok, int(row.argmax()))
 
 
+@pytest.mark.parametrize("work, dtype", [("fp32", torch.float32), ("bf16", torch.bfloat16)])
+def test_options_around_the_layer_stack_are_data_of_the_model(work, dtype, tmp_path):
+    """An embedding scale, a soft cap on the logits and a list of ids that are never produced come
+    from the architecture's declaration (``ModelSpec``), with no change to ``Stack``: a toy
+    configuration sets all three; stepping whole and in portions, eagerly and through captured
+    graphs, agrees with the plain restatement, and sampling at a high temperature never yields a
+    suppressed id."""
+    import toy_parts
+    from tokenomos_b200 import LLM, SamplingParams, models
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.engine.step import StepEntry, StepFunction
+    from tokenomos_b200.weights import write_model_folder
+
+    raw = toy_parts.toy_config("attention_scaled", "swiglu", embed_scale=3.5, logit_softcap=4.0,
+                               suppress=[0, 7, 59])
+    folder = write_model_folder(tmp_path / "toy_options", raw, seed=3, std=0.3)
+    model = models.load(folder, "cuda", models.configure(folder, work=work))
+    assert model.embed_scale == 3.5 and model.logit_softcap == 4.0 and model.suppress.tolist() == [0, 7, 59]
+    cache = CacheManager(model.state_specs(), 4, 24, 2, dtype, "cuda", max_len=64, poison=True)
+    step = StepFunction(model, cache)
+    T = 19
+    ids = torch.randint(0, raw["vocab_size"], (T,)).tolist()
+    cache.admit("w")
+    whole = step.run([StepEntry("w", ids, list(range(T)))])
+    cache.release("w")
+    cache.admit("p")
+    parts = torch.cat([step.run([StepEntry("p", ids[a:b], list(range(b - a)))]) for a, b in ((0, 5), (5, 7), (7, T))])
+    want = toy_parts.toy_forward(raw, _toy_weights(folder), ids)
+    kept = [t for t in range(raw["vocab_size"]) if t not in raw["suppress"]]
+    assert torch.isneginf(whole[:, raw["suppress"]]).all() and torch.isneginf(parts[:, raw["suppress"]]).all()
+    assert whole[:, kept].abs().max().item() <= 4.0            # the cap holds
+    tol = 2e-4 if dtype == torch.float32 else 4e-2
+    scale = want[:, kept].abs().max().item()
+    assert (whole.double().cpu()[:, kept] - want[:, kept]).abs().max().item() < tol * scale
+    assert (parts.double().cpu()[:, kept] - want[:, kept]).abs().max().item() < tol * scale
+    # through the entry point, captured: the suppressed ids never come out, and eager == captured
+    prompts = [ids[:9], ids[3:8], ids[5:]]
+    kw = dict(work=work, page=4, max_len=48, slots=3, pages=40, prefill_budget=10, poison=True)
+    p = SamplingParams(max_tokens=8, temperature=1.5, seed=2)
+    with LLM(str(folder), graphs=False, **kw) as llm:
+        eager = llm.generate(prompts, p)
+    with LLM(str(folder), graphs=True, **kw) as llm:
+        llm.engine.step_fn.capture_after = 0
+        graphed = llm.generate(prompts, p)
+        assert llm.engine.stats.graph_steps > 0
+    for a, b in zip(eager, graphed):
+        if dtype == torch.float32:       # (in bfloat16 a sampled token may sit on a rounding edge)
+            assert a.token_ids == b.token_ids
+        assert not (set(a.token_ids) | set(b.token_ids)) & set(raw["suppress"])
+
+
 @pytest.mark.filterwarnings("ignore::pytest.PytestUnhandledThreadExceptionWarning")
 def test_a_part_that_reads_host_lists_in_a_captured_step_fails_loudly(tmp_path):
     """A mixer that claims ``capture_safe`` but plans from ``ctx.host``'s per-sequence lists would

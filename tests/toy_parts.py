@@ -187,6 +187,8 @@ class ToyConfig:
             setattr(self, key, raw[key])
         self.heads, self.kv_heads, self.head_dim = raw.get("heads", 4), raw.get("kv_heads", 2), raw.get("head_dim", 16)
         self.inter = raw.get("inter", 2 * raw["width"])
+        self.embed_scale, self.logit_softcap = raw.get("embed_scale"), raw.get("logit_softcap")
+        self.suppress = tuple(raw.get("suppress", ()))
 
     @classmethod
     def from_dict(cls, raw: dict) -> "ToyConfig":
@@ -239,7 +241,8 @@ class ToyArch:
                 "mixer": mixer, "ffn": ffn, "pre_mixer_norm": norm(f"{p}n1", d), "pre_ffn_norm": norm(f"{p}n2", d),
                 "post_mixer_norm": None, "post_ffn_norm": None}))
         return ModelSpec(d, c.vocab_size, TensorDecl("toy.embed.weight", (c.vocab_size, d), ROLE_EMBEDDING),
-                         tuple(blocks), tuple(LayerCall(i) for i in range(c.layers)), norm("toy.final", d), None)
+                         tuple(blocks), tuple(LayerCall(i) for i in range(c.layers)), norm("toy.final", d), None,
+                         embed_scale=c.embed_scale, logit_softcap=c.logit_softcap, suppress=tuple(c.suppress))
 
 
 models.register(ToyArch())
@@ -260,6 +263,8 @@ def toy_forward(raw: dict, w: dict, ids: list[int]) -> torch.Tensor:
     T, d = len(ids), c.width
     H, Hkv, D = c.heads, c.kv_heads, c.head_dim
     r = w["toy.embed.weight"][ids]
+    if c.embed_scale is not None:
+        r = r * c.embed_scale
     causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
     for i in range(c.layers):
         p = f"toy.{i}."
@@ -298,4 +303,9 @@ def toy_forward(raw: dict, w: dict, ids: list[int]) -> torch.Tensor:
             r = r + f
         else:
             r = r + plain_lfm3.swiglu(x, w, p, torch.float64)
-    return plain_lfm3.rmsnorm(r, w["toy.final.weight"], c.eps) @ w["toy.embed.weight"].T
+    logits = plain_lfm3.rmsnorm(r, w["toy.final.weight"], c.eps) @ w["toy.embed.weight"].T
+    if c.logit_softcap is not None:
+        logits = c.logit_softcap * torch.tanh(logits / c.logit_softcap)
+    if c.suppress:
+        logits[:, list(c.suppress)] = float("-inf")
+    return logits

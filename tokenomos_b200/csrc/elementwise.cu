@@ -492,3 +492,68 @@ TK_API int tk_head_gate(void* x, const void* g, int64_t ldg, int rows, int heads
     TK_CHECK_LAUNCH("head_gate");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// model-level options some architectures have around the layer stack: a scale on the embedding
+// rows, a soft cap on the logits and a list of token ids that are never produced
+// (Tokenomos models/blocks/decoder.py:167-171,185-192)
+// ---------------------------------------------------------------------------------------------
+// x[i] = round(x[i] * round(scale)), both roundings to the storage type
+template <typename T>
+__global__ void scale_rows_kernel(T* x, int64_t total, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float s = round_as<T>(scale);
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (; i < total; i += step) x[i] = from_f<T>(to_f<T>(x[i]) * s);
+}
+
+TK_API int tk_scale_rows(void* x, int64_t total, float scale, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(total >= 0, "scale_rows: bad size");
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int64_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == TK_F32)
+        tk_launch(scale_rows_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, total, scale);
+    else if (dtype == TK_BF16)
+        tk_launch(scale_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)x, total, scale);
+    else
+        TK_CHECK_ARG(false, "scale_rows: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("scale_rows");
+    return 0;
+}
+
+// logits [rows, vocab] float32, in place: cap > 0: x = cap * tanh(x / cap); then the `n_suppress`
+// ids of `suppress` (each inside the vocabulary) become -inf in every row
+__global__ void logit_options_kernel(float* logits, int64_t ld, int rows, int vocab, float cap,
+                                     const int* suppress, int n_suppress) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = (int64_t)rows * vocab;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    const float inv = cap > 0.f ? 1.0f / cap : 0.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int col = (int)(i % vocab);
+        float* at = logits + (i / vocab) * ld + col;
+        bool hit = false;
+        for (int k = 0; k < n_suppress; ++k) hit = hit || suppress[k] == col;
+        if (hit) *at = -INFINITY;
+        else if (cap > 0.f) *at = cap * tanhf(*at * inv);
+    }
+}
+
+TK_API int tk_logit_options(float* logits, int64_t ld, int rows, int vocab, float cap, const int* suppress,
+                            int n_suppress, cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && vocab > 0 && ld >= vocab && n_suppress >= 0, "logit_options: bad sizes");
+    TK_CHECK_ARG(n_suppress == 0 || suppress != nullptr, "logit_options: the suppress list is missing");
+    if (rows == 0 || (cap <= 0.f && n_suppress == 0)) return 0;
+    const int threads = 256;
+    const int64_t want = ((int64_t)rows * vocab + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    tk_launch(logit_options_kernel, dim3(blocks), dim3(threads), 0, stream, logits, ld, rows, vocab, cap, suppress,
+              n_suppress);
+    TK_CHECK_LAUNCH("logit_options");
+    return 0;
+}

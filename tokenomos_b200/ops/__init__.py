@@ -138,6 +138,27 @@ def gather_rows_select(table: torch.Tensor, ids_host: torch.Tensor, use_prev: to
     return out
 
 
+def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """In place ``x = round(x * round(scale))`` (both to ``x``'s type): an embedding scale."""
+    _cuda(x)
+    if not x.is_contiguous():
+        raise KernelError("scale_rows: x must be contiguous")
+    _lib.call("tk_scale_rows", _ptr(x), x.numel(), float(scale), _dtype_code(x), _stream())
+    return x
+
+
+def logit_options(logits: torch.Tensor, softcap: float | None, suppress: torch.Tensor | None) -> torch.Tensor:
+    """In place on float32 ``logits`` [rows, vocab]: ``softcap * tanh(logits / softcap)`` if a cap
+    is given, then ``-inf`` at the token ids of ``suppress`` (int32, each inside the vocabulary)."""
+    _cuda(logits, suppress)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logit_options: logits must be float32 [rows, vocab] with contiguous rows")
+    n = 0 if suppress is None else _i32(suppress, "suppress").numel()
+    _lib.call("tk_logit_options", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
+              float(softcap or 0.0), _ptr(suppress), n, _stream())
+    return logits
+
+
 def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor | None,
                 eps: float, pre: tuple[torch.Tensor, float] | None = None):
     """``stream = residual + [pre-norm](x)``; ``y = rmsnorm(stream) * weight``.

@@ -53,6 +53,8 @@ _SIGNATURES = {
     "tk_gemm_simt": [P, L, P, L, P, P, L, I, I, I, I, I, P],
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, F, P, L, P],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
+    "tk_scale_rows": [P, L, F, I, P],
+    "tk_logit_options": [P, L, I, I, F, P, I, P],
     "tk_gemm_tc_status": [],
     "tk_sample_status": [],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, I, P],

@@ -86,8 +86,18 @@ def build_prenorm(parts: dict) -> PreNormBlock:
 
 class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
-                 head: Linear | None, tuning: Tuning = DEFAULT_TUNING):
+                 head: Linear | None, tuning: Tuning = DEFAULT_TUNING, embed_scale: float | None = None,
+                 logit_softcap: float | None = None, suppress: tuple[int, ...] = ()):
         self.embedding = embedding
+        self.embed_scale = None if embed_scale is None else float(embed_scale)
+        self.logit_softcap = None if logit_softcap is None else float(logit_softcap)
+        if self.logit_softcap is not None and self.logit_softcap <= 0:
+            raise ValueError(f"a logit soft cap of {logit_softcap}: it must be positive")
+        bad = [t for t in suppress if not 0 <= int(t) < embedding.shape[0]]
+        if bad:
+            raise ValueError(f"suppressed token ids {bad} outside the vocabulary of {embedding.shape[0]}")
+        self.suppress = (torch.tensor([int(t) for t in suppress], dtype=torch.int32, device=embedding.device)
+                         if suppress else None)
         self.blocks = blocks
         self.order = list(order)
         self.final_norm = final_norm
@@ -130,13 +140,15 @@ class Stack:
         return out
 
     def embed(self, ids: torch.Tensor) -> torch.Tensor:
-        return ops.gather_rows(self.embedding, ids)
+        h = ops.gather_rows(self.embedding, ids)
+        return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
 
     def embed_fed(self, ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
                   slot: torch.Tensor) -> torch.Tensor:
         """Embedding rows of a decode step whose ids may still be on the device: row r takes
         ``last_token[slot[r]]`` where ``use_prev[r]`` is set, else ``ids_host[r]``."""
-        return ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot)
+        h = ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot)
+        return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
 
     def forward(self, h: torch.Tensor, ctx: StepContext):
         """Runs the layer list; returns ``(h, residual, pending)`` of the last block: the final
@@ -157,4 +169,7 @@ class Stack:
             if residual is not None:
                 residual = ops.gather_rows(residual, rows)
         y, _ = self.final_norm.add_norm(h, residual, pending)
-        return self.head(y, out_dtype=torch.float32)
+        out = self.head(y, out_dtype=torch.float32)
+        if self.logit_softcap is not None or self.suppress is not None:
+            ops.logit_options(out, self.logit_softcap, self.suppress)
+        return out

@@ -43,4 +43,5 @@ def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
     final_norm = _part("norm", spec.final_norm, tensors, rt)
     head = Linear(tensors[spec.head.name], tuning=rt.tuning) if spec.head is not None else None
     return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head,
-                 tuning=rt.tuning)
+                 tuning=rt.tuning, embed_scale=spec.embed_scale, logit_softcap=spec.logit_softcap,
+                 suppress=spec.suppress)

@@ -75,6 +75,12 @@ class ModelSpec:
     # model does not declare is an error; tensors elsewhere (another tower of a multimodal
     # folder, a stored copy of a tied head) are not this model's business. Empty: every name.
     scope: tuple[str, ...] = ()
+    # options around the layer stack that some architectures have (None / empty: absent):
+    # the embedding rows times a constant (rounded to the work type, as is the product); the
+    # logits through ``cap * tanh(logits / cap)``; token ids whose logits are -inf
+    embed_scale: float | None = None
+    logit_softcap: float | None = None
+    suppress: tuple[int, ...] = ()
 
     def tensor_decls(self) -> list[TensorDecl]:
         """Every tensor the model reads, in a fixed order (the order random weights are drawn)."""
