@@ -462,6 +462,39 @@ def test_conv_gated_blocked_columns_equal_plain_columns():
         assert all(torch.equal(o, outs[0]) for o in outs) and all(torch.equal(st, states[0]) for st in states)
 
 
+@pytest.mark.parametrize("W, tile", [(3, 16), (4, 16), (8, 16), (3, 8), (2, 4)])
+def test_conv_gated_many_tiles_per_block_equal_the_walking_kernel(W, tile):
+    """Enough tiles that a block of the tiled kernel takes several in a row through its staging
+    pipeline (more than it has stages), in both row layouts, with portions that start at a cached
+    position, at position 0 and one shorter than the state: outputs and states are the walking
+    kernel's, bit for bit."""
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.shortconv import interleave_bcx
+    dtype, d, slots = torch.bfloat16, 1000, 6
+    taps, bias = torch.randn(d, W), torch.randn(d)
+    seqs = [(2, 0, 1500), (1, 7, 1), (3, 3, 2500), (4, 5, 37), (5, 0, max(1, W - 2))]
+    T = sum(n for _, _, n in seqs)
+    bcx = torch.randn(T, 3 * d).to(dtype)
+    blocked = interleave_bcx(bcx.t().contiguous(), 8).t().contiguous()
+    cu = [0]
+    for _, _, n in seqs:
+        cu.append(cu[-1] + n)
+    tiles = [(s_, o, min(tile, n - o)) for s_, (_, _, n) in enumerate(seqs) for o in range(0, n, tile)]
+    tok0 = [cu[s_] + o for s_, o, _ in tiles]
+    state0 = torch.randn(slots, W - 1, d).to(dtype)
+    outs, states = [], []
+    for rows, block, cap, first in ((bcx, 0, 0, None), (bcx, 0, tile, None), (blocked, 8, tile, None),
+                                    (blocked, 8, tile, i32(tok0))):
+        state = dev(state0).clone()
+        outs.append(ops.conv_gated(dev(rows), dev(taps), dev(bias), state, i32(cu),
+                                   i32([c for _, c, _ in seqs]), i32([s_ for s_, _, _ in seqs]),
+                                   i32([t[0] for t in tiles]), i32([t[1] for t in tiles]),
+                                   i32([t[2] for t in tiles]), block, cap, first))
+        states.append(state)
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+    assert all(torch.equal(st, states[0]) for st in states[1:])
+
+
 @pytest.mark.parametrize("W, d, K, M, with_bias", [(3, 64, 128, 8, False), (2, 40, 72, 5, True),
                                                   (4, 96, 520, 13, True), (8, 24, 64, 1, False),
                                                   (3, 2048, 2048, 8, False)])

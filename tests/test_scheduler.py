@@ -308,3 +308,22 @@ def test_decode_attention_split_rule():
                 assert n * rows * kv <= t.decode_ctas_per_sm * t.sm_count + rows * kv
                 assert n >= prev                    # a longer context never gets fewer splits
                 prev = n
+
+
+def test_one_kernel_decode_attention_split_rule():
+    """The one-kernel form's splits: as many as keep every CTA resident at once (two an SM), never
+    below 128 keys a split, at least one."""
+    from tokenomos_b200.parts.attention import Attention
+    from tokenomos_b200.parts.registry import Tuning
+    f, t = Attention.fused_splits, Tuning()
+    assert f(8, 8, 4096) == 4 and f(8, 8, 32768) == 4 and f(8, 8, 300) == 3
+    assert f(1, 8, 4096) == 32 and f(1, 8, 32768) == 37 and f(2, 8, 4096) == 18 and f(4, 8, 4096) == 9
+    assert f(8, 32, 4096) == 1 and f(8, 64, 4096) == 1              # more CTAs than fit even unsplit: one each
+    for rows in (1, 2, 3, 5, 8):
+        for kv in (1, 2, 3, 8):
+            for longest in (1, 127, 128, 129, 2048, 10 ** 5):
+                n = f(rows, kv, longest)
+                assert 1 <= n <= max(1, -(-longest // t.decode_min_keys))
+                assert n == 1 or n * rows * kv <= t.decode_fused_ctas_per_sm * t.sm_count
+    half = Tuning(sm_count=74)
+    assert f(8, 8, 4096, half) == 2

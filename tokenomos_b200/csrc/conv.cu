@@ -242,142 +242,236 @@ __global__ void conv_gated_vec_kernel(const T* bcx, int64_t stride, int d,
     }
 }
 
-// The form for prompt portions: a block takes a tile of up to CONV_TT tokens and CONV_CG groups
-// of VEC channels, one thread per (token, group). Every thread loads its own row's B, C and X
-// (16 bytes each), the first W - 1 token rows of the block also load the W - 1 inputs before the
-// tile (rows of the portion, or the state), u = B * X goes to shared memory, and after one
-// barrier every thread sums its W taps over shared memory. Few registers, every load of the
-// block in flight at once: the kernel runs at memory speed where the walking form above is bound
-// by the latency of its dependent trips (a 2,048-token portion of 2,048 channels: 17 us there).
+// The form for prompt portions: a block of CONV_TT x CONV_CG threads takes tiles of up to CONV_TT
+// tokens and CONV_CG groups of VEC channels, one thread per (token, group), `per_block` tiles of
+// the list one after the other. A tile's rows (B, C and X of its tokens as stored, and the W - 1
+// rows before it: rows of the portion, or the state with X = 1, or zeros) are copied into shared
+// memory with cp.async, three tiles ahead of the one that is computed, and the tile list's
+// entries are read a tile earlier still. A thread then sums its W taps over
+// round(B * X) of its own and the W - 1 rows before, straight from the staged rows (16 bytes
+// per thread and row, no bank conflicts), its taps in registers: one barrier per tile.
+// (Earlier forms, a 2,048-token portion of 2,048 channels: a thread that walks 8 tokens 17 us;
+// one tile per block through registers, u = B * X as 32-bit values in a second shared array
+// 15.7 us, the same with this pipeline 16-17 us: the shared-memory pipe was two thirds busy, half
+// of it bank conflicts of 32-byte rows, with two more barriers per tile.)
 constexpr int CONV_MAX_W = 8;
+constexpr int CONV_STAGES = 4;       // tiles whose rows are staged: one computed, three on their way
 
-template <typename T, int W, int CONV_TT, int CONV_CG>
-__global__ void __launch_bounds__(CONV_TT* CONV_CG)
+__device__ __forceinline__ void conv_cp16(void* dst, const void* src, bool valid) {
+    const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;                    // 0: sixteen zero bytes, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d32), "l"(src), "r"(bytes));
+}
+
+// a tile's entry of the lists, and what only a portion's first tile needs beside it
+struct ConvTile {
+    int off, n, start, len, ctx, slot;
+};
+
+// INTER: a row of bcx holds (B, C, X) of 8 or 4 channels in turn (`block` == VEC, what the decode
+// path's projection wants its rows as): a block's piece of a row is then one run of 3 CH values,
+// copied as it lies and picked apart when read.
+template <typename T, int W, int CONV_TT, int CONV_CG, bool INTER>
+__global__ void __launch_bounds__(CONV_TT* CONV_CG, W <= 4 ? 3 : 2)
 conv_gated_tile_kernel(const T* bcx, int64_t stride, int d, const float* __restrict__ w,
                        const float* __restrict__ bias, T* state, T* out, const int* cu,
                        const int* seq_ctx, const int* seq_slot, const int* tile_seq,
-                       const int* tile_off, const int* tile_n, const int* tile_tok0, int block) {
+                       const int* tile_off, const int* tile_n, const int* tile_tok0, int block,
+                       int n_tiles, int per_block) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int CH = CONV_CG * VEC;                         // channels of a block
-    __shared__ __align__(16) float u_s[CONV_TT + W - 1][CH];
-    __shared__ __align__(16) float taps_s[W][CH];
+    constexpr int HR = W - 1;                                 // rows before a tile
+    extern __shared__ __align__(16) unsigned char conv_smem[];
+    // [stage][B | X][HR + TT][CH] and [stage][C][TT][CH], as stored; INTER: [stage][HR + TT][3 CH]
+    T* raw = reinterpret_cast<T*>(conv_smem);
+    constexpr int STAGE = INTER ? 3 * (HR + CONV_TT) * CH : (2 * (HR + CONV_TT) + CONV_TT) * CH;
+    // where this thread's B, X and C of staged row r lie, from the stage's start
+    auto at_b = [&](int r) { return INTER ? r * 3 * CH + (int)threadIdx.x * 3 * VEC : r * CH + (int)threadIdx.x * VEC; };
+    auto at_x = [&](int r) { return INTER ? at_b(r) + 2 * VEC : (HR + CONV_TT) * CH + at_b(r); };
+    auto at_c = [&](int r) { return INTER ? at_b(r + HR) + VEC : 2 * (HR + CONV_TT) * CH + r * CH + (int)threadIdx.x * VEC; };
+    __shared__ ConvTile entries[CONV_STAGES];                 // the staged tiles' entries
     pdl_launch_dependents();
     const int gi = threadIdx.x, ti = threadIdx.y;
     const int c0 = blockIdx.x * CH;     // channel blocks are the grid's fast axis: blocks that run
                                          // together read neighbouring pieces of the same rows
     const int c = c0 + gi * VEC;
     const bool live = c < d;
-    // the taps do not depend on the kernel before this one
-    for (int i = ti * CONV_CG + gi; i < CH * W; i += CONV_TT * CONV_CG) {
-        const int ch = i / W, j = i % W;
-        taps_s[j][ch] = c0 + ch < d ? w[(size_t)(c0 + ch) * W + j] : 0.f;
+    // this thread's taps and bias (they do not depend on the kernel before this one)
+    float taps[W][VEC], bias_r[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        bias_r[i] = live && bias != nullptr ? bias[c + i] : 0.f;
+#pragma unroll
+        for (int j = 0; j < W; ++j) taps[j][i] = live ? w[(size_t)(c + i) * W + j] : 0.f;
     }
     pdl_wait();
-    // Trips to memory, one behind the other, are what a block's time is made of. A tile inside a
-    // portion (off >= W - 1) needs one for its entry of the tile lists and one for its rows; only
-    // a tile at the portion's start looks further: the sequence's length, cached count and slot.
-    const int off = tile_off[blockIdx.y];
-    const int n = tile_n[blockIdx.y];
-    const int s = tile_seq[blockIdx.y];
-    const int tok0 = tile_tok0 != nullptr ? tile_tok0[blockIdx.y] : -1;
-    if (n <= 0) return;          // an unused entry of a fixed-length tile list (captured steps)
-    const bool at_start = off < W - 1;
-    const int start = (tok0 >= 0 && !at_start) ? tok0 - off : cu[s];
-    int len = 0, ctx = 0;
-    T* st = state + c;
-    if (at_start) {
-        len = cu[s + 1] - start;
-        ctx = seq_ctx[s];
-        st += (size_t)TK_SLOT(TK_K_CONV, seq_slot[s]) * (W - 1) * d;
-    }
+    const int first = blockIdx.y * per_block;
+    const int count = min(per_block, n_tiles - first);
     const int cb = block ? (c / block) * 3 * block + c % block : c;
     const int cc = block ? cb + block : d + c, cx = block ? cb + 2 * block : 2 * d + c;
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    const bool writes_state = off == 0;
 
-    // an input at index li of the portion, as raw 16-byte pieces: (B, X) of that row, or the
-    // state row (in `b_raw`) before the portion, or zero before position 0
-    auto fetch = [&](int li, uint4& b_raw, uint4& x_raw) {
-        b_raw = x_raw = zero4;
-        if (li >= 0) {
-            const T* row = bcx + (size_t)(start + li) * stride;
-            b_raw = *reinterpret_cast<const uint4*>(row + cb);
-            x_raw = *reinterpret_cast<const uint4*>(row + cx);
-        } else if (ctx + li >= 0) {
-            b_raw = *reinterpret_cast<const uint4*>(st + (size_t)(W - 1 + li) * d);
+    auto read_entry = [&](int k) {
+        ConvTile t;
+        const int i = first + k;
+        t.off = tile_off[i];
+        t.n = tile_n[i];
+        const int s = tile_seq[i];
+        const int tok0 = tile_tok0 != nullptr ? tile_tok0[i] : -1;
+        t.len = t.ctx = t.slot = 0;
+        // a tile inside a portion needs nothing but its own entry; one at the portion's start
+        // looks further: the sequence's length, cached count and slot
+        if (t.n > 0 && t.off < HR) {
+            t.start = cu[s];
+            t.len = cu[s + 1] - t.start;
+            t.ctx = seq_ctx[s];
+            t.slot = TK_SLOT(TK_K_CONV, seq_slot[s]);
+        } else {
+            t.start = tok0 >= 0 ? tok0 - t.off : (t.n > 0 ? cu[s] : 0);
         }
+        return t;
     };
-    auto as_input = [&](int li, const uint4& b_raw, const uint4& x_raw, float (&u)[VEC]) {
-        const T* bv = reinterpret_cast<const T*>(&b_raw);
-        const T* xv = reinterpret_cast<const T*>(&x_raw);
+    // the copies of one tile: its own rows, and by the first HR token rows the rows before it
+    auto issue = [&](const ConvTile& t, int stage) {
+        T* sg = raw + stage * STAGE;
+        if (ti == 0 && gi == 0) entries[stage] = t;          // read back when the tile is computed
+        if (t.n > 0) {
+            const bool own = ti < t.n;
+            const T* row = bcx + (size_t)(t.start + t.off + (own ? ti : 0)) * stride;
+            const int li = t.off - HR + ti;               // of a row before the tile: its index in the portion
+            const T* prev = bcx + (size_t)(t.start + (li >= 0 ? li : 0)) * stride;
+            if constexpr (INTER) {
+                // 3 CONV_CG pieces of 16 bytes per row, CONV_CG lanes: three pieces each
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-            u[i] = li >= 0 ? round_as<T>(to_f<T>(bv[i]) * to_f<T>(xv[i])) : to_f<T>(bv[i]);
+                for (int q = 0; q < 3; ++q) {
+                    const int e = (gi + q * CONV_CG) * VEC;               // offset in the block's run
+                    const bool inside = 3 * c0 + e < 3 * d;
+                    conv_cp16(sg + (HR + ti) * 3 * CH + e, row + 3 * c0 + e, own && inside);
+                    if (ti < HR && li >= 0) conv_cp16(sg + ti * 3 * CH + e, prev + 3 * c0 + e, inside);
+                }
+            } else if (live) {
+                conv_cp16(sg + at_b(HR + ti), row + cb, own);
+                conv_cp16(sg + at_x(HR + ti), row + cx, own);
+                conv_cp16(sg + at_c(ti), row + cc, own);
+                if (ti < HR && li >= 0) {
+                    conv_cp16(sg + at_b(ti), prev + cb, true);
+                    conv_cp16(sg + at_x(ti), prev + cx, true);
+                }
+            }
+            if (live && ti < HR && li < 0) {
+                // the state row (an input as it was stored), or zero before position 0; its
+                // X is set to one when the copy has landed (`patch`)
+                const bool held = t.ctx + li >= 0;
+                const T* st_row = state + ((size_t)t.slot * HR + (held ? HR + li : 0)) * d + c;
+                conv_cp16(sg + at_b(ti), st_row, held);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    // a state row stands for B * X already: X = 1 makes the product the row itself (by the thread
+    // that copied the row, after its copies have landed and before the barrier)
+    auto patch = [&](const ConvTile& t, int stage) {
+        if (t.n > 0 && live && ti < HR && t.off - HR + ti < 0) {
+            T ones[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ones[i] = from_f<T>(1.0f);
+            *reinterpret_cast<uint4*>(raw + stage * STAGE + at_x(ti)) = *reinterpret_cast<const uint4*>(ones);
+        }
     };
 
-    uint4 rb = zero4, rx = zero4, rc = zero4, hb = zero4, hx = zero4, fb = zero4, fx = zero4;
-    const bool own = live && ti < n, halo = live && ti < W - 1;
-    if (own) {
-        const T* row = bcx + (size_t)(start + off + ti) * stride;
-        rb = *reinterpret_cast<const uint4*>(row + cb);
-        rx = *reinterpret_cast<const uint4*>(row + cx);
-        rc = *reinterpret_cast<const uint4*>(row + cc);
-    }
-    if (halo) {
-        fetch(off - (W - 1) + ti, hb, hx);
-        if (writes_state) fetch(len - (W - 1) + ti, fb, fx);
-    }
-    // shared memory is written and read four floats at a time
-    auto put = [&](float* dst, const float (&v)[VEC]) {
+    if (count <= 0) return;
+    // tiles 0 .. CONV_STAGES - 2 are asked for up front; every turn of the loop asks for one more
+    // (with the entry that the turn before read) and reads the entry of the one after that
 #pragma unroll
-        for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-    };
-    auto get = [&](const float* src, float (&v)[VEC]) {
-#pragma unroll
-        for (int i = 0; i < VEC; i += 4) {
-            const float4 f = *reinterpret_cast<const float4*>(src + i);
-            v[i] = f.x, v[i + 1] = f.y, v[i + 2] = f.z, v[i + 3] = f.w;
+    for (int k = 0; k < CONV_STAGES - 1; ++k) {
+        if (k < count) issue(read_entry(k), k);
+        else asm volatile("cp.async.commit_group;\n" ::);
+    }
+    ConvTile ahead = read_entry(min(CONV_STAGES - 1, count - 1));
+    __syncthreads();                // the first entries are in shared memory for everyone
+    for (int k = 0; k < count; ++k) {
+        const int stage = k % CONV_STAGES;
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(CONV_STAGES - 2));
+        {
+            // (the entry was stored at least one barrier ago)
+            const ConvTile mine = entries[stage];
+            patch(mine, stage);
         }
-    };
-    float u[VEC];
-    if (own) {
-        as_input(0, rb, rx, u);
-        put(&u_s[W - 1 + ti][gi * VEC], u);
-    }
-    if (halo) {
-        as_input(off - (W - 1) + ti, hb, hx, u);
-        put(&u_s[ti][gi * VEC], u);
-    }
-    __syncthreads();
-    if (own) {
-        float acc[VEC], in[VEC], tp[VEC];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < W; ++j) {
-            get(&u_s[ti + j][gi * VEC], in);
-            get(&taps_s[j][gi * VEC], tp);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] += in[i] * tp[i];
+        __syncthreads();            // tile k has landed for every thread; tile k - 1 is computed
+        const ConvTile t = entries[stage];
+        const int want = k + CONV_STAGES - 1;
+        if (want < count) issue(ahead, want % CONV_STAGES);      // into the stage tile k - 1 held
+        else asm volatile("cp.async.commit_group;\n" ::);
+        if (want + 1 < count) ahead = read_entry(want + 1);      // in flight while this tile is computed
+        if (t.n <= 0) continue;     // an unused entry of a fixed-length list (captured steps)
+        const T* sg = raw + stage * STAGE;
+        const bool own = live && ti < t.n, halo = live && ti < HR;
+        const bool writes_state = t.off == 0;
+        // the portion's last inputs, for the state: asked for now, used after the sums
+        uint4 fb = make_uint4(0u, 0u, 0u, 0u), fx = fb;
+        bool f_product = false;
+        T* st = state + (size_t)t.slot * HR * d + c;
+        if (halo && writes_state) {
+            const int li = t.len - HR + ti;
+            if (li >= 0) {
+                const T* row = bcx + (size_t)(t.start + li) * stride;
+                fb = *reinterpret_cast<const uint4*>(row + cb);
+                fx = *reinterpret_cast<const uint4*>(row + cx);
+                f_product = true;
+            } else if (t.ctx + li >= 0) {
+                fb = *reinterpret_cast<const uint4*>(st + (size_t)(HR + li) * d);
+            }
         }
-        const T* cv = reinterpret_cast<const T*>(&rc);
-        uint4 packed;
-        T* o = reinterpret_cast<T*>(&packed);
+        if (own) {
+            float acc[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            if (bias != nullptr) acc[i] += bias[c + i];
-            o[i] = from_f<T>(to_f<T>(cv[i]) * round_as<T>(acc[i]));
+            for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < W; ++j) {
+                const uint4 b_raw = *reinterpret_cast<const uint4*>(sg + at_b(ti + j));
+                const uint4 x_raw = *reinterpret_cast<const uint4*>(sg + at_x(ti + j));
+                if constexpr (sizeof(T) == 2) {
+                    // the product of two bfloat16 values is exact in 32-bit, so the packed
+                    // multiply's one rounding is round(B * X): a quarter of the instructions
+                    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b_raw);
+                    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
+#pragma unroll
+                    for (int i = 0; i < VEC / 2; ++i) {
+                        const float2 u = __bfloat1622float2(__hmul2(b2[i], x2[i]));
+                        acc[2 * i] += u.x * taps[j][2 * i];
+                        acc[2 * i + 1] += u.y * taps[j][2 * i + 1];
+                    }
+                } else {
+                    const T* bv = reinterpret_cast<const T*>(&b_raw);
+                    const T* xv = reinterpret_cast<const T*>(&x_raw);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] += round_as<T>(to_f<T>(bv[i]) * to_f<T>(xv[i])) * taps[j][i];
+                }
+            }
+            const uint4 rc = *reinterpret_cast<const uint4*>(sg + at_c(ti));
+            const T* cv = reinterpret_cast<const T*>(&rc);
+            uint4 packed;
+            T* o = reinterpret_cast<T*>(&packed);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                if (bias != nullptr) acc[i] += bias_r[i];
+                o[i] = from_f<T>(to_f<T>(cv[i]) * round_as<T>(acc[i]));
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)(t.start + t.off + ti) * d + c) = packed;
         }
-        *reinterpret_cast<uint4*>(out + (size_t)(start + off + ti) * d + c) = packed;
-    }
-    if (halo && writes_state) {
-        // the old rows were read before the barrier; the new ones are the portion's last inputs
-        as_input(len - (W - 1) + ti, fb, fx, u);
-        uint4 packed;
-        T* o = reinterpret_cast<T*>(&packed);
+        // The new state rows are the portion's last inputs; with a portion shorter than the
+        // state some of them are old rows moved up, which every thread has read (above) before
+        // any thread overwrites one (the barrier; `writes_state` is the same for the whole block).
+        if (writes_state) __syncthreads();
+        if (halo && writes_state) {
+            const T* bv = reinterpret_cast<const T*>(&fb);
+            const T* xv = reinterpret_cast<const T*>(&fx);
+            uint4 packed;
+            T* o = reinterpret_cast<T*>(&packed);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = from_f<T>(u[i]);
-        *reinterpret_cast<uint4*>(st + (size_t)ti * d) = packed;
+            for (int i = 0; i < VEC; ++i)
+                o[i] = f_product ? from_f<T>(round_as<T>(to_f<T>(bv[i]) * to_f<T>(xv[i]))) : bv[i];
+            *reinterpret_cast<uint4*>(st + (size_t)ti * d) = packed;
+        }
     }
 }
 
@@ -398,21 +492,40 @@ static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, c
     const bool tiled = vec_ok && tile_cap >= W - 1 && tile_cap >= 1 && tile_cap <= 16 && W <= CONV_MAX_W &&
                        n_tiles <= 65535;
     const int tt = tile_cap <= 4 ? 4 : (tile_cap <= 8 ? 8 : 16), cg = 256 / tt;
-    const dim3 tgrid((d + cg * VEC - 1) / (cg * VEC), n_tiles), tblock(cg, tt);
+    const int blocks_x = (d + cg * VEC - 1) / (cg * VEC);
+    // tiles a block takes one after the other: as many blocks as are resident at once, the rest in a row
+    const int resident = 148 * (W <= 4 ? 3 : 2);          // blocks the GPU holds at once (by registers)
+    int tiles_each = (int)(((long long)blocks_x * n_tiles + resident - 1) / resident);
+    tiles_each = tiles_each < 1 ? 1 : (tiles_each > 8 ? 8 : tiles_each);
+    const dim3 tgrid(blocks_x, (n_tiles + tiles_each - 1) / tiles_each), tblock(cg, tt);
+    const int ch = cg * VEC, hr = W - 1;
+    const bool inter = block == VEC;
+    const size_t tsmem = CONV_STAGES * (size_t)(inter ? 3 * (hr + tt) : 2 * (hr + tt) + tt) * ch * sizeof(T);
+#define TK_CONV_TILED_I(WW, TT_, CG_, INTER_)                                                    \
+    do {                                                                                         \
+        static size_t allowed = 48 * 1024;      /* (one process drives one GPU) */               \
+        if (tsmem > allowed) {                                                                   \
+            cudaFuncSetAttribute(conv_gated_tile_kernel<T, WW, TT_, CG_, INTER_>,                \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem);       \
+            allowed = tsmem;                                                                     \
+        }                                                                                        \
+        tk_launch(conv_gated_tile_kernel<T, WW, TT_, CG_, INTER_>, tgrid, tblock, tsmem, stream, \
+            (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,        \
+            tile_seq, tile_off, tile_n, tile_tok0, block, n_tiles, tiles_each);                  \
+    } while (0)
+#define TK_CONV_TILED(WW, TT_, CG_)                                                              \
+    do {                                                                                         \
+        if (inter) TK_CONV_TILED_I(WW, TT_, CG_, true);                                          \
+        else TK_CONV_TILED_I(WW, TT_, CG_, false);                                               \
+    } while (0)
 #define TK_CONV_CASE(WW)                                                                         \
     case WW:                                                                                     \
         if (tiled && tt == 16)                                                                   \
-            tk_launch(conv_gated_tile_kernel<T, WW, 16, 16>, tgrid, tblock, 0, stream,           \
-                (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
-                tile_seq, tile_off, tile_n, tile_tok0, block);                                   \
-        else if (tiled && tt == 8 && WW <= 9)                                                    \
-            tk_launch(conv_gated_tile_kernel<T, WW, 8, 32>, tgrid, tblock, 0, stream,            \
-                (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
-                tile_seq, tile_off, tile_n, tile_tok0, block);                                   \
+            TK_CONV_TILED(WW, 16, 16);                                                           \
+        else if (tiled && tt == 8)                                                               \
+            TK_CONV_TILED(WW, 8, 32);                                                            \
         else if (tiled && tt == 4 && WW <= 5)                                                    \
-            tk_launch(conv_gated_tile_kernel<T, WW, (WW <= 5 ? 4 : 8), (WW <= 5 ? 64 : 32)>, tgrid, tblock, 0, stream, \
-                (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
-                tile_seq, tile_off, tile_n, tile_tok0, block);                                   \
+            TK_CONV_TILED(WW, (WW <= 5 ? 4 : 8), (WW <= 5 ? 64 : 32));                           \
         else if (vec_ok)                                                                         \
             tk_launch(conv_gated_vec_kernel<T, WW>, dim3(grid), dim3(threads), 0, stream,        \
                 (const T*)bcx, stride, d, w, bias, (T*)state, (T*)out, cu, seq_ctx, seq_slot,    \
@@ -435,6 +548,8 @@ static int launch_conv(const void* bcx, int64_t stride, int d, const float* w, c
             return -1;
     }
 #undef TK_CONV_CASE
+#undef TK_CONV_TILED
+#undef TK_CONV_TILED_I
     TK_CHECK_LAUNCH("conv_gated");
     return 0;
 }
