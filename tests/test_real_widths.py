@@ -198,7 +198,7 @@ def test_every_route_at_real_widths_through_generate(real_folders, monkeypatch):
     assert ops.gemm_tc_status() == 0 and ops.attention_prefill_tc_status() == 0
     # up to 8 decoded tokens a block's norms and residual adds run inside its products
     # ("skinny+norm", "skinny+add"); 9 to 16 rows take the plain weight-streaming kernel
-    for key in ("skinny head", "tc head", "library head",                            # 1..4 rows, 5..64, more
+    for key in ("skinny head", "tc head", "library head",                            # 1..8 rows, 9..64, more
                 "skinny+add 2048x2048", "skinny 2048x2048", "library 2048x2048",     # out / o
                 "skinny+norm 3104x2048", "skinny 3104x2048", "library 3104x2048",    # q, k, v, gate
                 "skinny+add 2048x8192", "tc 2048x8192", "library 2048x8192",         # down

@@ -94,7 +94,8 @@ class Linear:
             return "library"             # no further checks: prompt portions come here
         skinny_ok = ops.gemm_skinny_ok(x[:1], self.weight)
         if skinny_ok and m <= t.skinny_tall_rows:
-            return "skinny"              # the head too: 0.67 ms a decode step at one row against 0.70
+            return "skinny"              # the head too (0.67 ms a decode step at one row against
+                                         # 0.70, 0.729 at 8 rows against 0.740 with the tcgen05 kernel)
         if n >= t.tc_tall_n and m <= t.tc_tall_rows and ops.gemm_tc_ok(x, self.weight):
             return "tc"
         if skinny_ok and (m <= t.skinny_rows or (m <= t.skinny_small_rows and n <= t.skinny_small_n

@@ -24,9 +24,9 @@ class Tuning:
     Dense products of 16-bit matrices, by rows of the input (``Linear.route``):
     ``skinny_rows``: up to here the register-streaming kernel, for any matrix;
     ``skinny_small_rows`` / ``skinny_small_n``: up to that many rows for matrices of at most that
-    many output rows; ``tc_tall_n`` / ``tc_tall_rows`` / ``tc_tall_from``: matrices at least that
-    tall (a vocabulary head) go to the TMA + tcgen05 kernel from ``tc_tall_from`` to
-    ``tc_tall_rows`` rows; ``tc_deep_k`` / ``tc_deep_rows``: matrices with an inner size of at
+    many output rows; ``skinny_tall_rows``: up to that many rows it also takes the tallest
+    matrices (a vocabulary head); ``tc_tall_n`` / ``tc_tall_rows``: above, matrices at least
+    ``tc_tall_n`` tall go to the TMA + tcgen05 kernel up to ``tc_tall_rows`` rows; ``tc_deep_k`` / ``tc_deep_rows``: matrices with an inner size of at
     least ``tc_deep_k`` (a feed-forward's down projection) go there above the skinny range up to
     ``tc_deep_rows`` rows; everything else is the library's.
     ``swiglu_fused_rows``: up to here gate/up and the activation are one kernel.
@@ -56,7 +56,7 @@ class Tuning:
     skinny_rows: int = 8
     skinny_small_rows: int = 16
     skinny_small_n: int = 4096
-    skinny_tall_rows: int = 4
+    skinny_tall_rows: int = 8
     tc_tall_n: int = 32768
     tc_tall_rows: int = 64
     tc_deep_k: int = 8192
