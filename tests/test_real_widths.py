@@ -40,7 +40,7 @@ BASE = {
     "conv_bias": False, "tie_embedding": True,
 }
 WIDTHS = {
-    # the cut of BASELINE configs[2], with the per-head output gate the benchmark folder has
+    # the cut of the 1.2B-size benchmark configuration, with the per-head output gate its folder has
     "1.2B": dict(BASE, hidden_size=2048, num_attention_heads=32, intermediate_size=8192, attention_gate=True),
     "350M": dict(BASE, hidden_size=1024, num_attention_heads=16, intermediate_size=4608),
     "2.6B": dict(BASE, hidden_size=2048, num_attention_heads=32, intermediate_size=10752),
