@@ -575,6 +575,30 @@ def run_sweep(model, cfg, page: int, pk: dict) -> int:
         r = device_prefill(model, cfg, page, reps=2, tokens=n)
         out["prefill"].append({"tokens": n, "ms": round(r["ms"], 3), "tok_s": round(r["tok_s"], 1),
                                "frac_bf16": round(r["flops"] / (r["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
+    # one long prompt cut into portions under a token budget, as the scheduler cuts it: late
+    # portions are few tiles behind a long context (wall clock of the whole call, one request)
+    from tokenomos_b200.engine.engine import Engine
+    from tokenomos_b200.engine.scheduler import Request
+
+    import torch
+
+    out["chunked_prefill"] = []
+    g = torch.Generator().manual_seed(1)
+    for prompt, budget in ((32000, 512), (32000, 128), (8000, 512)):
+        eng = Engine(model, slots=2, page=page, max_len=prompt + 64, prefill_budget=budget, graphs=True, warmup=True)
+        ids = torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist()
+        best = None
+        for _ in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.generate([Request(ids, max_new=2)])
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        out["chunked_prefill"].append({"prompt": prompt, "portion": budget, "ms": round(best * 1e3, 1),
+                                       "tok_s": round(prompt / best, 1)})
+        del eng
+        torch.cuda.empty_cache()
     print(json.dumps(out))
     return 0
 

@@ -627,11 +627,13 @@ def test_sample_is_batch_invariant_and_step_dependent():
 
 # ---- tensor-core attention (bfloat16, head sizes 64 and 128) -------------------------------------
 
-def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None, tc=False, gate=None):
+def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None, tc=False, gate=None,
+                       tc_split=1):
     """Like ``attention_case`` but through the tensor-core kernels: multi-token sequences go to
     the prefill kernel (``tc``: the tcgen05 one), single-token ones to the decode kernel (split
     ``nsplit`` ways). ``gate`` [T, H] (on the device): the kernels apply the per-head output gate
-    as they write (the reference returned stays ungated)."""
+    as they write (the reference returned stays ungated). ``tc_split``: CTAs that share a tile's
+    keys in the tcgen05 prefill kernel."""
     from tokenomos_b200 import ops
     dtype = torch.bfloat16
     assert ops.attention_mma_supported(H, Hkv, D, dtype)
@@ -674,7 +676,7 @@ def attention_mma_case(H, Hkv, D, P, seqs, window=None, boost=None, nsplit=None,
     if tok0:
         prefill = ops.attention_prefill_tc if tc else ops.attention_prefill_mma
         prefill(q_dev, pool_dev, out, i32(positions), i32(tok_seq), dev(table), i32(tok0), i32(ntok),
-                window, D ** -0.5, gate)
+                window, D ** -0.5, gate, **({"nsplit": tc_split} if tc else {}))
         if tc:
             assert ops.attention_prefill_tc_status() == 0
     if singles:
@@ -857,6 +859,24 @@ def test_attention_tc_prefill(H, Hkv, P):
     seqs = [(17, 3), (0, 40), (40, 100), (5, 2), (64, 64), (0, 130), (300, 257), (1, 63), (0, 2)]
     got, want = attention_mma_case(H, Hkv, 64, P, seqs, tc=True)
     close(got, want, torch.bfloat16, f"tc attention H{H} Hkv{Hkv} P{P}")
+
+
+@pytest.mark.parametrize("H, Hkv, P", [(32, 8, 16), (6, 3, 7), (4, 4, 32)])
+@pytest.mark.parametrize("split, window", [(2, None), (3, None), (8, None), (4, 70), (5, 1)])
+def test_attention_tc_prefill_with_a_tiles_keys_shared_by_several_ctas(H, Hkv, P, split, window):
+    """Portions behind long and short contexts with each tile's keys split over CTAs: sequences with
+    fewer key tiles than splits (some CTAs have nothing), a window, a gate; twice in a row (the
+    tickets of the first launch leave the second alone)."""
+    from tokenomos_b200 import ops
+    seqs = [(0, 40), (1900, 130), (17, 3), (333, 64), (0, 2), (700, 33), (64, 64), (5000, 70), (2600, 40)]
+    T = sum(n for _, n in seqs)
+    gate = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        got, want = attention_mma_case(H, Hkv, 64, P, seqs, window=window, tc=True, gate=gate, tc_split=split)
+        close(got, want * torch.sigmoid(gate.double().cpu())[:, :, None], torch.bfloat16,
+              f"tcgen05 prefill H{H} Hkv{Hkv} P{P} split {split} window {window}")
+        assert ops.attention_prefill_tc_status() == 0
+        assert int(ops._tickets[got.device].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("window", [1, 5, 64, 100])

@@ -134,6 +134,35 @@ def test_long_decoding_and_first_tokens(dtype, model_folders):
     compare(trace_util.collect(steps, per_step), want, tol(name, dtype), f"long decoding {dtype}")
 
 
+def test_portions_behind_a_long_context_share_their_keys(model_folders, monkeypatch):
+    """A 2,300-token request in portions of 64 and 40 tokens (head size 64, so the tcgen05 prefill
+    kernel; bfloat16): late portions are one or two tiles behind thousands of keys, and several
+    CTAs share each tile's keys. The logits are the plain implementation's, and the kernel was
+    indeed asked to share."""
+    from tokenomos_b200 import ops
+    name, dtype = "D", "bfloat16"
+    folder = model_folders[name][torch.bfloat16]
+    vocab = TINY[name]["config"]["vocab_size"]
+    g = torch.Generator().manual_seed(5)
+    reqs = {"long": torch.randint(0, vocab, (2300,), generator=g).tolist()}
+    config, w = plain_lfm3.read_folder(folder)
+    want = {rid: plain_lfm3.forward_logits(config, w, ids) for rid, ids in reqs.items()}
+    asked = []
+    real = ops.attention_prefill_tc
+
+    def counted(*a, **k):
+        asked.append(a[11] if len(a) > 11 else k.get("nsplit", 1))
+        return real(*a, **k)
+
+    monkeypatch.setattr(ops, "attention_prefill_tc", counted)
+    steps = trace_util.portions(reqs, sizes=(64, 40))
+    page = TINY[name]["page"]
+    per_step = trace_util.run_in_process(folder, dtype, steps, trace_util.max_live_tokens(steps, page), page)
+    compare(trace_util.collect(steps, per_step), want, tol(name, dtype), "portions behind a long context")
+    assert asked and max(asked) > 1, asked[:5]
+    assert ops.attention_prefill_tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(dtype, model_folders, tmp_path):
     """The program itself, as a user runs it: stdin, ``done`` lines, logits files."""

@@ -327,3 +327,21 @@ def test_one_kernel_decode_attention_split_rule():
                 assert n == 1 or n * rows * kv <= t.decode_fused_ctas_per_sm * t.sm_count
     half = Tuning(sm_count=74)
     assert f(8, 8, 4096, half) == 2
+
+
+def test_prefill_attention_split_rule():
+    """How many CTAs may share one tile's keys in the tcgen05 prefill kernel: as many as fill the
+    GPU once, within the scratch memory's budget, 16 at most, one when the step has many tiles."""
+    from tokenomos_b200.parts.attention import Attention
+    from tokenomos_b200.parts.registry import Tuning
+    f = Attention.prefill_splits
+    assert f(2048, 64, 32, 8) == 1 and f(8192, 256, 32, 8) == 1          # a step that fills the GPU by itself
+    assert f(512, 16, 32, 8) == 2 and f(128, 4, 32, 8) == 9 and f(32, 1, 32, 8) == 16
+    assert f(128, 69, 32, 8) == 3                                          # a captured step's long list: the memory budget
+    assert f(128, 4, 32, 8, Tuning(prefill_split_ctas_per_sm=0)) == 1      # switched off
+    for tokens in (1, 2, 31, 32, 33, 500, 5000):
+        for entries in (1, 5, 70, 300):
+            for kv in (1, 2, 8):
+                n = f(tokens, entries, 32, kv)
+                assert 1 <= n <= 16
+                assert n == 1 or entries * kv * n * 128 * 66 * 4 <= 64 << 20

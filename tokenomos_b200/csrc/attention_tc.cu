@@ -43,6 +43,7 @@ constexpr int AT_STAGES = 3;              // key / value tiles in flight
 constexpr int AT_KV_BYTES = AT_KEYS * AT_D * 2;
 constexpr int AT_Q_BYTES = AT_ROWS * AT_D * 2;
 constexpr int AT_P_BYTES = AT_ROWS * AT_KEYS * 2;
+constexpr int AT_SPLIT_TILES = 8;         // key tiles a CTA should have before a tile's keys are shared out
 constexpr float AT_LAZY = 8.0f;           // log2 of how far a probability may exceed 1 before a rescale
 constexpr long long AT_WAIT_CYCLES = 2000000000LL;
 
@@ -96,8 +97,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_bfloat16* out,
                        const int* positions, const int* tok_seq, const int* block_table, int bt_stride,
                        const int* tile_tok0, const int* tile_ntok, int H, int Hkv, int P, int window,
-                       float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
+                       float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg, int max_split,
+                       float* part_o, float* part_ml, int* tickets) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ int s_last;
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -130,7 +133,15 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
     const int pos_last = pos_first + ntok - 1;       // consecutive positions within a tile
     const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int j_begin = (lo / AT_KEYS) * AT_KEYS;
-    const int n_tiles = (pos_last - j_begin) / AT_KEYS + 1;
+    // Up to `max_split` CTAs (blockIdx.y) share a tile's keys, as many as leave each at least
+    // AT_SPLIT_TILES key tiles: CTA `split` takes key tiles split, split + nsplit, ...; the ones
+    // beyond that number have nothing to do. (The launch fixes the most; the tile decides.)
+    const int split = blockIdx.y;
+    const int all_tiles = (pos_last - j_begin) / AT_KEYS + 1;
+    const int nsplit = min(max_split, max(1, all_tiles / AT_SPLIT_TILES));
+    if (split >= nsplit) return;
+    const int n_tiles = (all_tiles - split + nsplit - 1) / nsplit;       // at least one
+    auto tile_j0 = [&](int it) { return j_begin + (split + it * nsplit) * AT_KEYS; };
 
     if (tid == 0) {
         for (int i = 0; i < AT_STAGES; ++i) {
@@ -182,19 +193,19 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         auto issue = [&](int it) {
             const int s = it % AT_STAGES;
             if (it >= AT_STAGES && ok) ok = at_wait(kv_empty(s), (uint32_t)((it / AT_STAGES - 1) & 1), 1);
-            const int j0 = j_begin + it * AT_KEYS;
+            const int j0 = tile_j0(it);
             const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage;
             if (p_shift >= 0) {
                 loader.issue_looked_up(kt, vs, pool, j0, lo, pos_last);
-                if (it + 1 < n_tiles) loader.lookup(bt_row, j0 + AT_KEYS, lo, pos_last);
+                if (it + 1 < n_tiles) loader.lookup(bt_row, tile_j0(it + 1), lo, pos_last);
             } else {
                 load_tile<AT_D>(kt, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
                 load_tile<AT_D>(vs, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
             }
             cp_async_commit();
         };
-        if (p_shift >= 0) loader.lookup(bt_row, j_begin, lo, pos_last);
-        issue(0);
+        if (p_shift >= 0 && n_tiles > 0) loader.lookup(bt_row, tile_j0(0), lo, pos_last);
+        if (n_tiles > 0) issue(0);
         // (after a failed wait the loop still runs to its end, without waiting: every thread must
         // meet every named barrier)
         for (int it = 0; it < n_tiles; ++it) {
@@ -235,7 +246,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                     umma_bf16(tmem + (uint32_t)b * AT_KEYS, qdesc + 2 * k, kdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
                 umma_commit(s_full(b));
             };
-            issue_s(0);
+            if (n_tiles > 0) issue_s(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) issue_s(j + 1);
                 if (!ok) break;
@@ -271,7 +282,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         float2 l_run = make_float2(0.f, 0.f), l_alt = make_float2(0.f, 0.f);   // the row sum in four lanes
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1, j0 = j_begin + j * AT_KEYS;
+            const int b = j & 1, j0 = tile_j0(j);
             // (after a failed wait the loop still runs to its end, without waiting: every thread
             // must meet every named barrier)
             if (ok) ok = at_wait(s_full(b), (uint32_t)((j >> 1) & 1), 6);
@@ -371,14 +382,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             asm volatile("bar.sync 3, 128;" ::: "memory");
             if (r == 0) mbar_arrive(p_full);
         }
-        if (ok) {
+        if (ok && n_tiles > 0) {
             ok = at_wait(pv_full, (uint32_t)((n_tiles - 1) & 1), 8);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float l_row = (l_run.x + l_run.y) + (l_alt.x + l_alt.y);
-            const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
             __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
             // the per-head output gate, if the layer has one: round(round(o) * round(sigmoid(g)))
             float gs = 1.0f;
@@ -386,22 +396,78 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                 const float gv = __bfloat162float(gate[(size_t)(tok0 + r / G) * ldg + kvh * G + r % G]);
                 gs = round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-gv)));
             }
+            // 16 finished values of the row: normalised, rounded, gated, stored
+            auto store16 = [&](int c, const float (&part)[16], float inv) {
+                if (dst == nullptr) return;
+                uint32_t packed[8];
 #pragma unroll
-            for (int c = 0; c < AT_D; c += 16) {
-                float part[16];
-                tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
-                if (dst != nullptr) {
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int e = 0; e < 16; e += 2) {
-                        packed[e >> 1] = pack_bf16_pair(part[e] * inv, part[e + 1] * inv);
-                        if (gate != nullptr) {
-                            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&packed[e >> 1]));
-                            packed[e >> 1] = pack_bf16_pair(f.x * gs, f.y * gs);
-                        }
+                for (int e = 0; e < 16; e += 2) {
+                    packed[e >> 1] = pack_bf16_pair(part[e] * inv, part[e + 1] * inv);
+                    if (gate != nullptr) {
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&packed[e >> 1]));
+                        packed[e >> 1] = pack_bf16_pair(f.x * gs, f.y * gs);
                     }
-                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+                *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            };
+            if (nsplit == 1) {
+                const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+#pragma unroll
+                for (int c = 0; c < AT_D; c += 16) {
+                    float part[16];
+                    tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+                    store16(c, part, inv);
+                }
+            } else {
+                // This CTA's share of the keys: the unnormalised row, its reference maximum and its
+                // sum go to scratch memory ([column][row], so that the 128 rows' accesses are
+                // contiguous); the CTA of this (tile, KV head) that draws the last ticket merges.
+                const size_t group = (size_t)tile * Hkv + kvh;
+                const size_t slot = group * max_split + split;
+                float* po = part_o + slot * (size_t)(AT_ROWS * AT_D);
+                if (n_tiles > 0) {
+#pragma unroll
+                    for (int c = 0; c < AT_D; c += 16) {
+                        float part[16];
+                        tmem_ld16(tmem_pv + lane_base + (uint32_t)c, part);
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) po[(size_t)(c + e) * AT_ROWS + r] = part[e];
+                    }
+                }
+                part_ml[(slot * AT_ROWS + r) * 2] = n_tiles > 0 ? m_ref : -INFINITY;
+                part_ml[(slot * AT_ROWS + r) * 2 + 1] = l_row;
+                __threadfence();
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                if (r == 0) s_last = atomicAdd(&tickets[group], 1) == nsplit - 1;
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                if (s_last) {
+                    __threadfence();
+                    const float* ml = part_ml + group * max_split * (size_t)(AT_ROWS * 2);
+                    float M = -INFINITY;
+                    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(&ml[((size_t)sp * AT_ROWS + r) * 2]));
+                    float L = 0.f;
+                    float acc[AT_D];
+#pragma unroll
+                    for (int c = 0; c < AT_D; ++c) acc[c] = 0.f;
+                    for (int sp = 0; sp < nsplit; ++sp) {
+                        const float ms = __ldcg(&ml[((size_t)sp * AT_ROWS + r) * 2]);
+                        if (ms == -INFINITY) continue;         // nothing visible in that share: its row was not written
+                        const float f = fast_exp2(ms - M);
+                        L += __ldcg(&ml[((size_t)sp * AT_ROWS + r) * 2 + 1]) * f;
+                        const float* src = part_o + (group * max_split + sp) * (size_t)(AT_ROWS * AT_D) + r;
+#pragma unroll
+                        for (int c = 0; c < AT_D; ++c) acc[c] = fmaf(__ldcg(src + (size_t)c * AT_ROWS), f, acc[c]);
+                    }
+                    const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+                    for (int c = 0; c < AT_D; c += 16) {
+                        float part[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) part[e] = acc[c + e];
+                        store16(c, part, inv);
+                    }
+                    if (r == 0) tickets[group] = 0;
                 }
             }
         }
@@ -427,6 +493,12 @@ TK_API int tk_attn_prefill_tc_supported(int H, int Hkv, int D) {
 // Tokens of one sequence that a tile of this kernel holds (what the caller cuts portions into).
 TK_API int tk_attn_prefill_tc_tokens(int H, int Hkv) { return AT_ROWS / (H / Hkv); }
 
+// Floats of scratch for n_tiles tiles split nsplit ways (nothing unsplit): the unnormalised rows
+// [n_tiles, Hkv, nsplit, 64, 128], then each row's reference maximum and sum [.., 128, 2].
+TK_API int64_t tk_attn_prefill_tc_scratch(int n_tiles, int Hkv, int nsplit) {
+    return nsplit <= 1 ? 0 : (int64_t)n_tiles * Hkv * nsplit * (AT_ROWS * AT_D + AT_ROWS * 2);
+}
+
 // 0, or where a CTA gave up waiting on a barrier since the last call (1 staging, 2-4 MMA issuer,
 // 6-8 softmax). Resets the word.
 TK_API int tk_attn_prefill_tc_status() {
@@ -439,16 +511,23 @@ TK_API int tk_attn_prefill_tc_status() {
 // q: [T, H, 64] bfloat16; kv_pool: [pages, 2, Hkv, P, 64]; out: [T, H, 64]; tiles of at most
 // tk_attn_prefill_tc_tokens tokens of one sequence with consecutive positions; window 0 = none.
 // gate: [T, >= H] bfloat16 with rows ldg apart, the per-head output gate applied to what is
-// written (null: none).
+// written (null: none). nsplit > 1: up to that many CTAs share a tile's keys (alternate key tiles;
+// each tile takes as many as leave a CTA 8 key tiles), for steps with few tiles and long
+// contexts, where one CTA per tile would walk its keys alone on an idle GPU; `scratch`: tk_attn_prefill_tc_scratch floats, `tickets`: n_tiles * Hkv ints that are
+// zero and are zero again afterwards (the last CTA of a tile to finish merges the shares).
 TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, const int* positions,
                               const int* tok_seq, const int* block_table, int bt_stride,
                               const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
-                              int P, int window, float scale, const void* gate, int64_t ldg,
-                              cudaStream_t stream) {
+                              int P, int window, float scale, const void* gate, int64_t ldg, int nsplit,
+                              float* scratch, int* tickets, cudaStream_t stream) {
     TK_CHECK_ARG(tk_attn_prefill_tc_supported(H, Hkv, D), "attn_prefill_tc: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64, a group that divides 128)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_tc: bad page size or tile count");
+    TK_CHECK_ARG(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (scratch != nullptr && tickets != nullptr)),
+                 "attn_prefill_tc: %d splits (1..64; more than one needs scratch memory and tickets)", nsplit);
     if (n_tiles == 0) return 0;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_tiles * Hkv * nsplit * (AT_ROWS * AT_D) : nullptr;
     int shift = -1;
     if ((P & (P - 1)) == 0) {
         shift = 0;
@@ -457,10 +536,10 @@ TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, con
     const size_t smem = 1024 + AT_Q_BYTES + (2 * AT_STAGES + 1) * AT_KV_BYTES + 2 * AT_P_BYTES + (2 * AT_STAGES + 8) * 8 + 64;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-        e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv), dim3(AT_THREADS), smem, stream,
+        e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv, nsplit), dim3(AT_THREADS), smem, stream,
                       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions, tok_seq,
                       block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, shift,
-                      (const __nv_bfloat16*)gate, ldg);
+                      (const __nv_bfloat16*)gate, ldg, nsplit, part_o, part_ml, tickets);
     if (e != cudaSuccess) {
         tk_set_error("attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         cudaGetLastError();

@@ -331,18 +331,26 @@ def attention_prefill_tc_tokens(heads: int, kv_heads: int) -> int:
 def attention_prefill_tc(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                          positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                          tile_tok0: torch.Tensor, tile_ntok: torch.Tensor, window: int | None,
-                         scale: float, gate: torch.Tensor | None = None) -> None:
+                         scale: float, gate: torch.Tensor | None = None, nsplit: int = 1) -> None:
     """``attention_prefill_mma`` on tcgen05.mma with the accumulators in tensor memory, for tiles
     of ``attention_prefill_tc_tokens`` tokens of one sequence; writes the tiles' rows of ``out``
-    (gated like ``attention_prefill_mma``'s)."""
+    (gated like ``attention_prefill_mma``'s). ``nsplit`` > 1: that many CTAs share each tile's
+    keys and the last one to finish merges their shares (through scratch memory that this
+    function allocates): for steps with few tiles behind long contexts."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_tc")
     g_ptr, ldg = _gate_view(gate, T, H, "attention_prefill_tc")
+    n_tiles = tile_tok0.numel()
+    nsplit = max(1, int(nsplit))
+    scratch = tickets = None
+    if nsplit > 1 and n_tiles:
+        scratch = torch.empty(n_tiles * Hkv * nsplit * (128 * D + 256), dtype=torch.float32, device=q.device)
+        tickets = _decode_tickets(n_tiles * Hkv, q.device)
     _lib.call("tk_attn_prefill_tc", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
-              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
-              float(scale), g_ptr, ldg, _stream())
+              _ptr(_i32(tile_ntok, "tile_ntok")), n_tiles, H, Hkv, D, P, int(window or 0),
+              float(scale), g_ptr, ldg, nsplit, _ptr(scratch), _ptr(tickets), _stream())
 
 
 def attention_prefill_tc_status() -> int:

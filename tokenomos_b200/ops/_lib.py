@@ -42,7 +42,7 @@ _SIGNATURES = {
     "tk_attn_prefill_tc_supported": [I, I, I],
     "tk_attn_prefill_tc_tokens": [I, I],
     "tk_attn_prefill_tc_status": [],
-    "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, P],
+    "tk_attn_prefill_tc": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, I, P, P, P],
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P, L, P],
     "tk_attn_decode_fused_supported": [I, I, I, I],
     "tk_attn_decode_fused_max_splits": [I, I, I],

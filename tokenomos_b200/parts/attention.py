@@ -184,6 +184,22 @@ class Attention:
         resident = tuning.decode_fused_ctas_per_sm * tuning.sm_count // per_split
         return max(1, min(resident, -(-longest // tuning.decode_min_keys)))
 
+    @staticmethod
+    def prefill_splits(tokens: int, entries: int, per_tile: int, kv_heads: int,
+                       tuning: Tuning = DEFAULT_TUNING) -> int:
+        """The most CTAs that may share one tile's keys in the tcgen05 prefill kernel, for a step
+        of ``tokens`` tokens whose tile list has ``entries`` entries (a captured step's list is
+        longer than what it uses). A tile is walked by one CTA, key tile after key tile; a step
+        with few tiles behind a long context would leave the GPU idle for hundreds of
+        microseconds (128 tokens behind 32,000 positions: 474 us a layer, 98 us shared 8 ways).
+        So: as many as fill the GPU once (``prefill_split_ctas_per_sm`` CTAs an SM), no more than
+        the scratch memory for the shares allows; the kernel gives each tile as many of them as
+        leave a CTA 8 key tiles, so a short context uses one whatever this says."""
+        tiles = max(1, -(-tokens // per_tile))
+        by_ctas = tuning.prefill_split_ctas_per_sm * tuning.sm_count // (tiles * max(1, kv_heads))
+        by_memory = (tuning.prefill_split_scratch_mb << 20) // (max(1, entries) * max(1, kv_heads) * 128 * 66 * 4)
+        return max(1, min(16, by_ctas, by_memory))
+
     def _attend_mma(self, q, pool, table, ctx: StepContext, gate=None) -> torch.Tensor:
         """The tensor-core kernels: prompt portions in tiles of 64 rows, decoded tokens split
         over their keys so that a small batch still fills the GPU."""
@@ -195,9 +211,13 @@ class Attention:
         per_tile = (ops.attention_prefill_tc_tokens if tc else ops.attention_prefill_mma_tokens)(
             self.heads, self.kv_heads)
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
-        if tok0.numel():
-            (ops.attention_prefill_tc if tc else ops.attention_prefill_mma)(
-                q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window, self.scale, gate)
+        if tok0.numel() and tc:
+            nsplit = self.prefill_splits(ctx.n_tokens, tok0.numel(), per_tile, self.kv_heads, self.tuning)
+            ops.attention_prefill_tc(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window,
+                                     self.scale, gate, nsplit)
+        elif tok0.numel():
+            ops.attention_prefill_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window,
+                                      self.scale, gate)
         # every sequence brings one token: row i is sequence i's, no list of rows needed
         decode_only = ctx.host.decode_only
         singles = None if decode_only else ctx.singles()

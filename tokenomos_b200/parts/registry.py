@@ -45,6 +45,8 @@ class Tuning:
     so a kernel that asks for another split than its neighbours cannot start under them, and the
     L1 it leaves is what their activation loads find; -1 leaves the choice to the driver, which
     it always is above ``skinny_rows`` rows.
+    ``prefill_split_ctas_per_sm`` / ``prefill_split_scratch_mb``: how far a prompt portion's
+    tiles may share their keys out over CTAs (``Attention.prefill_splits``).
     ``conv_tile``: tokens of a conv tile; up to 16 the tiled kernel takes them (one thread per
     token and 8 channels, a 2,048-token portion of 2,048 channels at memory speed).
     ``fuse_norms``: 16-bit models fold each pre-norm's weight into the columns of the projection
@@ -69,6 +71,8 @@ class Tuning:
     decode_fused_rows: int = 8
     decode_fused_ctas_per_sm: int = 2
     decode_fused_carveout: int = 62
+    prefill_split_ctas_per_sm: int = 2
+    prefill_split_scratch_mb: int = 64
     conv_tile: int = 16
     fuse_norms: bool = True
 
