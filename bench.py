@@ -394,14 +394,51 @@ def kernel_case(name: str) -> None:
     """One kernel alone for a profiler, over operands that rotate through more than the L2 holds:
     ``gemm_tc64``: the tcgen05 product of 64 rows with a [6144, 2048] matrix, 16 launches;
     ``conv_tile``: the tiled gated short conv over a 2,048-token portion of 2,048 channels (width 3,
-    tiles of 16 tokens), 20 launches in a CUDA graph that is replayed five times."""
+    tiles of 16 tokens), 20 launches in a CUDA graph that is replayed five times;
+    ``attn_portions`` (a measurement, not a profiler case): the tcgen05 prefill attention on
+    portions behind cached contexts, with a tile's keys shared by 1 to 16 CTAs."""
     import torch
 
     from tokenomos_b200 import ops
 
     ops.available()
     dev, bf16 = "cuda", torch.bfloat16
-    if name == "gemm_tc64":
+    if name == "attn_portions":
+        # the tcgen05 prefill attention on a portion of T tokens behind C cached positions (32
+        # heads of 64 over 8 KV heads, one sequence), with up to `split` CTAs sharing a tile's
+        # keys: CUDA events around 10 launches, after 3
+        H, Hkv, D, P = 32, 8, 64, 16
+        per = ops.attention_prefill_tc_tokens(H, Hkv)
+        for T, C in ((512, 0), (512, 3584), (512, 32256), (128, 4096), (128, 32640), (32, 32640), (2048, 0), (2048, 30720)):
+            q = torch.randn(T, H, D, device=dev, dtype=bf16)
+            pages = (C + T) // P + 2
+            pool = torch.randn(pages, 2, Hkv, P, D, device=dev, dtype=bf16)
+            out = torch.empty_like(q)
+            pos = torch.arange(C, C + T, dtype=torch.int32, device=dev)
+            seq = torch.zeros(T, dtype=torch.int32, device=dev)
+            table = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+            t0 = torch.arange(0, T, per, dtype=torch.int32, device=dev)
+            nt = torch.full((t0.numel(),), per, dtype=torch.int32, device=dev)
+            flops = 4.0 * H * D * sum(C + i + 1 for i in range(T))
+            line = f"portion {T:5d} behind {C:6d} ({t0.numel() * Hkv:4d} CTAs unsplit):"
+            for split in (1, 2, 4, 8, 16):
+                if split > 1 and t0.numel() * Hkv * split > 4 * 296:
+                    continue
+                for _ in range(3):
+                    ops.attention_prefill_tc(q, pool, out, pos, seq, table, t0, nt, None, D ** -0.5, None, split)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(10):
+                    ops.attention_prefill_tc(q, pool, out, pos, seq, table, t0, nt, None, D ** -0.5, None, split)
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) / 10 * 1e3
+                line += f"  x{split}: {us:7.1f} us ({flops / us / 1e6:5.0f} TFLOP/s)"
+            print(line, flush=True)
+        if ops.attention_prefill_tc_status():
+            raise RuntimeError("the tcgen05 attention reported an error")
+    elif name == "gemm_tc64":
         ws = [torch.randn(6144, 2048, device=dev, dtype=bf16) * 0.02 for _ in range(8)]
         x = torch.randn(64, 2048, device=dev, dtype=bf16)
         for i in range(16):
@@ -851,7 +888,7 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill", "ingraph"],
                     help="run only a small case for a profiler (see profile_case) and exit; ingraph: "
                          "the cost of each kind of kernel inside the captured decode step (ingraph_table)")
-    ap.add_argument("--kernel", default=None, choices=["gemm_tc64", "conv_tile"],
+    ap.add_argument("--kernel", default=None, choices=["gemm_tc64", "conv_tile", "attn_portions"],
                     help="run only one kernel over rotating operands for a profiler (see kernel_case) and exit")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
     ap.add_argument("--gpus", type=int, default=1)
