@@ -10,6 +10,9 @@
 //     of a CTA take alternate 32-key tiles of the CTA's key range, and `nsplit` CTAs split one
 //     sequence's keys so that small batches still fill the GPU. Partial results (row maximum,
 //     row sum, unnormalised output) go to scratch memory and a second kernel merges them.
+//   fused decode kernel (steps of a few single tokens): the same walk with the q/k norm, the
+//     rotation, the cache write, the merge (by the last CTA to finish) and the head gate in it.
+// The kernels apply the per-head output gate as they write, when the layer has one.
 // Masking, scale, rounding of P to bfloat16 and the unrounded row sum follow the generic kernel
 // (Tokenomos kernels/attention/paged.py:67-76,150,267; models/blocks/attention.py:31-40,173).
 // Keys past a query's position are never read: their shared-memory rows are zero-filled.
