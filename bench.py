@@ -593,6 +593,31 @@ def ingraph_table(layers: int, batch: int, ctx: int, page: int) -> None:
     print(f"  the kinds sum to {sum(r[0] for r in rows):.1f} us of the step's {whole:.1f}")
 
 
+def chunked_prefill(model, cfg, page: int, prompt: int, budget: int) -> dict:
+    """One long prompt through the engine in portions of ``budget`` tokens, as the scheduler cuts
+    it (late portions are few tiles behind a long context): wall clock of the whole call, one
+    request, the better of two calls after the engine has warmed up."""
+    import torch
+
+    from tokenomos_b200.engine.engine import Engine
+    from tokenomos_b200.engine.scheduler import Request
+
+    eng = Engine(model, slots=2, page=page, max_len=prompt + 64, prefill_budget=budget, graphs=True, warmup=True)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist()
+    best = None
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.generate([Request(ids, max_new=2)])
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    del eng
+    torch.cuda.empty_cache()
+    return {"prompt": prompt, "portion": budget, "ms": round(best * 1e3, 1), "tok_s": round(prompt / best, 1)}
+
+
 def run_sweep(model, cfg, page: int, pk: dict) -> int:
     """Decode at other batch sizes and context lengths, prefill at other lengths: one JSON line
     of points, each with its fraction of the roofline (decode: bytes the step must read over the
@@ -612,30 +637,8 @@ def run_sweep(model, cfg, page: int, pk: dict) -> int:
         r = device_prefill(model, cfg, page, reps=2, tokens=n)
         out["prefill"].append({"tokens": n, "ms": round(r["ms"], 3), "tok_s": round(r["tok_s"], 1),
                                "frac_bf16": round(r["flops"] / (r["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
-    # one long prompt cut into portions under a token budget, as the scheduler cuts it: late
-    # portions are few tiles behind a long context (wall clock of the whole call, one request)
-    from tokenomos_b200.engine.engine import Engine
-    from tokenomos_b200.engine.scheduler import Request
-
-    import torch
-
-    out["chunked_prefill"] = []
-    g = torch.Generator().manual_seed(1)
-    for prompt, budget in ((32000, 512), (32000, 128), (8000, 512)):
-        eng = Engine(model, slots=2, page=page, max_len=prompt + 64, prefill_budget=budget, graphs=True, warmup=True)
-        ids = torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist()
-        best = None
-        for _ in range(2):
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            eng.generate([Request(ids, max_new=2)])
-            torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            best = dt if best is None else min(best, dt)
-        out["chunked_prefill"].append({"prompt": prompt, "portion": budget, "ms": round(best * 1e3, 1),
-                                       "tok_s": round(prompt / best, 1)})
-        del eng
-        torch.cuda.empty_cache()
+    out["chunked_prefill"] = [chunked_prefill(model, cfg, page, prompt, budget)
+                              for prompt, budget in ((32000, 512), (32000, 128), (8000, 512))]
     print(json.dumps(out))
     return 0
 
@@ -957,6 +960,12 @@ def main() -> int:
         for b in (1, args.batch, 64):
             points[f"decode_b{b}_far"] = round(device_decode(
                 model, cfg, b, min(args.steps, 64), warmup, args.page, prompt=PROMPT_FAR)["tok_s"], 1)
+        # a 32,000-token prompt served in portions of 512 tokens (tokens a second over the call)
+        try:
+            points["prefill_32k_by_512"] = chunked_prefill(model, cfg, args.page, 32000, 512)["tok_s"]
+        except Exception as exc:  # the line above it must not be lost to this point
+            print(f"bench.py: the chunked prefill point failed: {exc}", file=sys.stderr)
+            points["prefill_32k_by_512"] = None
     e2e = e2e_decode(llm, cfg, args.batch, args.steps, warmup)
     clock_report = clocks.stop()
     llm.close()
