@@ -131,6 +131,39 @@ def test_replay_at_real_widths(name, dtype, real_folders):
             assert diff <= same * ref.abs().max().item(), (name, dtype, mode, rid, diff)
 
 
+def test_portions_behind_a_long_context_at_real_widths(real_folders):
+    """The 1.2B-width cut on a 2,500-token request: whole in one step (512 attention CTAs, none
+    shares its keys) against portions of 96 and 32 tokens (three tiles or one, whose keys up to
+    16 CTAs share), last logits of every portion, in bfloat16; and the portions in 32-bit against
+    the same in bfloat16 within the bound the two paths have against the oracle."""
+    from tokenomos_b200 import ops
+
+    folder = real_folders["1.2B"]
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, WIDTHS["1.2B"]["vocab_size"], (2500,), generator=g).tolist()
+    cuts, a = [], 0
+    while a < len(ids):
+        b = min(len(ids), a + (96 if len(cuts) % 2 == 0 else 32))
+        cuts.append((a, b))
+        a = b
+    portions = [{"step": i, "entries": [{"id": "r", "tokens": ids[a:b], "want": [b - a - 1]}],
+                 "end": ["r"] if b == len(ids) else []} for i, (a, b) in enumerate(cuts)]
+    whole = [{"step": 0, "entries": [{"id": "r", "tokens": ids, "want": [b - 1 for _, b in cuts]}], "end": ["r"]}]
+
+    def run(steps, dtype):
+        per_step = trace_util.run_in_process(folder, dtype, steps, trace_util.max_live_tokens(steps, PAGE), PAGE)
+        return trace_util.collect(steps, per_step)["r"]
+
+    one, cut = run(whole, "bfloat16"), run(portions, "bfloat16")
+    assert ops.attention_prefill_tc_status() == 0 and ops.gemm_tc_status() == 0
+    scale = one.abs().max().item()
+    assert (one - cut).abs().max().item() <= TOL_SAME["bfloat16"] * scale
+    exact = run(portions, "float32")
+    assert (exact - cut).abs().max().item() <= TOL["bfloat16"] * exact.abs().max().item()
+    agree = (exact.argmax(-1) == cut.argmax(-1)).float().mean().item()
+    assert agree >= 0.9, agree
+
+
 def _count_routes(model) -> dict[str, int]:
     """How many products each route of every ``Linear`` of the model took so far, by matrix shape,
     plus which form the feed-forward and the conv mixer took."""
