@@ -593,7 +593,7 @@ def ingraph_table(layers: int, batch: int, ctx: int, page: int) -> None:
     print(f"  the kinds sum to {sum(r[0] for r in rows):.1f} us of the step's {whole:.1f}")
 
 
-def chunked_prefill(model, cfg, page: int, prompt: int, budget: int) -> dict:
+def chunked_prefill(model, cfg, page: int, prompt: int, budget: int, max_new: int = 2) -> dict:
     """One long prompt through the engine in portions of ``budget`` tokens, as the scheduler cuts
     it (late portions are few tiles behind a long context): wall clock of the whole call, one
     request, the better of two calls after the engine has warmed up."""
@@ -609,7 +609,7 @@ def chunked_prefill(model, cfg, page: int, prompt: int, budget: int) -> dict:
     for _ in range(2):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        eng.generate([Request(ids, max_new=2)])
+        eng.generate([Request(ids, max_new=max_new)])
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
@@ -966,6 +966,13 @@ def main() -> int:
         except Exception as exc:  # the line above it must not be lost to this point
             print(f"bench.py: the chunked prefill point failed: {exc}", file=sys.stderr)
             points["prefill_32k_by_512"] = None
+        # the 2,048-token prompt as the reference arm times it: one request with one new token
+        # through the engine's own generate call, wall clock
+        try:
+            points["prefill_2048_through_engine_ms"] = chunked_prefill(model, cfg, args.page, PROMPT, PROMPT, 1)["ms"]
+        except Exception as exc:
+            print(f"bench.py: the prefill-through-the-engine point failed: {exc}", file=sys.stderr)
+            points["prefill_2048_through_engine_ms"] = None
     e2e = e2e_decode(llm, cfg, args.batch, args.steps, warmup)
     clock_report = clocks.stop()
     llm.close()
