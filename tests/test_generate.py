@@ -268,10 +268,14 @@ def test_a_kernel_that_gave_up_on_a_barrier_fails_the_waiting_caller(model_folde
         ok = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=3))
         assert len(ok[0].token_ids) == 3 and llm.failure is None
         monkeypatch.setattr(ops, "gemm_tc_status", lambda: 2)
+        # a ticket that such a kernel left drawn must not reach the next launch
+        drawn = ops._decode_tickets(8, torch.device("cuda", torch.cuda.current_device()))
+        drawn[3] = 1
         with pytest.raises(RuntimeError, match="engine thread failed") as err:
             llm.generate([[1, 2, 3]], SamplingParams(max_tokens=3))
         assert "gave up waiting on a barrier (place 2)" in str(err.value.__cause__)
         assert isinstance(llm.failure, RuntimeError)
+        assert int(drawn.abs().sum()) == 0
 
 
 @pytest.mark.filterwarnings("ignore::pytest.PytestUnhandledThreadExceptionWarning")

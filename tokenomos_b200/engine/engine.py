@@ -241,6 +241,7 @@ class Engine:
         self._checked_at = self.stats.steps
         for what, where in (("GEMM", ops.gemm_tc_status()), ("attention", ops.attention_prefill_tc_status())):
             if where:
+                ops.clear_tickets()      # a CTA that gave up may have left its tile's ticket drawn
                 raise RuntimeError(f"a tcgen05 {what} kernel gave up waiting on a barrier (place {where}); "
                                    "the tokens of the steps since the last check are not to be trusted")
         if ops.checks_enabled():

@@ -403,6 +403,13 @@ def _decode_tickets(n: int, device: torch.device) -> torch.Tensor:
     return have
 
 
+def clear_tickets() -> None:
+    """Put the ticket counters back to zero. The kernels that use them leave them at zero; one
+    that gave up on a barrier half way may not have, and the next launch must not inherit that."""
+    for t in list(_tickets.values()) + _tickets_outgrown:
+        t.zero_()
+
+
 def attention_decode_fused(qkv: torch.Tensor, kv_pool: torch.Tensor, q_norm: torch.Tensor | None,
                            k_norm: torch.Tensor | None, eps: float, inv_freq: torch.Tensor,
                            gate: torch.Tensor | None, positions: torch.Tensor, tok_seq: torch.Tensor,
